@@ -1,0 +1,77 @@
+"""CPU oracle of the masked GEMM.  TEST INFRASTRUCTURE ONLY -- never imported by the product path.
+
+Restates, in NumPy, what the reference defines the operation to be:
+
+* the dense-masked form `matmul(x, kernel * mask)` of the reference's model code
+  (Pruning/BERT/utils/modeling.py:992-1007; VGG/NMT rewire consumers to `w * mask`,
+  Pruning/VGG/myhook.py:146-166);
+* the compaction form its perf driver checks the kernel against: gather the kept K rows of A,
+  multiply by the tile's compacted weights, scatter the result columns
+  (Stream_Gemm_NN_reference, StreamMaskedGEMM/perf/basic_nn.cu:450-503; deleteRow/insertRow,
+  :141-194; weight compaction gen_masked_stream_weight, :757-769);
+* the driver's acceptance rule `checkout` (basic_nn.cu:771-798).
+
+Parity status: the reference holds no stored vectors for GEMM results (its only check is the
+in-binary comparison of the kernel with compaction + cuBLAS on unseeded random data,
+basic_nn.cu:1081-1090), and its CUDA kernel cannot be run here (no GPU in the build container; the
+Volta-only MMA bodies compile to nothing for sm_100).  The two restatements below are checked
+against each other and against float64; beyond that the GEMM parity is unpinned by reference data.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+
+def masked_matmul_dense(A, W, mask, dtype=np.float32):
+    """C[M, N] = A[M, K] @ (W[K, N] * mask)  (modeling.py:1001-1003, bias left out)."""
+    A = np.asarray(A, dtype=dtype)
+    Wm = np.asarray(W, dtype=dtype) * (np.asarray(mask) != 0)
+    return A @ Wm
+
+
+def pack_weights(W, tiles, rows_per_tile=128, ld=None, dtype=np.float32):
+    """Wp[t*rows_per_tile + j, i] = W[kept_k_t[i], kept_n_t[j]]  (basic_nn.cu:757-769), zero padded."""
+    W = np.asarray(W)
+    kc = tiles.k_counts()
+    if ld is None:
+        ld = max(64, int(-(-int(kc.max(initial=0)) // 64) * 64))
+    out = np.zeros((max(1, tiles.n_tiles) * rows_per_tile, ld), dtype=dtype)
+    for t in range(tiles.n_tiles):
+        r, c = tiles.tile_rows(t), tiles.tile_cols(t)
+        if len(r) and len(c):
+            out[t * rows_per_tile:t * rows_per_tile + len(c), :len(r)] = W[np.ix_(r, c)].T.astype(dtype)
+    return out
+
+
+def masked_matmul_compacted(At, W, tiles, alpha=1.0, beta=0.0, Ct=None, dtype=np.float32):
+    """Ct[N, M] by compaction (basic_nn.cu:450-503): per tile, gather the kept rows of At[K, M],
+    multiply by the compacted tile weights, write the kept columns' rows of Ct."""
+    At = np.asarray(At, dtype=dtype)
+    W = np.asarray(W, dtype=dtype)
+    K, M = At.shape
+    out = np.zeros((tiles.N, M), dtype=dtype) if Ct is None else np.array(Ct, dtype=dtype)
+    for t in range(tiles.n_tiles):
+        r, c = tiles.tile_rows(t), tiles.tile_cols(t)
+        if len(c) == 0:
+            continue
+        acc = W[np.ix_(r, c)].T @ At[r, :] if len(r) else np.zeros((len(c), M), dtype=dtype)
+        out[c, :] = alpha * acc + (beta * out[c, :] if beta != 0 else 0)
+    return out
+
+
+def checkout_errors(test, ref, err=1e-2):
+    """Number of elements the reference's acceptance rule rejects (basic_nn.cu:785):
+    v1/v2 > 1+err  or  v2/v1 > 1+err  or  |v2-v1| > err."""
+    v2 = np.asarray(test, dtype=np.float32).ravel()
+    v1 = np.asarray(ref, dtype=np.float32).ravel()
+    with np.errstate(divide="ignore", invalid="ignore"):
+        bad = (v1 / v2 > 1 + err) | (v2 / v1 > 1 + err) | (np.abs(v2 - v1) > err)
+    return int(bad.sum())
+
+
+def max_rel_error(test, ref):
+    """max |test - ref| / max |ref|: the matrix-level relative error the acceptance bound uses."""
+    test = np.asarray(test, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    denom = np.abs(ref).max()
+    return float(np.abs(test - ref).max() / denom) if denom > 0 else float(np.abs(test).max())

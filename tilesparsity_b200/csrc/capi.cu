@@ -1,0 +1,613 @@
+// C ABI of libtilesparse: argument checking, device bookkeeping, scheduling and kernel launches.
+// See include/tilesparse.h for the contract of every entry point.
+#include "../../include/tilesparse.h"
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <string>
+#include <vector>
+
+#include "ts_kernels.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define TS_CUDA(expr)                                                                    \
+  do {                                                                                   \
+    cudaError_t e_ = (expr);                                                             \
+    if (e_ != cudaSuccess) {                                                             \
+      return fail(e_ == cudaErrorMemoryAllocation ? TS_ERR_NOMEM : TS_ERR_CUDA,          \
+                  "%s failed: %s", #expr, cudaGetErrorString(e_));                       \
+    }                                                                                    \
+  } while (0)
+
+// cuTensorMapEncodeTiled is fetched through the runtime so the library links against cudart only.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+// Tensor map over a packed weight matrix [rows][ldw] of 16-bit elements, box 64 (K) x 128 (rows),
+// 128-byte swizzle, zero fill outside the matrix.
+int make_weight_tmap(CUtensorMap* map, int dtype, const void* base, long long rows, long long ldw) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (ldw * 2) % 16 != 0) {
+    return fail(TS_ERR_INVALID, "packed weights need a 16-byte aligned base and row pitch");
+  }
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(ldw), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldw) * 2};
+  cuuint32_t box[2] = {64, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dtype == TS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return TS_OK;
+}
+
+struct Schedule {
+  ts::WorkUnit* d_units = nullptr;
+  int rounds = 0;
+  int grid = 0;
+  int n_units = 0;
+  std::vector<float> cta_cost;
+};
+
+// Cost of one work unit in 64-row K blocks; the constant stands for the epilogue (TMEM read-out,
+// conversion and the output rows' bulk stores), which weighs about as much as two K blocks.
+inline float unit_cost(int k_count) { return static_cast<float>((k_count + 63) / 64) + 2.0f; }
+
+// Longest-processing-time list scheduling of (tile, batch block) units onto `n_ctas` persistent
+// CTAs.  Output: flat [rounds][grid] table, tile = -1 where a CTA has no unit in that round.
+void build_schedule(const std::vector<int>& k_counts, const std::vector<int>& n_counts, int M,
+                    int unit_rows, int n_ctas, std::vector<ts::WorkUnit>* flat, int* rounds,
+                    int* grid, int* n_units, std::vector<float>* cta_cost) {
+  struct U {
+    int tile, mb;
+    float cost;
+  };
+  std::vector<U> units;
+  const int mblocks = (M + unit_rows - 1) / unit_rows;
+  std::vector<int> order;
+  for (int t = 0; t < static_cast<int>(k_counts.size()); ++t) {
+    if (n_counts[t] > 0) order.push_back(t);
+  }
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int a, int b) { return k_counts[a] > k_counts[b]; });
+  for (int t : order) {
+    for (int mb = 0; mb < mblocks; ++mb) units.push_back({t, mb, unit_cost(k_counts[t])});
+  }
+  *n_units = static_cast<int>(units.size());
+  const int g = std::max(1, std::min(n_ctas, *n_units));
+  std::vector<std::vector<ts::WorkUnit>> lists(g);
+  typedef std::pair<float, int> Load;  // (load, cta), smallest load first, then lowest cta
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int b = 0; b < g; ++b) heap.push({0.0f, b});
+  cta_cost->assign(g, 0.0f);
+  for (const U& u : units) {
+    Load l = heap.top();
+    heap.pop();
+    lists[l.second].push_back({u.tile, u.mb});
+    l.first += u.cost;
+    (*cta_cost)[l.second] = l.first;
+    heap.push(l);
+  }
+  int r = 0;
+  for (const auto& l : lists) r = std::max<int>(r, static_cast<int>(l.size()));
+  flat->assign(static_cast<size_t>(r) * g, ts::WorkUnit{-1, 0});
+  for (int b = 0; b < g; ++b) {
+    for (size_t i = 0; i < lists[b].size(); ++i) (*flat)[i * g + b] = lists[b][i];
+  }
+  *rounds = r;
+  *grid = g;
+}
+
+int current_sm_count(int* out) {
+  int dev = 0;
+  TS_CUDA(cudaGetDevice(&dev));
+  TS_CUDA(cudaDeviceGetAttribute(out, cudaDevAttrMultiProcessorCount, dev));
+  return TS_OK;
+}
+
+}  // namespace
+
+struct ts_layer {
+  int K = 0, N = 0, G = 0, dtype = 0;
+  int device = 0;
+  int sm_count = 0;
+  int n_tiles = 0;
+  std::vector<int> tile_k_ptr, kept_k, tile_n_ptr, kept_n;  // absolute indices
+  std::vector<int> k_counts, n_counts;
+  int max_k = 0;
+  int* d_kept_k = nullptr;
+  int* d_kept_n = nullptr;
+  ts::TileDesc* d_tiles = nullptr;
+  uint16_t* d_wp = nullptr;
+  long long wp_rows = 0, ldw = 0;
+  bool packed = false;
+  CUtensorMap tmap;
+  int* d_status = nullptr;
+  std::map<int, Schedule> schedules;
+  void* d_at = nullptr;
+  size_t at_bytes = 0;
+  void* d_ct = nullptr;
+  size_t ct_bytes = 0;
+};
+
+namespace {
+
+void free_tiles(ts_layer* l) {
+  cudaFree(l->d_kept_k);
+  cudaFree(l->d_kept_n);
+  cudaFree(l->d_tiles);
+  cudaFree(l->d_wp);
+  l->d_kept_k = l->d_kept_n = nullptr;
+  l->d_tiles = nullptr;
+  l->d_wp = nullptr;
+  for (auto& kv : l->schedules) cudaFree(kv.second.d_units);
+  l->schedules.clear();
+  l->packed = false;
+}
+
+int get_schedule(ts_layer* l, int M, Schedule** out) {
+  auto it = l->schedules.find(M);
+  if (it != l->schedules.end()) {
+    *out = &it->second;
+    return TS_OK;
+  }
+  if (l->schedules.size() >= 16) {  // bounded cache: drop everything, rebuild on demand
+    TS_CUDA(cudaDeviceSynchronize());
+    for (auto& kv : l->schedules) cudaFree(kv.second.d_units);
+    l->schedules.clear();
+  }
+  Schedule s;
+  std::vector<ts::WorkUnit> flat;
+  build_schedule(l->k_counts, l->n_counts, M, ts::masked_gemm_unit_rows(), l->sm_count, &flat,
+                 &s.rounds, &s.grid, &s.n_units, &s.cta_cost);
+  if (!flat.empty()) {
+    TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkUnit)));
+    TS_CUDA(cudaMemcpy(s.d_units, flat.data(), flat.size() * sizeof(ts::WorkUnit),
+                       cudaMemcpyHostToDevice));
+  }
+  auto ins = l->schedules.emplace(M, s);
+  *out = &ins.first->second;
+  return TS_OK;
+}
+
+int check_gemm_args(const ts_layer* l, int M, const void* At, int64_t lda, const void* Ct,
+                    int64_t ldc) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (!l->packed) return fail(TS_ERR_INVALID, "layer has no packed weights (call ts_layer_pack_weights)");
+  if (M < 0 || (M % 8) != 0) return fail(TS_ERR_INVALID, "M=%d must be a non-negative multiple of 8", M);
+  if (M == 0) return TS_OK;
+  if (!At || !Ct) return fail(TS_ERR_INVALID, "At/Ct is NULL");
+  if (lda < M || ldc < M || (lda % 8) != 0 || (ldc % 8) != 0) {
+    return fail(TS_ERR_INVALID, "lda=%lld / ldc=%lld must be multiples of 8 and >= M=%d",
+                (long long)lda, (long long)ldc, M);
+  }
+  if ((reinterpret_cast<uintptr_t>(At) & 15u) || (reinterpret_cast<uintptr_t>(Ct) & 15u)) {
+    return fail(TS_ERR_INVALID, "At and Ct must be 16-byte aligned");
+  }
+  return TS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ts_version(void) { return 100; }
+
+int ts_last_error(char* buf, int n) {
+  if (!buf || n <= 0) return 0;
+  const int len = std::min<int>(n - 1, static_cast<int>(g_last_error.size()));
+  memcpy(buf, g_last_error.data(), len);
+  buf[len] = 0;
+  return len;
+}
+
+int ts_layer_create(ts_layer_t** out, int K, int N, int G, int dtype) {
+  if (!out) return fail(TS_ERR_INVALID, "out is NULL");
+  *out = nullptr;
+  if (K <= 0 || N <= 0) return fail(TS_ERR_INVALID, "K=%d and N=%d must be positive", K, N);
+  if (G <= 0 || G > 128) return fail(TS_ERR_INVALID, "G=%d must be in [1, 128]", G);
+  if (dtype != TS_DTYPE_F16 && dtype != TS_DTYPE_BF16) {
+    return fail(TS_ERR_INVALID, "dtype must be TS_DTYPE_F16 or TS_DTYPE_BF16");
+  }
+  int dev = 0, sms = 0, major = 0;
+  TS_CUDA(cudaGetDevice(&dev));
+  TS_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  TS_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10) {
+    return fail(TS_ERR_UNSUPPORTED, "device %d has compute capability %d.x; this library is sm_100a only",
+                dev, major);
+  }
+  ts_layer* l = new ts_layer();
+  l->K = K;
+  l->N = N;
+  l->G = G;
+  l->dtype = dtype;
+  l->device = dev;
+  l->sm_count = sms;
+  cudaError_t e = cudaMalloc(&l->d_status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(l->d_status, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    delete l;
+    return fail(TS_ERR_CUDA, "status word allocation failed: %s", cudaGetErrorString(e));
+  }
+  *out = l;
+  return TS_OK;
+}
+
+int ts_layer_destroy(ts_layer_t* l) {
+  if (!l) return TS_OK;
+  cudaDeviceSynchronize();
+  free_tiles(l);
+  cudaFree(l->d_status);
+  cudaFree(l->d_at);
+  cudaFree(l->d_ct);
+  delete l;
+  return TS_OK;
+}
+
+int ts_layer_set_tiles(ts_layer_t* l, int n_tiles, const int32_t* tile_k_ptr,
+                       const int32_t* kept_k_idx, const int32_t* tile_n_ptr,
+                       const int32_t* kept_n_idx, int index_format) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (n_tiles < 0) return fail(TS_ERR_INVALID, "n_tiles=%d is negative", n_tiles);
+  if (n_tiles > 0 && (!tile_k_ptr || !tile_n_ptr)) return fail(TS_ERR_INVALID, "tile pointers are NULL");
+  if (index_format != TS_INDEX_ABSOLUTE && index_format != TS_INDEX_RELATIVE) {
+    return fail(TS_ERR_INVALID, "unknown index_format %d", index_format);
+  }
+  std::vector<int> kp(n_tiles + 1, 0), np(n_tiles + 1, 0), kk, nn, kc(n_tiles), nc(n_tiles);
+  if (n_tiles > 0) {
+    if (tile_k_ptr[0] != 0 || tile_n_ptr[0] != 0) return fail(TS_ERR_INVALID, "tile pointers must start at 0");
+    for (int t = 0; t < n_tiles; ++t) {
+      if (tile_k_ptr[t + 1] < tile_k_ptr[t] || tile_n_ptr[t + 1] < tile_n_ptr[t]) {
+        return fail(TS_ERR_INVALID, "tile pointers must be non-decreasing (tile %d)", t);
+      }
+    }
+    const int tk = tile_k_ptr[n_tiles], tn = tile_n_ptr[n_tiles];
+    if ((tk > 0 && !kept_k_idx) || (tn > 0 && !kept_n_idx)) return fail(TS_ERR_INVALID, "index lists are NULL");
+    kk.resize(tk);
+    nn.resize(tn);
+    for (int t = 0; t < n_tiles; ++t) {
+      kp[t + 1] = tile_k_ptr[t + 1];
+      np[t + 1] = tile_n_ptr[t + 1];
+      kc[t] = kp[t + 1] - tile_k_ptr[t];
+      nc[t] = np[t + 1] - tile_n_ptr[t];
+      if (nc[t] > l->G) return fail(TS_ERR_INVALID, "tile %d keeps %d columns, more than G=%d", t, nc[t], l->G);
+      int prev = -1;
+      for (int i = 0; i < kc[t]; ++i) {
+        const int p = tile_k_ptr[t] + i;
+        const int v = kept_k_idx[p] + (index_format == TS_INDEX_RELATIVE ? i : 0);
+        if (v < 0 || v >= l->K) return fail(TS_ERR_INVALID, "tile %d: kept row %d out of [0,%d)", t, v, l->K);
+        if (v <= prev) return fail(TS_ERR_INVALID, "tile %d: kept rows must be strictly ascending", t);
+        prev = v;
+        kk[p] = v;
+      }
+      for (int j = 0; j < nc[t]; ++j) {
+        const int p = tile_n_ptr[t] + j;
+        const int v = kept_n_idx[p] + (index_format == TS_INDEX_RELATIVE ? j : 0);
+        if (v < 0 || v >= l->N) return fail(TS_ERR_INVALID, "tile %d: kept column %d out of [0,%d)", t, v, l->N);
+        nn[p] = v;
+      }
+    }
+  }
+  TS_CUDA(cudaSetDevice(l->device));
+  TS_CUDA(cudaDeviceSynchronize());
+  free_tiles(l);
+  l->n_tiles = n_tiles;
+  l->tile_k_ptr = kp;
+  l->tile_n_ptr = np;
+  l->kept_k = kk;
+  l->kept_n = nn;
+  l->k_counts = kc;
+  l->n_counts = nc;
+  l->max_k = 0;
+  for (int v : kc) l->max_k = std::max(l->max_k, v);
+  l->ldw = std::max<long long>(64, (l->max_k + 63) / 64 * 64);
+  l->wp_rows = static_cast<long long>(std::max(1, n_tiles)) * 128;
+  TS_CUDA(cudaMalloc(&l->d_kept_k, std::max<size_t>(1, kk.size()) * sizeof(int)));
+  TS_CUDA(cudaMalloc(&l->d_kept_n, std::max<size_t>(1, nn.size()) * sizeof(int)));
+  TS_CUDA(cudaMalloc(&l->d_tiles, std::max(1, n_tiles) * sizeof(ts::TileDesc)));
+  TS_CUDA(cudaMalloc(&l->d_wp, static_cast<size_t>(l->wp_rows) * l->ldw * 2));
+  if (!kk.empty()) TS_CUDA(cudaMemcpy(l->d_kept_k, kk.data(), kk.size() * sizeof(int), cudaMemcpyHostToDevice));
+  if (!nn.empty()) TS_CUDA(cudaMemcpy(l->d_kept_n, nn.data(), nn.size() * sizeof(int), cudaMemcpyHostToDevice));
+  std::vector<ts::TileDesc> td(n_tiles);
+  for (int t = 0; t < n_tiles; ++t) {
+    td[t].k_list = l->d_kept_k + kp[t];
+    td[t].n_list = l->d_kept_n + np[t];
+    td[t].k_count = kc[t];
+    td[t].n_count = nc[t];
+    td[t].w_row0 = t * 128;
+    td[t].c_row0 = 0;
+    td[t].relative = 0;
+    td[t].pad_ = 0;
+  }
+  if (n_tiles > 0) {
+    TS_CUDA(cudaMemcpy(l->d_tiles, td.data(), td.size() * sizeof(ts::TileDesc), cudaMemcpyHostToDevice));
+  }
+  return make_weight_tmap(&l->tmap, l->dtype, l->d_wp, l->wp_rows, l->ldw);
+}
+
+int ts_layer_pack_weights(ts_layer_t* l, const void* W_dev, int64_t ldw_in, int w_dtype, void* stream) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (!l->d_wp) return fail(TS_ERR_INVALID, "layer has no tiles (call ts_layer_set_tiles)");
+  if (!W_dev) return fail(TS_ERR_INVALID, "W is NULL");
+  if (ldw_in < l->N) return fail(TS_ERR_INVALID, "ldw_in=%lld is smaller than N=%d", (long long)ldw_in, l->N);
+  if (w_dtype != TS_DTYPE_F16 && w_dtype != TS_DTYPE_BF16 && w_dtype != TS_DTYPE_F32) {
+    return fail(TS_ERR_INVALID, "unknown weight dtype %d", w_dtype);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TS_CUDA(cudaMemsetAsync(l->d_wp, 0, static_cast<size_t>(l->wp_rows) * l->ldw * 2, s));
+  TS_CUDA(ts::pack_weights_launch(w_dtype, l->dtype, W_dev, ldw_in, l->d_tiles, l->n_tiles, l->max_k,
+                                  l->d_wp, l->ldw, s));
+  l->packed = true;
+  return TS_OK;
+}
+
+int ts_layer_get_packed(const ts_layer_t* l, void* out_host, int64_t* rows, int64_t* ldw) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (rows) *rows = l->wp_rows;
+  if (ldw) *ldw = l->ldw;
+  if (!out_host) return TS_OK;
+  if (!l->packed) return fail(TS_ERR_INVALID, "layer has no packed weights");
+  TS_CUDA(cudaDeviceSynchronize());
+  TS_CUDA(cudaMemcpy(out_host, l->d_wp, static_cast<size_t>(l->wp_rows) * l->ldw * 2, cudaMemcpyDeviceToHost));
+  return TS_OK;
+}
+
+int ts_layer_stats(const ts_layer_t* l, int64_t* kept_flops_per_row, int64_t* packed_bytes,
+                   int64_t* index_bytes, int* n_tiles, int* max_kept_k) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  int64_t kn = 0, idx = 0;
+  for (int t = 0; t < l->n_tiles; ++t) {
+    kn += static_cast<int64_t>(l->k_counts[t]) * l->n_counts[t];
+    idx += l->k_counts[t] + l->n_counts[t];
+  }
+  if (kept_flops_per_row) *kept_flops_per_row = 2 * kn;
+  if (packed_bytes) *packed_bytes = 2 * kn;
+  if (index_bytes) *index_bytes = 4 * idx;
+  if (n_tiles) *n_tiles = l->n_tiles;
+  if (max_kept_k) *max_kept_k = l->max_k;
+  return TS_OK;
+}
+
+int ts_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
+                   float alpha, float beta, void* stream) {
+  int rc = check_gemm_args(l, M, At, lda, Ct, ldc);
+  if (rc != TS_OK) return rc;
+  if (M == 0 || l->n_tiles == 0) return TS_OK;
+  Schedule* s = nullptr;
+  rc = get_schedule(l, M, &s);
+  if (rc != TS_OK) return rc;
+  if (s->n_units == 0) return TS_OK;
+  TS_CUDA(ts::masked_gemm_launch(l->dtype, l->tmap, l->d_tiles, s->d_units, s->rounds, s->grid, At, lda,
+                                 Ct, ldc, M, alpha, beta, l->d_status, static_cast<cudaStream_t>(stream)));
+  return TS_OK;
+}
+
+int ts_masked_gemm_simt(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
+                        float alpha, float beta, void* stream) {
+  int rc = check_gemm_args(l, M, At, lda, Ct, ldc);
+  if (rc != TS_OK) return rc;
+  if (M == 0 || l->n_tiles == 0) return TS_OK;
+  TS_CUDA(ts::masked_gemm_simt_launch(l->dtype, l->d_tiles, l->n_tiles, l->d_wp, l->ldw, At, lda, Ct, ldc,
+                                      M, alpha, beta, static_cast<cudaStream_t>(stream)));
+  return TS_OK;
+}
+
+int ts_masked_gemm_host(ts_layer_t* l, int M, const void* At_host, void* Ct_host, float alpha,
+                        float beta, void* stream) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (M <= 0 || (M % 8) != 0) return fail(TS_ERR_INVALID, "M=%d must be a positive multiple of 8", M);
+  if (!At_host || !Ct_host) return fail(TS_ERR_INVALID, "host buffers are NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t a_bytes = static_cast<size_t>(l->K) * M * 2, c_bytes = static_cast<size_t>(l->N) * M * 2;
+  if (a_bytes > l->at_bytes) {
+    TS_CUDA(cudaStreamSynchronize(s));
+    cudaFree(l->d_at);
+    l->d_at = nullptr;
+    l->at_bytes = 0;
+    TS_CUDA(cudaMalloc(&l->d_at, a_bytes));
+    l->at_bytes = a_bytes;
+  }
+  if (c_bytes > l->ct_bytes) {
+    TS_CUDA(cudaStreamSynchronize(s));
+    cudaFree(l->d_ct);
+    l->d_ct = nullptr;
+    l->ct_bytes = 0;
+    TS_CUDA(cudaMalloc(&l->d_ct, c_bytes));
+    l->ct_bytes = c_bytes;
+    // Columns no tile keeps are never written by the kernel: they stay zero in the staging buffer.
+    TS_CUDA(cudaMemsetAsync(l->d_ct, 0, c_bytes, s));
+  }
+  TS_CUDA(cudaMemcpyAsync(l->d_at, At_host, a_bytes, cudaMemcpyHostToDevice, s));
+  if (beta != 0.0f) TS_CUDA(cudaMemcpyAsync(l->d_ct, Ct_host, c_bytes, cudaMemcpyHostToDevice, s));
+  int rc = ts_masked_gemm(l, M, l->d_at, M, l->d_ct, M, alpha, beta, stream);
+  if (rc != TS_OK) return rc;
+  TS_CUDA(cudaMemcpyAsync(Ct_host, l->d_ct, c_bytes, cudaMemcpyDeviceToHost, s));
+  TS_CUDA(cudaStreamSynchronize(s));
+  return TS_OK;
+}
+
+int ts_layer_check(ts_layer_t* l, void* stream) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int st = 0;
+  TS_CUDA(cudaMemcpyAsync(&st, l->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  TS_CUDA(cudaStreamSynchronize(s));
+  if (st != 0) {
+    TS_CUDA(cudaMemsetAsync(l->d_status, 0, sizeof(int), s));
+    TS_CUDA(cudaStreamSynchronize(s));
+    return fail(st, "a masked GEMM kernel reported status %d (%s)", st,
+                st == TS_ERR_TIMEOUT ? "a bounded device-side wait ran out" : "unknown");
+  }
+  return TS_OK;
+}
+
+int ts_layer_schedule_stats(ts_layer_t* l, int M, int* n_ctas, float* cta_cost, int* n_units) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (M <= 0) return fail(TS_ERR_INVALID, "M=%d must be positive", M);
+  if (!l->d_tiles) return fail(TS_ERR_INVALID, "layer has no tiles");
+  Schedule* s = nullptr;
+  int rc = get_schedule(l, M, &s);
+  if (rc != TS_OK) return rc;
+  if (n_ctas) *n_ctas = s->grid;
+  if (n_units) *n_units = s->n_units;
+  if (cta_cost) memcpy(cta_cost, s->cta_cost.data(), s->cta_cost.size() * sizeof(float));
+  return TS_OK;
+}
+
+// Workspace of the reference-signature entry point: one per device, grown on demand, reused by
+// every call (calls on one device must be issued on one stream or externally ordered).
+namespace {
+struct ShimWorkspace {
+  ts::TileDesc* d_tiles = nullptr;
+  ts::WorkUnit* d_units = nullptr;
+  size_t unit_cap = 0;
+  int* d_status = nullptr;
+};
+std::mutex g_shim_mu;
+std::map<int, ShimWorkspace> g_shim_ws;
+}  // namespace
+
+int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const void* B, float beta,
+                      void* C, int block_num, const int* N_cal, const int* K_cal,
+                      int* const* mask_n, int* const* mask_k, const int* off_B, const int* off_C,
+                      int dtype, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(TS_ERR_INVALID, "M, N, K must be positive");
+  if ((M % 8) != 0 || (K % 8) != 0) return fail(TS_ERR_INVALID, "M and K must be multiples of 8");
+  if (block_num < 0 || block_num > 32) {
+    return fail(TS_ERR_INVALID, "block_num=%d out of [0, 32] (MAX_BLOCK_NUM of the reference)", block_num);
+  }
+  if (dtype != TS_DTYPE_F16 && dtype != TS_DTYPE_BF16) return fail(TS_ERR_INVALID, "dtype must be f16 or bf16");
+  if (block_num == 0) return TS_OK;
+  if (!A || !B || !C || !N_cal || !K_cal || !mask_n || !mask_k || !off_B || !off_C) {
+    return fail(TS_ERR_INVALID, "NULL argument");
+  }
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(C) & 15u)) {
+    return fail(TS_ERR_INVALID, "A and C must be 16-byte aligned");
+  }
+  std::vector<ts::TileDesc> td(block_num);
+  std::vector<int> kc(block_num), nc(block_num);
+  for (int t = 0; t < block_num; ++t) {
+    if (N_cal[t] < 0 || N_cal[t] > 128) return fail(TS_ERR_INVALID, "N_cal[%d]=%d out of [0,128]", t, N_cal[t]);
+    if (K_cal[t] < 0 || K_cal[t] > K) return fail(TS_ERR_INVALID, "K_cal[%d]=%d out of [0,K]", t, K_cal[t]);
+    if (off_B[t] % K != 0 || off_C[t] % M != 0) {
+      return fail(TS_ERR_INVALID, "off_B[%d] must be a multiple of K and off_C[%d] of M", t, t);
+    }
+    if ((K_cal[t] > 0 && !mask_k[t]) || (N_cal[t] > 0 && !mask_n[t])) {
+      return fail(TS_ERR_INVALID, "mask pointer of tile %d is NULL", t);
+    }
+    td[t].k_list = mask_k[t];
+    td[t].n_list = mask_n[t];
+    td[t].k_count = kc[t] = K_cal[t];
+    td[t].n_count = nc[t] = N_cal[t];
+    td[t].w_row0 = off_B[t] / K;
+    td[t].c_row0 = off_C[t] / M;
+    td[t].relative = 1;
+    td[t].pad_ = 0;
+  }
+  int dev = 0, sms = 0;
+  TS_CUDA(cudaGetDevice(&dev));
+  int rc = current_sm_count(&sms);
+  if (rc != TS_OK) return rc;
+  std::vector<ts::WorkUnit> flat;
+  std::vector<float> cost;
+  int rounds = 0, grid = 0, n_units = 0;
+  build_schedule(kc, nc, M, ts::masked_gemm_unit_rows(), sms, &flat, &rounds, &grid, &n_units, &cost);
+  if (n_units == 0) return TS_OK;
+  CUtensorMap tmap;
+  rc = make_weight_tmap(&tmap, dtype, B, N, K);
+  if (rc != TS_OK) return rc;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::lock_guard<std::mutex> lock(g_shim_mu);
+  ShimWorkspace& ws = g_shim_ws[dev];
+  if (!ws.d_tiles) {
+    TS_CUDA(cudaMalloc(&ws.d_tiles, 32 * sizeof(ts::TileDesc)));
+    TS_CUDA(cudaMalloc(&ws.d_status, sizeof(int)));
+    TS_CUDA(cudaMemset(ws.d_status, 0, sizeof(int)));
+  }
+  if (flat.size() > ws.unit_cap) {
+    TS_CUDA(cudaStreamSynchronize(s));
+    cudaFree(ws.d_units);
+    ws.d_units = nullptr;
+    ws.unit_cap = 0;
+    TS_CUDA(cudaMalloc(&ws.d_units, flat.size() * sizeof(ts::WorkUnit)));
+    ws.unit_cap = flat.size();
+  }
+  // Pageable sources: the runtime stages them before returning, so the vectors may die after this.
+  TS_CUDA(cudaMemcpyAsync(ws.d_tiles, td.data(), td.size() * sizeof(ts::TileDesc), cudaMemcpyHostToDevice, s));
+  TS_CUDA(cudaMemcpyAsync(ws.d_units, flat.data(), flat.size() * sizeof(ts::WorkUnit), cudaMemcpyHostToDevice, s));
+  TS_CUDA(ts::masked_gemm_launch(dtype, tmap, ws.d_tiles, ws.d_units, rounds, grid, A, M, C, M, M, alpha,
+                                 beta, ws.d_status, s));
+  return TS_OK;
+}
+
+int ts_transpose16(const void* in_dev, int64_t ld_in, void* out_dev, int64_t ld_out, int rows,
+                   int cols, void* stream) {
+  if (rows < 0 || cols < 0) return fail(TS_ERR_INVALID, "negative shape");
+  if (rows == 0 || cols == 0) return TS_OK;
+  if (!in_dev || !out_dev) return fail(TS_ERR_INVALID, "NULL pointer");
+  if (ld_in < cols || ld_out < rows) return fail(TS_ERR_INVALID, "leading dimensions too small");
+  TS_CUDA(ts::transpose16_launch(in_dev, ld_in, out_dev, ld_out, rows, cols, static_cast<cudaStream_t>(stream)));
+  return TS_OK;
+}
+
+int ts_shard_plan(int n_tiles, const int64_t* cost, int n_parts, int32_t* owner_out) {
+  if (n_tiles < 0 || n_parts <= 0) return fail(TS_ERR_INVALID, "n_tiles=%d, n_parts=%d", n_tiles, n_parts);
+  if (n_tiles == 0) return TS_OK;
+  if (!cost || !owner_out) return fail(TS_ERR_INVALID, "NULL argument");
+  std::vector<int> order(n_tiles);
+  for (int t = 0; t < n_tiles; ++t) order[t] = t;
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost[a] > cost[b]; });
+  typedef std::pair<int64_t, int> Load;
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int p = 0; p < n_parts; ++p) heap.push({0, p});
+  for (int t : order) {
+    Load l = heap.top();
+    heap.pop();
+    owner_out[t] = l.second;
+    l.first += std::max<int64_t>(cost[t], 0);
+    heap.push(l);
+  }
+  return TS_OK;
+}
+
+}  // extern "C"
