@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtilesparse.so")
+# TILESPARSE_LIB points the loader at another build of the same library (e.g. a traced one).
+LIB_PATH = os.environ.get("TILESPARSE_LIB") or os.path.join(HERE, "libtilesparse.so")
 
 TS_OK = 0
 TS_ERR_INVALID, TS_ERR_CUDA, TS_ERR_TIMEOUT, TS_ERR_UNSUPPORTED, TS_ERR_NOMEM = 1, 2, 3, 4, 5

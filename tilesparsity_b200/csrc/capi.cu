@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -80,10 +81,13 @@ int make_weight_tmap(CUtensorMap* map, int dtype, const void* base, long long ro
 }
 
 struct Schedule {
-  ts::WorkUnit* d_units = nullptr;
+  ts::WorkItem* d_units = nullptr;
+  ts::BlockDesc* d_blocks = nullptr;
+  int blk_stride = 0;
   int rounds = 0;
   int grid = 0;
   int n_units = 0;
+  int unit_rows = 0;
   std::vector<float> cta_cost;
 };
 
@@ -91,49 +95,100 @@ struct Schedule {
 // conversion and the output rows' bulk stores), which weighs about as much as two K blocks.
 inline float unit_cost(int k_count) { return static_cast<float>((k_count + 63) / 64) + 2.0f; }
 
+// Batch rows per work unit: 256-row units halve the weight traffic per output, 128-row units give
+// small problems enough units to occupy every SM and shorten the per-unit latency chain.  The
+// TS_UNIT_ROWS environment variable (128 or 256) overrides the choice.
+int choose_unit_rows(int n_live_tiles, int M, int n_ctas) {
+  if (const char* e = getenv("TS_UNIT_ROWS")) {
+    const int v = atoi(e);
+    if (v == 128 || v == 256) return v;
+  }
+  const long long units256 = static_cast<long long>(n_live_tiles) * ((M + 255) / 256);
+  return units256 >= 4LL * n_ctas ? 256 : 128;
+}
+
 // Longest-processing-time list scheduling of (tile, batch block) units onto `n_ctas` persistent
-// CTAs.  Output: flat [rounds][grid] table, tile = -1 where a CTA has no unit in that round.
-void build_schedule(const std::vector<int>& k_counts, const std::vector<int>& n_counts, int M,
-                    int unit_rows, int n_ctas, std::vector<ts::WorkUnit>* flat, int* rounds,
-                    int* grid, int* n_units, std::vector<float>* cta_cost) {
-  struct U {
-    int tile, mb;
-    float cost;
-  };
-  std::vector<U> units;
+// CTAs.  Output: flat [rounds][grid] table; a CTA's units fill its column from round 0 without
+// gaps, tile = -1 marks the end.
+void build_schedule(const std::vector<ts::TileDesc>& tiles, int M, int unit_rows, int n_ctas,
+                    std::vector<ts::WorkItem>* flat, int* rounds, int* grid, int* n_units,
+                    std::vector<float>* cta_cost, std::vector<ts::BlockDesc>* blocks,
+                    int* blk_stride) {
   const int mblocks = (M + unit_rows - 1) / unit_rows;
   std::vector<int> order;
-  for (int t = 0; t < static_cast<int>(k_counts.size()); ++t) {
-    if (n_counts[t] > 0) order.push_back(t);
+  for (int t = 0; t < static_cast<int>(tiles.size()); ++t) {
+    if (tiles[t].n_count > 0) order.push_back(t);
   }
   std::stable_sort(order.begin(), order.end(),
-                   [&](int a, int b) { return k_counts[a] > k_counts[b]; });
-  for (int t : order) {
-    for (int mb = 0; mb < mblocks; ++mb) units.push_back({t, mb, unit_cost(k_counts[t])});
-  }
-  *n_units = static_cast<int>(units.size());
+                   [&](int a, int b) { return tiles[a].k_count > tiles[b].k_count; });
+  *n_units = static_cast<int>(order.size()) * mblocks;
   const int g = std::max(1, std::min(n_ctas, *n_units));
-  std::vector<std::vector<ts::WorkUnit>> lists(g);
+  std::vector<std::vector<ts::WorkItem>> lists(g);
   typedef std::pair<float, int> Load;  // (load, cta), smallest load first, then lowest cta
   std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
   for (int b = 0; b < g; ++b) heap.push({0.0f, b});
   cta_cost->assign(g, 0.0f);
-  for (const U& u : units) {
-    Load l = heap.top();
-    heap.pop();
-    lists[l.second].push_back({u.tile, u.mb});
-    l.first += u.cost;
-    (*cta_cost)[l.second] = l.first;
-    heap.push(l);
+  for (int t : order) {
+    const ts::TileDesc& td = tiles[t];
+    for (int mb = 0; mb < mblocks; ++mb) {
+      Load l = heap.top();
+      heap.pop();
+      ts::WorkItem w;
+      w.k_list = td.k_list;
+      w.n_list = td.n_list;
+      w.k_count = td.k_count;
+      w.n_count = td.n_count;
+      w.w_row0 = td.w_row0;
+      w.c_row0 = td.c_row0;
+      w.relative = td.relative;
+      w.mblock = mb;
+      w.tile = t;
+      w.pad_ = 0;
+      lists[l.second].push_back(w);
+      l.first += unit_cost(td.k_count);
+      (*cta_cost)[l.second] = l.first;
+      heap.push(l);
+    }
   }
   int r = 0;
   for (const auto& l : lists) r = std::max<int>(r, static_cast<int>(l.size()));
-  flat->assign(static_cast<size_t>(r) * g, ts::WorkUnit{-1, 0});
+  ts::WorkItem none;
+  memset(&none, 0, sizeof(none));
+  none.tile = -1;
+  flat->assign(static_cast<size_t>(r) * g, none);
   for (int b = 0; b < g; ++b) {
     for (size_t i = 0; i < lists[b].size(); ++i) (*flat)[i * g + b] = lists[b][i];
   }
   *rounds = r;
   *grid = g;
+
+  // The same lists at K-block granularity for the gather warps.  The stream of every CTA ends with
+  // end markers; 24 of them cover the deepest look-ahead (4 blocks x 4 warps) with room to spare.
+  size_t max_blocks = 0;
+  for (const auto& l : lists) {
+    size_t nb = 0;
+    for (const ts::WorkItem& w : l) nb += (w.k_count + 63) / 64;
+    max_blocks = std::max(max_blocks, nb);
+  }
+  *blk_stride = static_cast<int>(max_blocks) + 24;
+  ts::BlockDesc end;
+  end.idx = nullptr;
+  end.m0 = 0;
+  end.meta = ts::kBlockEnd;
+  blocks->assign(static_cast<size_t>(g) * *blk_stride, end);
+  for (int b = 0; b < g; ++b) {
+    size_t o = static_cast<size_t>(b) * *blk_stride;
+    for (const ts::WorkItem& w : lists[b]) {
+      for (int pos = 0; pos < w.k_count; pos += 64) {
+        ts::BlockDesc d;
+        d.idx = w.k_list + pos;
+        d.m0 = w.mblock * unit_rows;
+        d.meta = static_cast<uint32_t>(std::min(64, w.k_count - pos)) | (w.relative ? 0x80u : 0u) |
+                 (static_cast<uint32_t>(pos) << 8);
+        (*blocks)[o++] = d;
+      }
+    }
+  }
 }
 
 int current_sm_count(int* out) {
@@ -156,6 +211,7 @@ struct ts_layer {
   int* d_kept_k = nullptr;
   int* d_kept_n = nullptr;
   ts::TileDesc* d_tiles = nullptr;
+  std::vector<ts::TileDesc> h_tiles;
   uint16_t* d_wp = nullptr;
   long long wp_rows = 0, ldw = 0;
   bool packed = false;
@@ -178,7 +234,10 @@ void free_tiles(ts_layer* l) {
   l->d_kept_k = l->d_kept_n = nullptr;
   l->d_tiles = nullptr;
   l->d_wp = nullptr;
-  for (auto& kv : l->schedules) cudaFree(kv.second.d_units);
+  for (auto& kv : l->schedules) {
+    cudaFree(kv.second.d_units);
+    cudaFree(kv.second.d_blocks);
+  }
   l->schedules.clear();
   l->packed = false;
 }
@@ -191,16 +250,26 @@ int get_schedule(ts_layer* l, int M, Schedule** out) {
   }
   if (l->schedules.size() >= 16) {  // bounded cache: drop everything, rebuild on demand
     TS_CUDA(cudaDeviceSynchronize());
-    for (auto& kv : l->schedules) cudaFree(kv.second.d_units);
+    for (auto& kv : l->schedules) {
+      cudaFree(kv.second.d_units);
+      cudaFree(kv.second.d_blocks);
+    }
     l->schedules.clear();
   }
   Schedule s;
-  std::vector<ts::WorkUnit> flat;
-  build_schedule(l->k_counts, l->n_counts, M, ts::masked_gemm_unit_rows(), l->sm_count, &flat,
-                 &s.rounds, &s.grid, &s.n_units, &s.cta_cost);
+  std::vector<ts::WorkItem> flat;
+  std::vector<ts::BlockDesc> blocks;
+  int live = 0;
+  for (int v : l->n_counts) live += v > 0;
+  s.unit_rows = choose_unit_rows(live, M, l->sm_count);
+  build_schedule(l->h_tiles, M, s.unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
+                 &s.cta_cost, &blocks, &s.blk_stride);
   if (!flat.empty()) {
-    TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkUnit)));
-    TS_CUDA(cudaMemcpy(s.d_units, flat.data(), flat.size() * sizeof(ts::WorkUnit),
+    TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkItem)));
+    TS_CUDA(cudaMemcpy(s.d_units, flat.data(), flat.size() * sizeof(ts::WorkItem),
+                       cudaMemcpyHostToDevice));
+    TS_CUDA(cudaMalloc(&s.d_blocks, blocks.size() * sizeof(ts::BlockDesc)));
+    TS_CUDA(cudaMemcpy(s.d_blocks, blocks.data(), blocks.size() * sizeof(ts::BlockDesc),
                        cudaMemcpyHostToDevice));
   }
   auto ins = l->schedules.emplace(M, s);
@@ -361,6 +430,7 @@ int ts_layer_set_tiles(ts_layer_t* l, int n_tiles, const int32_t* tile_k_ptr,
   if (n_tiles > 0) {
     TS_CUDA(cudaMemcpy(l->d_tiles, td.data(), td.size() * sizeof(ts::TileDesc), cudaMemcpyHostToDevice));
   }
+  l->h_tiles = td;
   return make_weight_tmap(&l->tmap, l->dtype, l->d_wp, l->wp_rows, l->ldw);
 }
 
@@ -416,7 +486,7 @@ int ts_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, 
   rc = get_schedule(l, M, &s);
   if (rc != TS_OK) return rc;
   if (s->n_units == 0) return TS_OK;
-  TS_CUDA(ts::masked_gemm_launch(l->dtype, l->tmap, l->d_tiles, s->d_units, s->rounds, s->grid, At, lda,
+  TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, l->tmap, s->d_units, s->rounds, s->grid, s->d_blocks, s->blk_stride, At, lda,
                                  Ct, ldc, M, alpha, beta, l->d_status, static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
@@ -497,9 +567,10 @@ int ts_layer_schedule_stats(ts_layer_t* l, int M, int* n_ctas, float* cta_cost, 
 // every call (calls on one device must be issued on one stream or externally ordered).
 namespace {
 struct ShimWorkspace {
-  ts::TileDesc* d_tiles = nullptr;
-  ts::WorkUnit* d_units = nullptr;
+  ts::WorkItem* d_units = nullptr;
   size_t unit_cap = 0;
+  ts::BlockDesc* d_blocks = nullptr;
+  size_t block_cap = 0;
   int* d_status = nullptr;
 };
 std::mutex g_shim_mu;
@@ -547,10 +618,13 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   TS_CUDA(cudaGetDevice(&dev));
   int rc = current_sm_count(&sms);
   if (rc != TS_OK) return rc;
-  std::vector<ts::WorkUnit> flat;
+  std::vector<ts::WorkItem> flat;
   std::vector<float> cost;
-  int rounds = 0, grid = 0, n_units = 0;
-  build_schedule(kc, nc, M, ts::masked_gemm_unit_rows(), sms, &flat, &rounds, &grid, &n_units, &cost);
+  std::vector<ts::BlockDesc> blocks;
+  int rounds = 0, grid = 0, n_units = 0, live = 0, blk_stride = 0;
+  for (int v : nc) live += v > 0;
+  const int unit_rows = choose_unit_rows(live, M, sms);
+  build_schedule(td, M, unit_rows, sms, &flat, &rounds, &grid, &n_units, &cost, &blocks, &blk_stride);
   if (n_units == 0) return TS_OK;
   CUtensorMap tmap;
   rc = make_weight_tmap(&tmap, dtype, B, N, K);
@@ -559,8 +633,7 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   std::lock_guard<std::mutex> lock(g_shim_mu);
   ShimWorkspace& ws = g_shim_ws[dev];
-  if (!ws.d_tiles) {
-    TS_CUDA(cudaMalloc(&ws.d_tiles, 32 * sizeof(ts::TileDesc)));
+  if (!ws.d_status) {
     TS_CUDA(cudaMalloc(&ws.d_status, sizeof(int)));
     TS_CUDA(cudaMemset(ws.d_status, 0, sizeof(int)));
   }
@@ -569,14 +642,23 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
     cudaFree(ws.d_units);
     ws.d_units = nullptr;
     ws.unit_cap = 0;
-    TS_CUDA(cudaMalloc(&ws.d_units, flat.size() * sizeof(ts::WorkUnit)));
+    TS_CUDA(cudaMalloc(&ws.d_units, flat.size() * sizeof(ts::WorkItem)));
     ws.unit_cap = flat.size();
   }
+  if (blocks.size() > ws.block_cap) {
+    TS_CUDA(cudaStreamSynchronize(s));
+    cudaFree(ws.d_blocks);
+    ws.d_blocks = nullptr;
+    ws.block_cap = 0;
+    TS_CUDA(cudaMalloc(&ws.d_blocks, blocks.size() * sizeof(ts::BlockDesc)));
+    ws.block_cap = blocks.size();
+  }
   // Pageable sources: the runtime stages them before returning, so the vectors may die after this.
-  TS_CUDA(cudaMemcpyAsync(ws.d_tiles, td.data(), td.size() * sizeof(ts::TileDesc), cudaMemcpyHostToDevice, s));
-  TS_CUDA(cudaMemcpyAsync(ws.d_units, flat.data(), flat.size() * sizeof(ts::WorkUnit), cudaMemcpyHostToDevice, s));
-  TS_CUDA(ts::masked_gemm_launch(dtype, tmap, ws.d_tiles, ws.d_units, rounds, grid, A, M, C, M, M, alpha,
-                                 beta, ws.d_status, s));
+  TS_CUDA(cudaMemcpyAsync(ws.d_units, flat.data(), flat.size() * sizeof(ts::WorkItem), cudaMemcpyHostToDevice, s));
+  TS_CUDA(cudaMemcpyAsync(ws.d_blocks, blocks.data(), blocks.size() * sizeof(ts::BlockDesc),
+                          cudaMemcpyHostToDevice, s));
+  TS_CUDA(ts::masked_gemm_launch(dtype, unit_rows, tmap, ws.d_units, rounds, grid, ws.d_blocks, blk_stride, A, M,
+                                 C, M, M, alpha, beta, ws.d_status, s));
   return TS_OK;
 }
 
@@ -589,6 +671,15 @@ int ts_transpose16(const void* in_dev, int64_t ld_in, void* out_dev, int64_t ld_
   TS_CUDA(ts::transpose16_launch(in_dev, ld_in, out_dev, ld_out, rows, cols, static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
+
+#ifdef TS_KERNEL_TRACE
+// Debug builds only: cycle stamps of CTA 0 of the most recent traced launches.
+int ts_debug_read_trace(long long* out64, int clear) {
+  TS_CUDA(cudaDeviceSynchronize());
+  TS_CUDA(ts::masked_gemm_read_trace(out64, clear != 0));
+  return TS_OK;
+}
+#endif
 
 int ts_shard_plan(int n_tiles, const int64_t* cost, int n_parts, int32_t* owner_out) {
   if (n_tiles < 0 || n_parts <= 0) return fail(TS_ERR_INVALID, "n_tiles=%d, n_parts=%d", n_tiles, n_parts);

@@ -43,11 +43,35 @@ struct TileDesc {
   int pad_;
 };
 
-// One unit of work for the persistent GEMM: column tile `tile`, rows [mblock*MT, +MT) of the batch.
-struct WorkUnit {
-  int tile;
+// One unit of work of the persistent GEMM: one column tile x one block of batch rows.  Entries are
+// self-contained (they carry the tile's lists and counts) so a CTA reaches its first data request
+// with two dependent global reads: work item -> kept-row indices -> activation rows.
+struct alignas(16) WorkItem {
+  const int* k_list;
+  const int* n_list;
+  int k_count;
+  int n_count;
+  int w_row0;
+  int c_row0;
+  int relative;
   int mblock;
+  int tile;  // < 0: no unit
+  int pad_;
 };
+static_assert(sizeof(WorkItem) == 48, "WorkItem is read as three 16-byte words");
+
+// One 64-row K block of a work unit, as the activation-gather warps consume it.  A CTA's blocks are
+// stored in processing order, so a gather warp addresses its descriptors by block number alone and
+// can request them, and the kept-row indices they point at, several blocks ahead.
+//   meta: bits 0-6 number of valid rows (1..64), bit 7 relative-offset lists, bits 8-31 position of
+//   the block's first row inside the tile's list; 0xFFFFFFFF marks the end of the CTA's stream.
+struct alignas(16) BlockDesc {
+  const int* idx;  // the block's first kept-row index (tile list + position)
+  int m0;          // first batch row of the unit
+  uint32_t meta;
+};
+static_assert(sizeof(BlockDesc) == 16, "BlockDesc is copied as one 16-byte word");
+constexpr uint32_t kBlockEnd = 0xFFFFFFFFu;
 
 // ---------------------------------------------------------------------------------------------
 // Generic helpers
@@ -92,17 +116,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to `hint_ns` while the phase is pending.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Cycle budget of one wait (about two seconds at 2 GHz).  A healthy pipeline waits microseconds.
 constexpr long long kWaitCycleLimit = 4000000000LL;
 
 // Bounded wait.  Returns false when the CTA is aborting (another wait ran out) or this one did.
+// A waiting warp shares its scheduler with warps that have work to issue, so between polls it
+// sleeps instead of spinning.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
+    if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
+    __nanosleep(32);
+    if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitCycleLimit) {
         *abort_flag = 1;
@@ -130,13 +172,39 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // ---------------------------------------------------------------------------------------------
 // cp.async (16-byte, L2-only) with zero fill when src_bytes == 0
 // ---------------------------------------------------------------------------------------------
+// No "memory" clobber on purpose: the destination is only ever read by the tensor core through a
+// descriptor and the source is read-only input, so the compiler may move ordinary loads (the
+// kept-row index reads that feed the next copy's address) across it.  Ordering against the stage's
+// mbarrier comes from cp.async.mbarrier.arrive, which is volatile and follows in program order.
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
-               : "memory");
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_16_ca(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// Plain 16-byte copy (no zero-fill operand): the form the load/store unit issues fastest.
+__device__ __forceinline__ void cp_async_16_full(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
 
 __device__ __forceinline__ void cp_async_commit() {
   asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// The mbarrier receives one (pre-counted) arrival once every cp.async this thread issued so far
+// has written its bytes.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 template <int N>

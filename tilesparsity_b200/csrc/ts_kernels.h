@@ -10,15 +10,20 @@
 
 namespace ts {
 
-// Batch rows covered by one work unit of the tensor-core GEMM.
-int masked_gemm_unit_rows();
-
-// Tensor-core masked GEMM (masked_gemm_sm100.cu).  `sched` holds rounds*grid work units; entry
-// r*grid + b is the r-th unit of CTA b (tile < 0: none).
-cudaError_t masked_gemm_launch(int dtype, const CUtensorMap& tmap_w, const TileDesc* tiles,
-                               const WorkUnit* sched, int rounds, int grid, const void* At,
+// Tensor-core masked GEMM (masked_gemm_sm100.cu).  `sched` holds rounds*grid work items; entry
+// r*grid + b is the r-th unit of CTA b (tile < 0: none, and none after it).  unit_rows is the
+// number of batch rows per work unit the schedule was built for: 128 or 256.  `blocks` is the same
+// schedule at K-block granularity: CTA b's 64-row blocks in processing order at
+// blocks[b*blk_stride ...], terminated (and padded to blk_stride) by end markers.
+cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w,
+                               const WorkItem* sched, int rounds, int grid,
+                               const BlockDesc* blocks, int blk_stride, const void* At,
                                long long lda, void* Ct, long long ldc, int M, float alpha,
                                float beta, int* status, cudaStream_t stream);
+
+#ifdef TS_KERNEL_TRACE
+cudaError_t masked_gemm_read_trace(long long* out64, bool clear);
+#endif
 
 // CUDA-core twin of the masked GEMM with the same operands (masked_gemm_simt.cu).
 cudaError_t masked_gemm_simt_launch(int dtype, const TileDesc* tiles, int n_tiles, const void* Wp,
