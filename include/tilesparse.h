@@ -142,6 +142,70 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
                       int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Mask construction
+ * ------------------------------------------------------------------------------------------- */
+
+/* Algorithms.  The first four are the reference's pruning_fun names (Pruning/VGG/prune_algo.py:
+ * 267-278); the BERT ones are the pruning types of SparseColumnPruningRank.pruning
+ * (Pruning/BERT/utils/MyHook.py:216-313). */
+#define TS_MASK_TW1 0           /* "tw1"  tiled_wise_1d      prune_algo.py:113-148              */
+#define TS_MASK_TW2 1           /* "tw2"  tiled_wise_2d      prune_algo.py:55-111               */
+#define TS_MASK_TW1M 2          /* "tw1m" tiled_wise_1d_mix  prune_algo.py:180-184 (TEW)        */
+#define TS_MASK_TW2M 3          /* "tw2m" tiled_wise_2d_mix  prune_algo.py:187-191 (TEW)        */
+#define TS_MASK_BERT_PER_TILE 4 /* type 2 granularity_pruning, per-tile percentile, MyHook.py:202-214 */
+#define TS_MASK_BERT_TW_K 5     /* type 7, tw1 with N divisible by G,          MyHook.py:226-258 */
+#define TS_MASK_BERT_TW_KN 6    /* type 8, tw2 without the sparsity remap,     MyHook.py:260-313 */
+#define TS_MASK_TOPK_L1 7       /* per-tile top-k by L1 row magnitude, ties to the lower row index;
+                                   k = round(K*(1-sparsity/100)); no reference counterpart      */
+
+typedef struct ts_mask_result ts_mask_result_t;
+
+/* Builds tile-wise masks for a group of layers that share one threshold, on the GPU, bit-identical
+ * to pruning_fun(name)(scores, sparsity, G[, g1percent]) of the reference with NumPy 2.3.
+ *   scores_dev[l]  float32 [Ks[l]][lds[l]] (lds NULL: dense rows), the scores as the reference's hooks
+ *                  hand them over (2-D, absolute values; img2col_forward, prune_algo.py:16-24)
+ *   sparsity       percent in [0, 100]; sparsity_is_f64 != 0 selects the double-precision percentile
+ *                  arithmetic NumPy uses when the caller passes a numpy.float64 instead of a Python
+ *                  number (the tw2 variants always switch to it after their remap, prune_algo.py:61)
+ *   g1percent      element-wise residual percentage of the TEW variants, ignored otherwise
+ *   masks_dev[l]   optional uint8 [Ks[l]][ld_masks[l]] outputs receiving the 0/1 mask (TW part plus,
+ *                  for TEW, the residual elements); the array or any entry may be NULL
+ *   residual_dev[l] optional uint8 [Ks[l]][Ns[l]] outputs receiving the residual elements only
+ *   *out           tile structure of every layer (the TW part): read it with ts_mask_result_*
+ * Allocates device scratch (norms, keys, histograms), synchronises `stream` several times and
+ * returns when the masks are complete. */
+int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                     const int64_t* lds, int G, double sparsity, int sparsity_is_f64, double g1percent,
+                     uint8_t* const* masks_dev, const int64_t* ld_masks, uint8_t* const* residual_dev,
+                     ts_mask_result_t** out, void* stream);
+
+/* Sizes of one layer's tile structure. */
+int ts_mask_result_layer(const ts_mask_result_t* r, int layer, int* n_tiles, int* total_kept_k,
+                         int* total_kept_n);
+
+/* Copies one layer's tile structure to host arrays (any may be NULL): tile_bounds[n_tiles+1] column
+ * split points, CSR of kept rows (ascending absolute indices) and of kept columns per tile: the
+ * format ts_layer_set_tiles takes with TS_INDEX_ABSOLUTE.  Replaces convert_mask_to_offset
+ * (MyHook.py:66-74) up to the offset encoding. */
+int ts_mask_result_copy(const ts_mask_result_t* r, int layer, int32_t* tile_bounds, int32_t* tile_k_ptr,
+                        int32_t* kept_k, int32_t* tile_n_ptr, int32_t* kept_n);
+
+/* Thresholds used: out3[0] column stage, out3[1] row stage (NaN for per-tile modes), out3[2] TEW
+ * residual; NaN where a stage did not run. */
+int ts_mask_result_thresholds(const ts_mask_result_t* r, double* out3);
+
+int ts_mask_result_destroy(ts_mask_result_t* r);
+
+/* The rank_lo-th and rank_hi-th smallest (0-based, rank_hi in {rank_lo, rank_lo+1}) of n float32
+ * values on the device, by radix select.  Allocates a small scratch, synchronises `stream`.
+ * The order-statistic core of np.percentile (prune_algo.py:66,95,134,166). */
+int ts_order_statistics(const float* vals_dev, int64_t n, int64_t rank_lo, int64_t rank_hi, float* out2,
+                        void* stream);
+
+/* np.percentile(vals, q) (method "linear") of n float32 values on the device; q_is_f64 as above. */
+int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, double* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Helpers
  * ------------------------------------------------------------------------------------------- */
 

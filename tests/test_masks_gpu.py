@@ -1,0 +1,92 @@
+"""GPU mask builder vs the reference's masks (golden fixtures) and the CPU oracle: bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from make_golden import CASES, case_inputs, load_golden
+from oracle import tw_masks as om
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu_masks(algo, scores, sparsity, gran, g1):
+    from tilesparsity_b200 import masks as tm
+    return tm.build_mask(algo, scores, sparsity, gran, g1, want_residual=algo.endswith("m"))
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_matches_reference_golden(name):
+    algo, shapes, sparsity, gran, g1, seed, dist = CASES[name]
+    scores = case_inputs(name)
+    res = _gpu_masks(algo, scores, sparsity, gran, g1)
+    gold = load_golden(name)
+    assert len(res.masks) == len(gold)
+    for m, g in zip(res.masks, gold):
+        got = m.cpu().numpy()
+        assert got.shape == g.shape
+        assert np.array_equal(got, g), f"{name}: {int((got != g).sum())} mask bits differ from the reference"
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_tile_lists_describe_the_mask(name):
+    algo, shapes, sparsity, gran, g1, seed, dist = CASES[name]
+    scores = case_inputs(name)
+    res = _gpu_masks(algo, scores, sparsity, gran, g1)
+    for i, (m, ts) in enumerate(zip(res.masks, res.tiles)):
+        tw = ts.dense_mask()
+        full = m.cpu().numpy()
+        if res.residuals is not None:
+            r = res.residuals[i].cpu().numpy()
+            assert not (r & tw).any()
+            assert np.array_equal(tw | r, full)
+        else:
+            assert np.array_equal(tw, full)
+        for t in range(ts.n_tiles):
+            rows = ts.tile_rows(t)
+            assert np.all(np.diff(rows) > 0)
+
+
+@pytest.mark.parametrize("algo,sparsity,gran,g1,shapes,seed", [
+    ("tw1", 75.0, 128, None, [(256, 1024)], 1),
+    ("tw1", np.float64(62.5), 128, None, [(128, 384), (96, 640)], 2),
+    ("tw1", 33.3, 64, None, [(200, 333)], 3),
+    ("tw2", 75.0, 128, None, [(256, 1024)], 4),
+    ("tw2", 90, 128, None, [(192, 2048)], 5),
+    ("tw2", 40.0, 32, None, [(100, 257), (64, 96)], 6),
+    ("tw1m", 75.0, 128, 1.5, [(256, 1024)], 7),
+    ("tw2m", 60.0, 64, 2.0, [(160, 512)], 8),
+])
+def test_matches_oracle(algo, sparsity, gran, g1, shapes, seed):
+    g = np.random.Generator(np.random.PCG64(seed))
+    scores = [np.abs(g.standard_normal(s, dtype=np.float32) * np.float32(0.05)) for s in shapes]
+    fn = om.pruning_fun(algo)
+    ref = fn(scores, sparsity, gran) if g1 is None else fn(scores, sparsity, gran, g1)
+    res = _gpu_masks(algo, scores, sparsity, gran, g1)
+    for m, r in zip(res.masks, ref):
+        assert np.array_equal(m.cpu().numpy(), np.asarray(r, dtype=bool))
+
+
+def test_bert_variants_and_topk():
+    g = np.random.Generator(np.random.PCG64(77))
+    s = np.abs(g.standard_normal((192, 512), dtype=np.float32))
+    for name, ref in [("bert_type7", om.bert_type7([s], 70.0, 128)[0]), ("bert_type8", om.bert_type8([s], 50.0, 128)[0]),
+                      ("bert_type2", om.bert_type2(s, 75.0, 128)), ("topk_l1", om.topk_l1(s, 75.0, 128))]:
+        sp = {"bert_type7": 70.0, "bert_type8": 50.0}.get(name, 75.0)
+        res = _gpu_masks(name, [s], sp, 128, None)
+        assert np.array_equal(res.masks[0].cpu().numpy(), np.asarray(ref, dtype=bool)), name
+    # ties: equal rows must be resolved towards the lower index
+    t = np.ones((64, 128), dtype=np.float32)
+    res = _gpu_masks("topk_l1", [t], 75.0, 128, None)
+    assert np.array_equal(res.tiles[0].tile_rows(0), np.arange(16))
+
+
+@pytest.mark.parametrize("n,q", [(1, 50.0), (2, 75.0), (1000, 75.0), (4097, 33.3), (100003, np.float64(12.5)),
+                                 (65536, 100.0), (65536, 0.0), (3000000, 98.5)])
+def test_percentile_matches_numpy(n, q):
+    from tilesparsity_b200 import masks as tm
+    g = np.random.Generator(np.random.PCG64(n))
+    v = (g.standard_normal(n, dtype=np.float32) * np.float32(3.0)).astype(np.float32)
+    v[: n // 7] = v[0]                    # duplicates around the ranks
+    ref = np.percentile([np.float32(x) for x in v] if n <= 5000 else v, q)
+    got = tm.percentile(torch.from_numpy(v).cuda(), q)
+    assert float(ref) == got

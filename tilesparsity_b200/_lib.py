@@ -17,6 +17,8 @@ TS_OK = 0
 TS_ERR_INVALID, TS_ERR_CUDA, TS_ERR_TIMEOUT, TS_ERR_UNSUPPORTED, TS_ERR_NOMEM = 1, 2, 3, 4, 5
 TS_DTYPE_F16, TS_DTYPE_BF16, TS_DTYPE_F32 = 0, 1, 2
 TS_INDEX_ABSOLUTE, TS_INDEX_RELATIVE = 0, 1
+MASK_MODES = {"tw1": 0, "tw2": 1, "tw1m": 2, "tw2m": 3, "bert_type2": 4, "bert_type7": 5, "bert_type8": 6,
+              "topk_l1": 7}
 
 
 class TileSparseError(RuntimeError):
@@ -28,7 +30,7 @@ class TileSparseError(RuntimeError):
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m tilesparsity_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python tilesparsity_b200/build.py` "
             "(there is no fallback implementation)")
     return C.CDLL(LIB_PATH)
 
@@ -57,6 +59,15 @@ SIGNATURES = {
     "ts_stream_gemm_nn": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_float, _vp, _vp, C.c_float, _vp, C.c_int,
                                     C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(_vp), C.POINTER(_vp),
                                     C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, _vp]),
+    "ts_build_tw_mask": (C.c_int, [C.c_int, C.c_int, C.POINTER(_vp), C.POINTER(C.c_int), C.POINTER(C.c_int), _i64p,
+                                   C.c_int, C.c_double, C.c_int, C.c_double, C.POINTER(_vp), _i64p, C.POINTER(_vp),
+                                   C.POINTER(_vp), _vp]),
+    "ts_mask_result_layer": (C.c_int, [_vp, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "ts_mask_result_copy": (C.c_int, [_vp, C.c_int, _i32p, _i32p, _i32p, _i32p, _i32p]),
+    "ts_mask_result_thresholds": (C.c_int, [_vp, C.POINTER(C.c_double)]),
+    "ts_mask_result_destroy": (C.c_int, [_vp]),
+    "ts_order_statistics": (C.c_int, [_vp, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_float), _vp]),
+    "ts_percentile_f32": (C.c_int, [_vp, C.c_int64, C.c_double, C.c_int, C.POINTER(C.c_double), _vp]),
     "ts_transpose16": (C.c_int, [_vp, C.c_int64, _vp, C.c_int64, C.c_int, C.c_int, _vp]),
     "ts_shard_plan": (C.c_int, [C.c_int, _i64p, C.c_int, _i32p]),
 }

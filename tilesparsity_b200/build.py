@@ -1,6 +1,6 @@
 """In-tree build of libtilesparse.so for sm_100a.
 
-`python -m tilesparsity_b200.build` compiles every file under csrc/ with nvcc (cross-compiles
+`python tilesparsity_b200/build.py` compiles every file under csrc/ with nvcc (cross-compiles
 without a GPU) and writes the shared library next to this file, where the loader looks for it.
 """
 from __future__ import annotations

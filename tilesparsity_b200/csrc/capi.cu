@@ -16,10 +16,11 @@
 #include "ts_kernels.h"
 
 namespace {
-
 thread_local std::string g_last_error;
+}  // namespace
 
-int fail(int code, const char* fmt, ...) {
+// Records the calling thread's error text and returns `code`; shared by every C-ABI source file.
+int ts_internal_fail(int code, const char* fmt, ...) {
   char buf[512];
   va_list ap;
   va_start(ap, fmt);
@@ -28,6 +29,9 @@ int fail(int code, const char* fmt, ...) {
   g_last_error = buf;
   return code;
 }
+#define fail ts_internal_fail
+
+namespace {
 
 #define TS_CUDA(expr)                                                                    \
   do {                                                                                   \

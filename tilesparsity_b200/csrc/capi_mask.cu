@@ -1,0 +1,581 @@
+// C ABI of the mask builder: host orchestration of the kernels in mask_build.cu.
+//
+// The host side owns the parts of the reference algorithm that are scalar: the percentile's index
+// arithmetic and interpolation (np.percentile, method "linear"), the sparsity remap of the 2-D
+// variant (Pruning/VGG/prune_algo.py:61) and the regrouping of surviving columns into tiles
+// (prune_algo.py:72-89).  They are written as single IEEE-754 operations in the arithmetic type
+// NumPy would use, so that thresholds, and with them the masks, come out bit-identical.
+#include "../../include/tilesparse.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+#include <string>
+#include <vector>
+
+#include "ts_mask_kernels.h"
+
+// error reporting shared with capi.cu
+int ts_internal_fail(int code, const char* fmt, ...);
+
+namespace {
+
+#define TSM_CUDA(expr)                                                                         \
+  do {                                                                                         \
+    cudaError_t e_ = (expr);                                                                   \
+    if (e_ != cudaSuccess) {                                                                   \
+      return ts_internal_fail(e_ == cudaErrorMemoryAllocation ? TS_ERR_NOMEM : TS_ERR_CUDA,    \
+                              "%s failed: %s", #expr, cudaGetErrorString(e_));                 \
+    }                                                                                          \
+  } while (0)
+
+#define TSM_OK(expr)          \
+  do {                        \
+    int rc_ = (expr);         \
+    if (rc_ != TS_OK) return rc_; \
+  } while (0)
+
+// Device allocations of one call, released together.
+struct Arena {
+  std::vector<void*> ptrs;
+  ~Arena() {
+    for (void* p : ptrs) cudaFree(p);
+  }
+  template <typename T>
+  int alloc(T** out, size_t count) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, std::max<size_t>(count, 1) * sizeof(T));
+    if (e != cudaSuccess) {
+      return ts_internal_fail(TS_ERR_NOMEM, "device allocation of %zu bytes failed: %s",
+                              count * sizeof(T), cudaGetErrorString(e));
+    }
+    ptrs.push_back(p);
+    *out = static_cast<T*>(p);
+    return TS_OK;
+  }
+};
+
+uint32_t float_key(float f) {
+  uint32_t b;
+  memcpy(&b, &f, 4);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+float key_float(uint32_t k) {
+  const uint32_t b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  float f;
+  memcpy(&f, &b, 4);
+  return f;
+}
+
+// The pi-th and ni-th smallest of vals[0..n) (0-based, pi <= ni <= pi+1), by an 8-bit radix select
+// driven from the host (four histogram passes, then one pass for the upper neighbour).
+// scratch: 256 uint32 + one uint64 + one uint32, all on the device.
+int order_statistics(const float* vals, long long n, long long pi, long long ni, float* a, float* b,
+                     unsigned int* d_hist, unsigned long long* d_count, unsigned int* d_min,
+                     cudaStream_t s) {
+  if (n <= 0 || pi < 0 || ni >= n || ni < pi || ni > pi + 1) {
+    return ts_internal_fail(TS_ERR_INVALID, "order_statistics: bad ranks %lld/%lld of %lld", pi, ni, n);
+  }
+  uint32_t prefix = 0;
+  long long rank = pi;
+  unsigned int hist[256];
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    TSM_CUDA(cudaMemsetAsync(d_hist, 0, 256 * sizeof(unsigned int), s));
+    TSM_CUDA(ts::select_hist_launch(vals, n, prefix, shift, d_hist, s));
+    TSM_CUDA(cudaMemcpyAsync(hist, d_hist, sizeof(hist), cudaMemcpyDeviceToHost, s));
+    TSM_CUDA(cudaStreamSynchronize(s));
+    long long cum = 0;
+    int d = 0;
+    for (; d < 256; ++d) {
+      if (cum + hist[d] > rank) break;
+      cum += hist[d];
+    }
+    if (d == 256) return ts_internal_fail(TS_ERR_CUDA, "radix select lost its rank (non-finite input?)");
+    rank -= cum;
+    prefix |= static_cast<uint32_t>(d) << shift;
+  }
+  *a = key_float(prefix);
+  *b = *a;
+  if (ni != pi) {
+    const unsigned int init_min = 0xffffffffu;
+    TSM_CUDA(cudaMemsetAsync(d_count, 0, sizeof(unsigned long long), s));
+    TSM_CUDA(cudaMemcpyAsync(d_min, &init_min, sizeof(init_min), cudaMemcpyHostToDevice, s));
+    TSM_CUDA(ts::select_neighbor_launch(vals, n, prefix, d_count, d_min, s));
+    unsigned long long count_le = 0;
+    unsigned int min_gt = 0;
+    TSM_CUDA(cudaMemcpyAsync(&count_le, d_count, sizeof(count_le), cudaMemcpyDeviceToHost, s));
+    TSM_CUDA(cudaMemcpyAsync(&min_gt, d_min, sizeof(min_gt), cudaMemcpyDeviceToHost, s));
+    TSM_CUDA(cudaStreamSynchronize(s));
+    if (static_cast<long long>(count_le) < ni + 1) *b = key_float(min_gt);  // next rank is a larger value
+  }
+  return TS_OK;
+}
+
+// np.percentile's rank arithmetic ("linear": virtual index (n-1)*q, neighbours floor and floor+1).
+// With a weak (Python) q everything is float32; with a float64 q it is double.
+struct Ranks {
+  long long pi, ni;
+  float gamma_f;
+  double gamma_d;
+};
+
+Ranks percentile_ranks(long long n, double q, bool wide) {
+  Ranks r;
+  if (wide) {
+    volatile double qd = q / 100.0;
+    volatile double virt = static_cast<double>(n - 1) * qd;
+    const double prev = std::floor(virt);
+    r.pi = static_cast<long long>(prev);
+    r.ni = r.pi + 1;
+    if (virt >= static_cast<double>(n - 1)) r.pi = r.ni = n - 1;
+    r.gamma_d = virt - prev;
+    r.gamma_f = 0.0f;
+  } else {
+    volatile float qf = static_cast<float>(q) / 100.0f;
+    volatile float virt = static_cast<float>(n - 1) * qf;
+    const float prev = std::floor(virt);
+    r.pi = static_cast<long long>(prev);
+    r.ni = r.pi + 1;
+    if (virt >= static_cast<float>(n - 1)) r.pi = r.ni = n - 1;
+    r.gamma_f = virt - prev;
+    r.gamma_d = 0.0;
+  }
+  if (r.pi < 0) r.pi = r.ni = 0;
+  if (r.ni > n - 1) r.ni = n - 1;
+  return r;
+}
+
+// NumPy's _lerp: a + (b-a)*t, replaced by b - (b-a)*(1-t) when t >= 0.5.  The difference b-a is a
+// float32 operation in both paths (a and b are float32 array elements); the rest follows t's type.
+double percentile_lerp(float a, float b, const Ranks& r, bool wide) {
+  volatile float diff = b - a;
+  if (wide) {
+    const double t = r.gamma_d;
+    volatile double prod = static_cast<double>(diff) * t;
+    volatile double res = static_cast<double>(a) + prod;
+    if (t >= 0.5) {
+      volatile double omt = 1.0 - t;
+      volatile double prod2 = static_cast<double>(diff) * omt;
+      res = static_cast<double>(b) - prod2;
+    }
+    return res;
+  }
+  const float t = r.gamma_f;
+  volatile float prod = diff * t;
+  volatile float res = a + prod;
+  if (t >= 0.5f) {
+    volatile float omt = 1.0f - t;
+    volatile float prod2 = diff * omt;
+    res = b - prod2;
+  }
+  return static_cast<double>(res);
+}
+
+// A tile ends right after its G-th kept column; no cut at the matrix edge (prune_algo.py:72-89).
+std::vector<int> regroup_bounds(const uint8_t* colkeep, int N, int G) {
+  std::vector<int> b{0};
+  int count = 0;
+  for (int c = 0; c < N; ++c) {
+    if (colkeep[c]) ++count;
+    if (count == G) {
+      if (c + 1 < N) {
+        b.push_back(c + 1);
+        count = 0;
+      }
+    }
+  }
+  b.push_back(N);
+  return b;
+}
+
+std::vector<int> fixed_bounds(int N, int G) {
+  std::vector<int> b;
+  for (int c = 0; c < N; c += G) b.push_back(c);
+  b.push_back(N);
+  return b;
+}
+
+struct LayerIn {
+  const float* score;
+  int K, N;
+  long long ld;
+  uint8_t* mask;
+  long long ld_mask;
+  uint8_t* residual;
+};
+
+}  // namespace
+
+struct ts_mask_result {
+  struct Layer {
+    int K = 0, N = 0;
+    std::vector<int> bounds, tile_k_ptr, kept_k, tile_n_ptr, kept_n;
+  };
+  std::vector<Layer> layers;
+  double thr[3] = {std::numeric_limits<double>::quiet_NaN(), std::numeric_limits<double>::quiet_NaN(),
+                   std::numeric_limits<double>::quiet_NaN()};
+};
+
+namespace {
+
+struct Scratch {
+  unsigned int* hist = nullptr;
+  unsigned long long* count = nullptr;
+  unsigned int* min_gt = nullptr;
+};
+
+// Row stage shared by every mode: norms of all tile-rows of all layers, a keep flag for each, the
+// per-tile kept-row lists, and (optionally) the dense masks.
+//   sel: 0 = one global percentile over all layers (tw1 / tw2 stage 2), 1 = per-tile percentile
+//        (BERT type 2), 2 = per-tile top-k by L1 (k = round(K * (1 - q/100))).
+int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>& bounds,
+              const std::vector<uint8_t*>& colkeep_dev, const std::vector<std::vector<uint8_t>>& colkeep_host,
+              int sel, double q, bool wide, ts_mask_result* res, double* thr_out, Arena& arena,
+              const Scratch& sc, cudaStream_t s) {
+  const int nl = static_cast<int>(L.size());
+  std::vector<long long> off(nl + 1, 0);
+  std::vector<int> tile_off(nl + 1, 0);
+  for (int l = 0; l < nl; ++l) {
+    const int nt = static_cast<int>(bounds[l].size()) - 1;
+    off[l + 1] = off[l] + static_cast<long long>(nt) * L[l].K;
+    tile_off[l + 1] = tile_off[l] + nt;
+  }
+  const long long total = off[nl];
+  const int total_tiles = tile_off[nl];
+  float* norms = nullptr;
+  uint8_t* keep = nullptr;
+  TSM_OK(arena.alloc(&norms, total));
+  TSM_OK(arena.alloc(&keep, total));
+  std::vector<int*> bounds_dev(nl, nullptr);
+  for (int l = 0; l < nl; ++l) {
+    TSM_OK(arena.alloc(&bounds_dev[l], bounds[l].size()));
+    TSM_CUDA(cudaMemcpyAsync(bounds_dev[l], bounds[l].data(), bounds[l].size() * sizeof(int),
+                             cudaMemcpyHostToDevice, s));
+    const int nt = static_cast<int>(bounds[l].size()) - 1;
+    if (sel == 2) {
+      TSM_CUDA(ts::tile_row_l1_launch(L[l].score, L[l].ld, L[l].K, bounds_dev[l], nt, norms + off[l], s));
+    } else {
+      TSM_CUDA(ts::tile_row_norms_launch(L[l].score, L[l].ld, L[l].K, bounds_dev[l], nt,
+                                         colkeep_dev.empty() ? nullptr : colkeep_dev[l], norms + off[l],
+                                         sel == 0 ? 1 : 0, s));
+    }
+  }
+  if (sel == 0) {
+    const Ranks r = percentile_ranks(total, q, wide);
+    float a = 0, b = 0;
+    TSM_OK(order_statistics(norms, total, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s));
+    const double thr = percentile_lerp(a, b, r, wide);
+    if (thr_out) *thr_out = thr;
+    TSM_CUDA(ts::threshold_launch(norms, total, thr, keep, s));
+  } else {
+    for (int l = 0; l < nl; ++l) {
+      const int nt = static_cast<int>(bounds[l].size()) - 1;
+      const int K = L[l].K;
+      if (sel == 2) {
+        const int k_keep = static_cast<int>(std::nearbyint(K * (1.0 - q / 100.0)));
+        TSM_CUDA(ts::tile_rank_launch(norms + off[l], K, nt, 0, k_keep, 0, 0, keep + off[l], nullptr, s));
+      } else {
+        const Ranks r = percentile_ranks(K, q, wide);
+        float* stats = nullptr;
+        double* thr_dev = nullptr;
+        TSM_OK(arena.alloc(&stats, 2 * static_cast<size_t>(nt)));
+        TSM_OK(arena.alloc(&thr_dev, nt));
+        TSM_CUDA(ts::tile_rank_launch(norms + off[l], K, nt, 1, 0, static_cast<int>(r.pi),
+                                      static_cast<int>(r.ni), nullptr, stats, s));
+        std::vector<float> st(2 * static_cast<size_t>(nt));
+        TSM_CUDA(cudaMemcpyAsync(st.data(), stats, st.size() * sizeof(float), cudaMemcpyDeviceToHost, s));
+        TSM_CUDA(cudaStreamSynchronize(s));
+        std::vector<double> thr(nt);
+        for (int t = 0; t < nt; ++t) thr[t] = percentile_lerp(st[2 * t], st[2 * t + 1], r, wide);
+        TSM_CUDA(cudaMemcpyAsync(thr_dev, thr.data(), nt * sizeof(double), cudaMemcpyHostToDevice, s));
+        TSM_CUDA(ts::threshold_per_tile_launch(norms + off[l], K, nt, thr_dev, keep + off[l], s));
+        TSM_CUDA(cudaStreamSynchronize(s));  // thr (host) must outlive the copy
+      }
+    }
+  }
+
+  // kept-row lists: one segment per (layer, tile)
+  std::vector<long long> seg(total_tiles + 1, 0);
+  for (int l = 0; l < nl; ++l) {
+    const int nt = tile_off[l + 1] - tile_off[l];
+    for (int t = 0; t <= nt; ++t) seg[tile_off[l] + t] = off[l] + static_cast<long long>(t) * L[l].K;
+  }
+  long long* seg_dev = nullptr;
+  int* counts_dev = nullptr;
+  int* optr_dev = nullptr;
+  TSM_OK(arena.alloc(&seg_dev, seg.size()));
+  TSM_OK(arena.alloc(&counts_dev, total_tiles));
+  TSM_OK(arena.alloc(&optr_dev, total_tiles + 1));
+  TSM_CUDA(cudaMemcpyAsync(seg_dev, seg.data(), seg.size() * sizeof(long long), cudaMemcpyHostToDevice, s));
+  TSM_CUDA(ts::segment_count_launch(keep, seg_dev, total_tiles, counts_dev, s));
+  std::vector<int> counts(total_tiles);
+  TSM_CUDA(cudaMemcpyAsync(counts.data(), counts_dev, total_tiles * sizeof(int), cudaMemcpyDeviceToHost, s));
+  TSM_CUDA(cudaStreamSynchronize(s));
+  std::vector<int> optr(total_tiles + 1, 0);
+  for (int t = 0; t < total_tiles; ++t) optr[t + 1] = optr[t] + counts[t];
+  int* list_dev = nullptr;
+  TSM_OK(arena.alloc(&list_dev, optr[total_tiles]));
+  TSM_CUDA(cudaMemcpyAsync(optr_dev, optr.data(), optr.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+  TSM_CUDA(ts::segment_compact_launch(keep, seg_dev, total_tiles, optr_dev, list_dev, s));
+  std::vector<int> list(optr[total_tiles]);
+  if (!list.empty()) {
+    TSM_CUDA(cudaMemcpyAsync(list.data(), list_dev, list.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
+  }
+  TSM_CUDA(cudaStreamSynchronize(s));
+
+  res->layers.resize(nl);
+  for (int l = 0; l < nl; ++l) {
+    ts_mask_result::Layer& R = res->layers[l];
+    const int nt = tile_off[l + 1] - tile_off[l];
+    R.K = L[l].K;
+    R.N = L[l].N;
+    R.bounds = bounds[l];
+    R.tile_k_ptr.assign(nt + 1, 0);
+    R.tile_n_ptr.assign(nt + 1, 0);
+    R.kept_k.clear();
+    R.kept_n.clear();
+    for (int t = 0; t < nt; ++t) {
+      const int gt = tile_off[l] + t;
+      R.kept_k.insert(R.kept_k.end(), list.begin() + optr[gt], list.begin() + optr[gt + 1]);
+      R.tile_k_ptr[t + 1] = static_cast<int>(R.kept_k.size());
+      for (int c = bounds[l][t]; c < bounds[l][t + 1]; ++c) {
+        if (colkeep_host.empty() || colkeep_host[l][c]) R.kept_n.push_back(c);
+      }
+      R.tile_n_ptr[t + 1] = static_cast<int>(R.kept_n.size());
+    }
+    if (L[l].mask) {
+      std::vector<int> tile_of_col(L[l].N);
+      for (int t = 0; t < nt; ++t) {
+        for (int c = bounds[l][t]; c < bounds[l][t + 1]; ++c) tile_of_col[c] = t;
+      }
+      int* toc_dev = nullptr;
+      TSM_OK(arena.alloc(&toc_dev, tile_of_col.size()));
+      TSM_CUDA(cudaMemcpyAsync(toc_dev, tile_of_col.data(), tile_of_col.size() * sizeof(int),
+                               cudaMemcpyHostToDevice, s));
+      TSM_CUDA(ts::dense_mask_launch(keep + off[l], colkeep_dev.empty() ? nullptr : colkeep_dev[l], toc_dev,
+                                     L[l].K, L[l].N, L[l].mask, L[l].ld_mask, s));
+      TSM_CUDA(cudaStreamSynchronize(s));  // tile_of_col (host) must outlive the copy
+    }
+  }
+  return TS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                     const int64_t* lds, int G, double sparsity, int sparsity_is_f64, double g1percent,
+                     uint8_t* const* masks_dev, const int64_t* ld_masks, uint8_t* const* residual_dev,
+                     ts_mask_result_t** out, void* stream) {
+  if (!out) return ts_internal_fail(TS_ERR_INVALID, "out is NULL");
+  *out = nullptr;
+  if (mode < TS_MASK_TW1 || mode > TS_MASK_TOPK_L1) return ts_internal_fail(TS_ERR_INVALID, "unknown mode %d", mode);
+  if (n_layers <= 0 || !scores_dev || !Ks || !Ns) return ts_internal_fail(TS_ERR_INVALID, "no layers");
+  if (G <= 0) return ts_internal_fail(TS_ERR_INVALID, "G=%d must be positive", G);
+  if (!(sparsity >= 0.0 && sparsity <= 100.0)) {
+    return ts_internal_fail(TS_ERR_INVALID, "sparsity=%g must be in [0, 100]", sparsity);
+  }
+  const bool tew = mode == TS_MASK_TW1M || mode == TS_MASK_TW2M;
+  if (tew && !(g1percent >= 0.0 && sparsity + g1percent <= 100.0)) {
+    return ts_internal_fail(TS_ERR_INVALID, "g1percent=%g out of range", g1percent);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Arena arena;
+  std::vector<LayerIn> L(n_layers);
+  for (int l = 0; l < n_layers; ++l) {
+    if (!scores_dev[l] || Ks[l] <= 0 || Ns[l] <= 0) return ts_internal_fail(TS_ERR_INVALID, "layer %d is empty", l);
+    L[l].score = static_cast<const float*>(scores_dev[l]);
+    L[l].K = Ks[l];
+    L[l].N = Ns[l];
+    L[l].ld = lds ? lds[l] : Ns[l];
+    if (L[l].ld < L[l].N) return ts_internal_fail(TS_ERR_INVALID, "layer %d: ld smaller than N", l);
+    L[l].mask = masks_dev ? masks_dev[l] : nullptr;
+    L[l].ld_mask = (ld_masks && L[l].mask) ? ld_masks[l] : Ns[l];
+    L[l].residual = residual_dev ? residual_dev[l] : nullptr;
+    if (tew && !L[l].mask) {  // the residual ranking needs the dense TW mask
+      TSM_OK(arena.alloc(&L[l].mask, static_cast<size_t>(L[l].K) * L[l].N));
+      L[l].ld_mask = L[l].N;
+    }
+    const bool divisible = mode == TS_MASK_BERT_PER_TILE || mode == TS_MASK_BERT_TW_K;
+    if (divisible && (L[l].N % G) != 0) {
+      return ts_internal_fail(TS_ERR_INVALID, "layer %d: N=%d is not divisible by the granularity %d", l, L[l].N, G);
+    }
+  }
+  Scratch sc;
+  TSM_OK(arena.alloc(&sc.hist, 256));
+  TSM_OK(arena.alloc(&sc.count, 1));
+  TSM_OK(arena.alloc(&sc.min_gt, 1));
+  ts_mask_result* res = new ts_mask_result();
+
+  const bool two_d = mode == TS_MASK_TW2 || mode == TS_MASK_TW2M || mode == TS_MASK_BERT_TW_KN;
+  double q = tew ? sparsity + g1percent : sparsity;
+  bool wide = sparsity_is_f64 != 0;
+  if (mode == TS_MASK_TW2 || mode == TS_MASK_TW2M) {
+    volatile double x = q * 100.0;
+    volatile double y = 10000.0 - x;
+    volatile double z = std::sqrt(y);
+    q = 100.0 - z;                       // prune_algo.py:61, a NumPy float64 from here on
+    wide = true;
+  }
+  std::vector<std::vector<int>> bounds(n_layers);
+  std::vector<uint8_t*> colkeep_dev;
+  std::vector<std::vector<uint8_t>> colkeep_host;
+  int rc = TS_OK;
+  do {
+    if (two_d) {
+      // stage 1: global percentile over the column norms of all layers (prune_algo.py:64-67)
+      long long totalN = 0;
+      for (int l = 0; l < n_layers; ++l) totalN += L[l].N;
+      float* cn = nullptr;
+      uint8_t* ck = nullptr;
+      if ((rc = arena.alloc(&cn, totalN)) != TS_OK) break;
+      if ((rc = arena.alloc(&ck, totalN)) != TS_OK) break;
+      long long o = 0;
+      cudaError_t e = cudaSuccess;
+      for (int l = 0; l < n_layers && e == cudaSuccess; ++l) {
+        e = ts::col_norms_launch(L[l].score, L[l].ld, L[l].K, L[l].N, cn + o, s);
+        o += L[l].N;
+      }
+      if (e != cudaSuccess) {
+        rc = ts_internal_fail(TS_ERR_CUDA, "column norm kernel failed: %s", cudaGetErrorString(e));
+        break;
+      }
+      const Ranks r = percentile_ranks(totalN, q, wide);
+      float a = 0, b = 0;
+      if ((rc = order_statistics(cn, totalN, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s)) != TS_OK) break;
+      res->thr[0] = percentile_lerp(a, b, r, wide);
+      e = ts::threshold_launch(cn, totalN, res->thr[0], ck, s);
+      std::vector<uint8_t> all(totalN);
+      if (e == cudaSuccess) e = cudaMemcpyAsync(all.data(), ck, totalN, cudaMemcpyDeviceToHost, s);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+      if (e != cudaSuccess) {
+        rc = ts_internal_fail(TS_ERR_CUDA, "column threshold failed: %s", cudaGetErrorString(e));
+        break;
+      }
+      o = 0;
+      colkeep_dev.resize(n_layers);
+      colkeep_host.resize(n_layers);
+      for (int l = 0; l < n_layers; ++l) {
+        colkeep_dev[l] = ck + o;
+        colkeep_host[l].assign(all.begin() + o, all.begin() + o + L[l].N);
+        bounds[l] = regroup_bounds(colkeep_host[l].data(), L[l].N, G);
+        o += L[l].N;
+      }
+    } else {
+      for (int l = 0; l < n_layers; ++l) bounds[l] = fixed_bounds(L[l].N, G);
+    }
+    const int sel = mode == TS_MASK_BERT_PER_TILE ? 1 : (mode == TS_MASK_TOPK_L1 ? 2 : 0);
+    if ((rc = row_stage(L, bounds, colkeep_dev, colkeep_host, sel, q, wide, res, &res->thr[1], arena, sc, s)) != TS_OK) break;
+
+    if (tew) {
+      // element-wise residual (tw_mix_fn, prune_algo.py:151-177): rank |w| - mask over every
+      // element of every layer, keep the top g1percent percent on top of the TW mask
+      long long total = 0;
+      for (int l = 0; l < n_layers; ++l) total += static_cast<long long>(L[l].K) * L[l].N;
+      float* vals = nullptr;
+      if ((rc = arena.alloc(&vals, total)) != TS_OK) break;
+      long long o = 0;
+      cudaError_t e = cudaSuccess;
+      for (int l = 0; l < n_layers && e == cudaSuccess; ++l) {
+        e = ts::tew_values_launch(L[l].score, L[l].ld, L[l].mask, L[l].ld_mask, L[l].K, L[l].N, vals + o, s);
+        o += static_cast<long long>(L[l].K) * L[l].N;
+      }
+      if (e != cudaSuccess) {
+        rc = ts_internal_fail(TS_ERR_CUDA, "residual value kernel failed: %s", cudaGetErrorString(e));
+        break;
+      }
+      const double q2 = 100.0 - g1percent;
+      const bool wide2 = sparsity_is_f64 != 0;
+      const Ranks r = percentile_ranks(total, q2, wide2);
+      float a = 0, b = 0;
+      if ((rc = order_statistics(vals, total, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s)) != TS_OK) break;
+      res->thr[2] = percentile_lerp(a, b, r, wide2);
+      o = 0;
+      for (int l = 0; l < n_layers && e == cudaSuccess; ++l) {
+        e = ts::tew_apply_launch(vals + o, res->thr[2], L[l].K, L[l].N, L[l].mask, L[l].ld_mask, L[l].residual, s);
+        o += static_cast<long long>(L[l].K) * L[l].N;
+      }
+      if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+      if (e != cudaSuccess) {
+        rc = ts_internal_fail(TS_ERR_CUDA, "residual apply kernel failed: %s", cudaGetErrorString(e));
+        break;
+      }
+    }
+  } while (false);
+  cudaStreamSynchronize(s);  // the arena is freed on return
+  if (rc != TS_OK) {
+    delete res;
+    return rc;
+  }
+  *out = res;
+  return TS_OK;
+}
+
+int ts_mask_result_layer(const ts_mask_result_t* r, int layer, int* n_tiles, int* total_kept_k,
+                         int* total_kept_n) {
+  if (!r || layer < 0 || layer >= static_cast<int>(r->layers.size())) {
+    return ts_internal_fail(TS_ERR_INVALID, "bad mask result / layer index");
+  }
+  const ts_mask_result::Layer& R = r->layers[layer];
+  if (n_tiles) *n_tiles = static_cast<int>(R.bounds.size()) - 1;
+  if (total_kept_k) *total_kept_k = static_cast<int>(R.kept_k.size());
+  if (total_kept_n) *total_kept_n = static_cast<int>(R.kept_n.size());
+  return TS_OK;
+}
+
+int ts_mask_result_copy(const ts_mask_result_t* r, int layer, int32_t* tile_bounds, int32_t* tile_k_ptr,
+                        int32_t* kept_k, int32_t* tile_n_ptr, int32_t* kept_n) {
+  if (!r || layer < 0 || layer >= static_cast<int>(r->layers.size())) {
+    return ts_internal_fail(TS_ERR_INVALID, "bad mask result / layer index");
+  }
+  const ts_mask_result::Layer& R = r->layers[layer];
+  auto cp = [](int32_t* dst, const std::vector<int>& v) {
+    if (dst && !v.empty()) memcpy(dst, v.data(), v.size() * sizeof(int));
+  };
+  cp(tile_bounds, R.bounds);
+  cp(tile_k_ptr, R.tile_k_ptr);
+  cp(kept_k, R.kept_k);
+  cp(tile_n_ptr, R.tile_n_ptr);
+  cp(kept_n, R.kept_n);
+  return TS_OK;
+}
+
+int ts_mask_result_thresholds(const ts_mask_result_t* r, double* out3) {
+  if (!r || !out3) return ts_internal_fail(TS_ERR_INVALID, "NULL argument");
+  for (int i = 0; i < 3; ++i) out3[i] = r->thr[i];
+  return TS_OK;
+}
+
+int ts_mask_result_destroy(ts_mask_result_t* r) {
+  delete r;
+  return TS_OK;
+}
+
+int ts_order_statistics(const float* vals_dev, int64_t n, int64_t rank_lo, int64_t rank_hi, float* out2,
+                        void* stream) {
+  if (!vals_dev || !out2) return ts_internal_fail(TS_ERR_INVALID, "NULL argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Arena arena;
+  Scratch sc;
+  TSM_OK(arena.alloc(&sc.hist, 256));
+  TSM_OK(arena.alloc(&sc.count, 1));
+  TSM_OK(arena.alloc(&sc.min_gt, 1));
+  return order_statistics(vals_dev, n, rank_lo, rank_hi, &out2[0], &out2[1], sc.hist, sc.count, sc.min_gt, s);
+}
+
+int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, double* out, void* stream) {
+  if (!vals_dev || !out || n <= 0) return ts_internal_fail(TS_ERR_INVALID, "bad argument");
+  if (!(q >= 0.0 && q <= 100.0)) return ts_internal_fail(TS_ERR_INVALID, "q=%g must be in [0, 100]", q);
+  const Ranks r = percentile_ranks(n, q, q_is_f64 != 0);
+  float ab[2];
+  TSM_OK(ts_order_statistics(vals_dev, n, r.pi, r.ni, ab, stream));
+  *out = percentile_lerp(ab[0], ab[1], r, q_is_f64 != 0);
+  return TS_OK;
+}
+
+}  // extern "C"

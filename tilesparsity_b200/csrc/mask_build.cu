@@ -1,0 +1,416 @@
+// Tile-wise (TW / TEW) mask construction kernels.
+//
+// Device-side counterpart of the reference's NumPy mask builder (Pruning/VGG/prune_algo.py:55-193;
+// BERT variants Pruning/BERT/utils/MyHook.py:202-313).  The masks must equal the reference's bit
+// for bit, so every float32 step reproduces what NumPy computes there, in the same order and with
+// the same roundings (no fused multiply-add anywhere):
+//
+//   row norms   np.linalg.norm(tile, axis=1) / width   (prune_algo.py:90,128): squares rounded to
+//               float32, NumPy's pairwise add.reduce (eight running sums over elements j, j+8, ...
+//               combined as ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7)), leftovers in order; runs longer than
+//               128 split at n/2 rounded down to a multiple of 8), sqrt, division by the width;
+//   col norms   np.linalg.norm(score, axis=0) / K      (prune_algo.py:64): squares summed down the
+//               rows in order;
+//   percentile  np.percentile(all norms, q)            (prune_algo.py:66,95,134,166): two exact
+//               order statistics by radix select; the interpolation between them runs on the host
+//               (capi.cu) in the arithmetic type NumPy would use;
+//   keep        norm > threshold, strict               (prune_algo.py:67,99,140,171).
+//
+// All kernels are HBM-bound streaming passes: the score matrix is read once per norm pass (4 bytes
+// per element), the radix select reads its 4-byte keys once per 8-bit digit.
+#include "ts_common.cuh"
+#include "ts_mask_kernels.h"
+
+namespace ts {
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// NumPy's pairwise float32 sum of the squares of a strided run, computed by 8 cooperating lanes.
+// ---------------------------------------------------------------------------------------------
+struct RowSrc {
+  const float* row;        // first element of the run
+  const uint8_t* colmask;  // nullptr, or one byte per element of the run (0: element counts as +0)
+};
+
+__device__ __forceinline__ float sq_at(const RowSrc& s, int i) {
+  if (s.colmask && !s.colmask[i]) return 0.0f;
+  const float x = __ldg(s.row + i);
+  return __fmul_rn(x, x);
+}
+
+// Sum of run [o, o+n), 8 <= n <= 128, by the 8 lanes of a group; every lane returns the sum.
+__device__ __forceinline__ float leaf_sum8(const RowSrc& s, int o, int n, int j) {
+  float r = sq_at(s, o + j);
+  const int body = n - (n % 8);
+  for (int i = 8; i < body; i += 8) r = __fadd_rn(r, sq_at(s, o + i + j));
+  r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 1));   // r0+r1, r2+r3, r4+r5, r6+r7
+  r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 2));   // (r0+r1)+(r2+r3), (r4+r5)+(r6+r7)
+  r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 4));
+  for (int i = body; i < n; ++i) r = __fadd_rn(r, sq_at(s, o + i));
+  return r;
+}
+
+// Whole run of any length.  The control flow depends only on n, which is uniform across a warp.
+__device__ float pairwise_sq_sum(const RowSrc& s, int o, int n, int j) {
+  if (n < 8) {
+    float r = 0.0f;
+    for (int i = 0; i < n; ++i) r = __fadd_rn(r, sq_at(s, o + i));
+    return r;
+  }
+  if (n <= 128) return leaf_sum8(s, o, n, j);
+  int n2 = n / 2;
+  n2 -= n2 % 8;
+  const float a = pairwise_sq_sum(s, o, n2, j);
+  const float b = pairwise_sq_sum(s, o + n2, n - n2, j);
+  return __fadd_rn(a, b);
+}
+
+// norms[t*K + k] = ||score[k, bounds[t]:bounds[t+1]] (.* colmask)||_2 (/ width)
+// grid: (ceil(K / 32), n_tiles), block 256 = 32 groups of 8 lanes, one (row, tile) per group.
+__global__ void __launch_bounds__(256)
+tile_row_norms_kernel(const float* __restrict__ score, long long ld, int K,
+                      const int* __restrict__ bounds, const uint8_t* __restrict__ colmask,
+                      float* __restrict__ norms, int divide) {
+  const int t = blockIdx.y;
+  const int c0 = bounds[t], width = bounds[t + 1] - c0;
+  const int group = threadIdx.x >> 3, j = threadIdx.x & 7;
+  const int k = blockIdx.x * 32 + group;
+  const int kk = k < K ? k : K - 1;   // clamped rows keep the warp converged; their result is dropped
+  RowSrc s;
+  s.row = score + static_cast<long long>(kk) * ld + c0;
+  s.colmask = colmask ? colmask + c0 : nullptr;
+  const float sum = pairwise_sq_sum(s, 0, width, j);
+  float v = __fsqrt_rn(sum);
+  if (divide) v = __fdiv_rn(v, static_cast<float>(width));
+  if (k < K && j == 0) norms[static_cast<long long>(t) * K + k] = v;
+}
+
+// l1[t*K + k] = sum_c |score[k, c]| over the tile's columns, left to right.
+__global__ void __launch_bounds__(256)
+tile_row_l1_kernel(const float* __restrict__ score, long long ld, int K,
+                   const int* __restrict__ bounds, float* __restrict__ out) {
+  const int t = blockIdx.y;
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  const int c0 = bounds[t], c1 = bounds[t + 1];
+  const float* row = score + static_cast<long long>(k) * ld;
+  float r = 0.0f;
+  for (int c = c0; c < c1; ++c) r = __fadd_rn(r, fabsf(__ldg(row + c)));
+  out[static_cast<long long>(t) * K + k] = r;
+}
+
+// out[n] = sqrt(sum_k score[k][n]^2 in row order) / K
+__global__ void __launch_bounds__(128)
+col_norms_kernel(const float* __restrict__ score, long long ld, int K, int N,
+                 float* __restrict__ out) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  float x = __ldg(score + n);
+  float acc = __fmul_rn(x, x);
+  for (int k = 1; k < K; ++k) {
+    x = __ldg(score + static_cast<long long>(k) * ld + n);
+    acc = __fadd_rn(acc, __fmul_rn(x, x));
+  }
+  out[n] = __fdiv_rn(__fsqrt_rn(acc), static_cast<float>(K));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Radix select over float32 values (order-preserving 32-bit keys)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t float_key(float f) {
+  const uint32_t b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// hist[d] += #{i : key_i agrees with `prefix` on the bits above shift+8 and has digit d at shift}
+__global__ void __launch_bounds__(256)
+select_hist_kernel(const float* __restrict__ vals, long long n, uint32_t prefix, int shift,
+                   unsigned int* __restrict__ hist) {
+  __shared__ unsigned int h[256];
+  h[threadIdx.x] = 0;
+  __syncthreads();
+  const uint32_t hi_mask = shift >= 24 ? 0u : (0xffffffffu << (shift + 8));
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t key = float_key(__ldg(vals + i));
+    if ((key & hi_mask) == (prefix & hi_mask)) atomicAdd(&h[(key >> shift) & 0xffu], 1u);
+  }
+  __syncthreads();
+  if (h[threadIdx.x]) atomicAdd(&hist[threadIdx.x], h[threadIdx.x]);
+}
+
+// res[0..1] (64-bit) += #{key_i <= key};  res[2] = min(res[2], min{key_i : key_i > key})
+__global__ void __launch_bounds__(256)
+select_neighbor_kernel(const float* __restrict__ vals, long long n, uint32_t key,
+                       unsigned long long* __restrict__ count_le, unsigned int* __restrict__ min_gt) {
+  unsigned long long c = 0;
+  unsigned int m = 0xffffffffu;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t k = float_key(__ldg(vals + i));
+    if (k <= key) ++c;
+    else m = min(m, k);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+    m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (c) atomicAdd(count_le, c);
+    if (m != 0xffffffffu) atomicMin(min_gt, m);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Thresholding and list building
+// ---------------------------------------------------------------------------------------------
+// keep[i] = vals[i] > thr  (compared in double: exact for both float32 and float64 thresholds)
+__global__ void __launch_bounds__(256)
+threshold_kernel(const float* __restrict__ vals, long long n, double thr, uint8_t* __restrict__ keep) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i < n) keep[i] = static_cast<double>(vals[i]) > thr ? 1 : 0;
+}
+
+// One block per segment: counts[s] = number of set flags in keep[seg_ptr[s] .. seg_ptr[s+1]).
+__global__ void __launch_bounds__(256)
+segment_count_kernel(const uint8_t* __restrict__ keep, const long long* __restrict__ seg_ptr,
+                     int* __restrict__ counts) {
+  const long long a = seg_ptr[blockIdx.x], b = seg_ptr[blockIdx.x + 1];
+  int c = 0;
+  for (long long i = a + threadIdx.x; i < b; i += blockDim.x) c += keep[i];
+  __shared__ int red[256];
+  red[threadIdx.x] = c;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[blockIdx.x] = red[0];
+}
+
+// One block per segment: list[out_ptr[s] + r] = position (inside the segment) of its r-th set flag.
+__global__ void __launch_bounds__(256)
+segment_compact_kernel(const uint8_t* __restrict__ keep, const long long* __restrict__ seg_ptr,
+                       const int* __restrict__ out_ptr, int* __restrict__ list) {
+  const long long a = seg_ptr[blockIdx.x], b = seg_ptr[blockIdx.x + 1];
+  int* out = list + out_ptr[blockIdx.x];
+  __shared__ int scan[256];
+  __shared__ int base;
+  if (threadIdx.x == 0) base = 0;
+  __syncthreads();
+  for (long long i0 = a; i0 < b; i0 += blockDim.x) {
+    const long long i = i0 + threadIdx.x;
+    const int f = (i < b) ? keep[i] : 0;
+    scan[threadIdx.x] = f;
+    __syncthreads();
+    for (int o = 1; o < 256; o <<= 1) {
+      const int v = threadIdx.x >= o ? scan[threadIdx.x - o] : 0;
+      __syncthreads();
+      scan[threadIdx.x] += v;
+      __syncthreads();
+    }
+    if (f) out[base + scan[threadIdx.x] - 1] = static_cast<int>(i - a);
+    __syncthreads();
+    if (threadIdx.x == 255) base += scan[255];
+    __syncthreads();
+  }
+}
+
+// mask[k][n] = rowkeep[tile(n)*K + k] & colkeep[n] (| residual[k][n])
+__global__ void __launch_bounds__(256)
+dense_mask_kernel(const uint8_t* __restrict__ rowkeep, const uint8_t* __restrict__ colkeep,
+                  const int* __restrict__ tile_of_col, int K, int N, uint8_t* __restrict__ mask,
+                  long long ld_mask) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y;
+  if (n >= N) return;
+  const int t = tile_of_col[n];
+  uint8_t m = rowkeep[static_cast<long long>(t) * K + k];
+  if (colkeep) m &= colkeep[n];
+  mask[static_cast<long long>(k) * ld_mask + n] = m;
+}
+
+// TEW ranking values: v[k*N + n] = sqrt(w*w) - mask[k][n]   (prune_algo.py:156-159)
+__global__ void __launch_bounds__(256)
+tew_values_kernel(const float* __restrict__ score, long long ld, const uint8_t* __restrict__ mask,
+                  long long ld_mask, int K, int N, float* __restrict__ vals) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y;
+  if (n >= N) return;
+  const float x = __ldg(score + static_cast<long long>(k) * ld + n);
+  const float a = __fsqrt_rn(__fmul_rn(x, x));
+  const float m = mask[static_cast<long long>(k) * ld_mask + n] ? 1.0f : 0.0f;
+  vals[static_cast<long long>(k) * N + n] = __fsub_rn(a, m);
+}
+
+// mask[k][n] |= v > thr; residual[k][n] = (v > thr) & !mask_before   (prune_algo.py:171-175)
+__global__ void __launch_bounds__(256)
+tew_apply_kernel(const float* __restrict__ vals, double thr, int K, int N, uint8_t* __restrict__ mask,
+                 long long ld_mask, uint8_t* __restrict__ residual) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y;
+  if (n >= N) return;
+  const long long mi = static_cast<long long>(k) * ld_mask + n;
+  const bool extra = static_cast<double>(vals[static_cast<long long>(k) * N + n]) > thr;
+  const uint8_t before = mask[mi];
+  if (residual) residual[static_cast<long long>(k) * N + n] = (extra && !before) ? 1 : 0;
+  if (extra) mask[mi] = 1;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-tile selection by rank counting (one block per tile, the tile's K values in shared memory)
+// ---------------------------------------------------------------------------------------------
+// mode 0: keep the k_keep largest values, ties to the lower row index.
+// mode 1: per-tile percentile (MyHook.py:202-214): the two order statistics at ranks pi / ni are
+//         written to stats[2t], stats[2t+1]; the host interpolates and thresholds afterwards.
+__global__ void __launch_bounds__(256)
+tile_rank_kernel(const float* __restrict__ vals, int K, int mode, int k_keep, int pi, int ni,
+                 uint8_t* __restrict__ keep, float* __restrict__ stats) {
+  extern __shared__ float sv[];
+  const float* v = vals + static_cast<long long>(blockIdx.x) * K;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) sv[i] = v[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < K; i += blockDim.x) {
+    const float x = sv[i];
+    int rank = 0;
+    if (mode == 0) {
+      for (int jj = 0; jj < K; ++jj) {
+        const float y = sv[jj];
+        rank += (y > x) || (y == x && jj < i);
+      }
+      keep[static_cast<long long>(blockIdx.x) * K + i] = rank < k_keep ? 1 : 0;
+    } else {
+      for (int jj = 0; jj < K; ++jj) {
+        const float y = sv[jj];
+        rank += (y < x) || (y == x && jj < i);
+      }
+      if (rank == pi) stats[2 * blockIdx.x] = x;
+      if (rank == ni) stats[2 * blockIdx.x + 1] = x;
+    }
+  }
+}
+
+// keep[t*K + k] = vals[t*K + k] > thr[t]
+__global__ void __launch_bounds__(256)
+threshold_per_tile_kernel(const float* __restrict__ vals, int K, const double* __restrict__ thr,
+                          uint8_t* __restrict__ keep) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t = blockIdx.y;
+  if (k >= K) return;
+  const long long i = static_cast<long long>(t) * K + k;
+  keep[i] = static_cast<double>(vals[i]) > thr[t] ? 1 : 0;
+}
+
+int stream_grid(long long n) {
+  long long b = (n + 255) / 256;
+  return static_cast<int>(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
+}
+
+}  // namespace
+
+cudaError_t tile_row_norms_launch(const float* score, long long ld, int K, const int* bounds_dev,
+                                  int n_tiles, const uint8_t* colmask, float* norms, int divide,
+                                  cudaStream_t s) {
+  if (K <= 0 || n_tiles <= 0) return cudaSuccess;
+  dim3 grid((K + 31) / 32, n_tiles);
+  tile_row_norms_kernel<<<grid, 256, 0, s>>>(score, ld, K, bounds_dev, colmask, norms, divide);
+  return cudaGetLastError();
+}
+
+cudaError_t tile_row_l1_launch(const float* score, long long ld, int K, const int* bounds_dev,
+                               int n_tiles, float* out, cudaStream_t s) {
+  if (K <= 0 || n_tiles <= 0) return cudaSuccess;
+  dim3 grid((K + 255) / 256, n_tiles);
+  tile_row_l1_kernel<<<grid, 256, 0, s>>>(score, ld, K, bounds_dev, out);
+  return cudaGetLastError();
+}
+
+cudaError_t col_norms_launch(const float* score, long long ld, int K, int N, float* out,
+                             cudaStream_t s) {
+  if (K <= 0 || N <= 0) return cudaSuccess;
+  col_norms_kernel<<<(N + 127) / 128, 128, 0, s>>>(score, ld, K, N, out);
+  return cudaGetLastError();
+}
+
+cudaError_t select_hist_launch(const float* vals, long long n, uint32_t prefix, int shift,
+                               unsigned int* hist, cudaStream_t s) {
+  select_hist_kernel<<<stream_grid(n), 256, 0, s>>>(vals, n, prefix, shift, hist);
+  return cudaGetLastError();
+}
+
+cudaError_t select_neighbor_launch(const float* vals, long long n, uint32_t key,
+                                   unsigned long long* count_le, unsigned int* min_gt,
+                                   cudaStream_t s) {
+  select_neighbor_kernel<<<stream_grid(n), 256, 0, s>>>(vals, n, key, count_le, min_gt);
+  return cudaGetLastError();
+}
+
+cudaError_t threshold_launch(const float* vals, long long n, double thr, uint8_t* keep,
+                             cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  threshold_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(vals, n, thr, keep);
+  return cudaGetLastError();
+}
+
+cudaError_t segment_count_launch(const uint8_t* keep, const long long* seg_ptr, int n_seg, int* counts,
+                                 cudaStream_t s) {
+  if (n_seg <= 0) return cudaSuccess;
+  segment_count_kernel<<<n_seg, 256, 0, s>>>(keep, seg_ptr, counts);
+  return cudaGetLastError();
+}
+
+cudaError_t segment_compact_launch(const uint8_t* keep, const long long* seg_ptr, int n_seg,
+                                   const int* out_ptr, int* list, cudaStream_t s) {
+  if (n_seg <= 0) return cudaSuccess;
+  segment_compact_kernel<<<n_seg, 256, 0, s>>>(keep, seg_ptr, out_ptr, list);
+  return cudaGetLastError();
+}
+
+cudaError_t dense_mask_launch(const uint8_t* rowkeep, const uint8_t* colkeep, const int* tile_of_col,
+                              int K, int N, uint8_t* mask, long long ld_mask, cudaStream_t s) {
+  if (K <= 0 || N <= 0) return cudaSuccess;
+  dim3 grid((N + 255) / 256, K);
+  dense_mask_kernel<<<grid, 256, 0, s>>>(rowkeep, colkeep, tile_of_col, K, N, mask, ld_mask);
+  return cudaGetLastError();
+}
+
+cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* mask, long long ld_mask,
+                              int K, int N, float* vals, cudaStream_t s) {
+  if (K <= 0 || N <= 0) return cudaSuccess;
+  dim3 grid((N + 255) / 256, K);
+  tew_values_kernel<<<grid, 256, 0, s>>>(score, ld, mask, ld_mask, K, N, vals);
+  return cudaGetLastError();
+}
+
+cudaError_t tew_apply_launch(const float* vals, double thr, int K, int N, uint8_t* mask,
+                             long long ld_mask, uint8_t* residual, cudaStream_t s) {
+  if (K <= 0 || N <= 0) return cudaSuccess;
+  dim3 grid((N + 255) / 256, K);
+  tew_apply_kernel<<<grid, 256, 0, s>>>(vals, thr, K, N, mask, ld_mask, residual);
+  return cudaGetLastError();
+}
+
+cudaError_t tile_rank_launch(const float* vals, int K, int n_tiles, int mode, int k_keep, int pi,
+                             int ni, uint8_t* keep, float* stats, cudaStream_t s) {
+  if (K <= 0 || n_tiles <= 0) return cudaSuccess;
+  const size_t smem = static_cast<size_t>(K) * sizeof(float);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(tile_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
+  tile_rank_kernel<<<n_tiles, 256, smem, s>>>(vals, K, mode, k_keep, pi, ni, keep, stats);
+  return cudaGetLastError();
+}
+
+cudaError_t threshold_per_tile_launch(const float* vals, int K, int n_tiles, const double* thr,
+                                      uint8_t* keep, cudaStream_t s) {
+  if (K <= 0 || n_tiles <= 0) return cudaSuccess;
+  dim3 grid((K + 255) / 256, n_tiles);
+  threshold_per_tile_kernel<<<grid, 256, 0, s>>>(vals, K, thr, keep);
+  return cudaGetLastError();
+}
+
+}  // namespace ts

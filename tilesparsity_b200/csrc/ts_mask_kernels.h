@@ -1,0 +1,44 @@
+// Host-callable launchers of the mask-construction kernels (mask_build.cu).  Internal.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ts {
+
+// norms[t*K + k] = ||score[k, bounds[t]:bounds[t+1]] (.* colmask)||_2, divided by the tile width
+// when `divide` is set.  bounds_dev holds n_tiles+1 column indices on the device.
+cudaError_t tile_row_norms_launch(const float* score, long long ld, int K, const int* bounds_dev,
+                                  int n_tiles, const uint8_t* colmask, float* norms, int divide,
+                                  cudaStream_t s);
+// out[t*K + k] = sum of |score[k, c]| over the tile's columns, left to right.
+cudaError_t tile_row_l1_launch(const float* score, long long ld, int K, const int* bounds_dev,
+                               int n_tiles, float* out, cudaStream_t s);
+// out[n] = ||score[:, n]||_2 / K, rows accumulated in order.
+cudaError_t col_norms_launch(const float* score, long long ld, int K, int N, float* out,
+                             cudaStream_t s);
+// One digit pass of the radix select: hist[256] must be zero on entry.
+cudaError_t select_hist_launch(const float* vals, long long n, uint32_t prefix, int shift,
+                               unsigned int* hist, cudaStream_t s);
+// *count_le += #{key <= key}; *min_gt = min(*min_gt, smallest key above `key`).
+cudaError_t select_neighbor_launch(const float* vals, long long n, uint32_t key,
+                                   unsigned long long* count_le, unsigned int* min_gt,
+                                   cudaStream_t s);
+cudaError_t threshold_launch(const float* vals, long long n, double thr, uint8_t* keep,
+                             cudaStream_t s);
+cudaError_t segment_count_launch(const uint8_t* keep, const long long* seg_ptr, int n_seg, int* counts,
+                                 cudaStream_t s);
+cudaError_t segment_compact_launch(const uint8_t* keep, const long long* seg_ptr, int n_seg,
+                                   const int* out_ptr, int* list, cudaStream_t s);
+cudaError_t dense_mask_launch(const uint8_t* rowkeep, const uint8_t* colkeep, const int* tile_of_col,
+                              int K, int N, uint8_t* mask, long long ld_mask, cudaStream_t s);
+cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* mask, long long ld_mask,
+                              int K, int N, float* vals, cudaStream_t s);
+cudaError_t tew_apply_launch(const float* vals, double thr, int K, int N, uint8_t* mask,
+                             long long ld_mask, uint8_t* residual, cudaStream_t s);
+cudaError_t tile_rank_launch(const float* vals, int K, int n_tiles, int mode, int k_keep, int pi,
+                             int ni, uint8_t* keep, float* stats, cudaStream_t s);
+cudaError_t threshold_per_tile_launch(const float* vals, int K, int n_tiles, const double* thr,
+                                      uint8_t* keep, cudaStream_t s);
+
+}  // namespace ts

@@ -1,0 +1,131 @@
+"""GPU mask construction with the reference's call shape.
+
+`pruning_fun(name)(scores, sparsity, granularity=128[, g1percent])` mirrors
+Pruning/VGG/prune_algo.py:267-278 for the tile-wise algorithms (`tw1`, `tw2`, `tw1m`, `tw2m`): a
+list of 2-D score arrays in, a list of 0/1 masks of the same shapes out, one threshold shared by
+the whole list.  Scores may be NumPy arrays or CUDA tensors; masks come back in kind.  All scoring,
+selection and thresholding runs in libtilesparse's CUDA kernels (ts_build_tw_mask); there is no CPU
+path.  `build_mask` additionally returns the tile structure (per-tile kept-row lists, kept columns)
+that `TWLayer` consumes, which closes the gap the reference leaves between its mask builder and its
+GEMM driver.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import check, lib
+from .tiles import TileSet
+
+
+@dataclass
+class MaskResult:
+    masks: list            # uint8/bool CUDA tensors [K, N], one per layer (TW part | TEW residual)
+    tiles: list            # TileSet per layer: the tile-wise part
+    residuals: list        # bool CUDA tensors [K, N] with the TEW residual elements, or None
+    thresholds: tuple      # (column stage, row stage, residual stage); NaN where a stage did not run
+
+
+def img2col_forward(weights):
+    """HWIO conv kernels -> 2-D [(kh*kw*cin), cout]; absolute values (prune_algo.py:16-24)."""
+    out = []
+    for w in weights:
+        t = w if isinstance(w, torch.Tensor) else torch.from_numpy(np.asarray(w))
+        if t.dim() == 4:
+            t = t.reshape(t.shape[0] * t.shape[1] * t.shape[2], t.shape[3])
+        out.append(t.abs())
+    return out
+
+
+def _is_f64(x) -> bool:
+    return isinstance(x, np.floating) and not isinstance(x, np.float32)
+
+
+def build_mask(name: str, scores, sparsity, granularity: int = 128, g1percent=None, want_residual: bool = False,
+               device=None) -> MaskResult:
+    """Runs one of the mask algorithms on the GPU.  `name` is a reference name (tw1, tw2, tw1m, tw2m),
+    a BERT pruning type (bert_type2 / bert_type7 / bert_type8) or topk_l1."""
+    if name not in _lib.MASK_MODES:
+        raise KeyError(f"unknown mask algorithm {name!r}")
+    if not torch.cuda.is_available():
+        raise RuntimeError("build_mask needs a CUDA device (there is no CPU fallback)")
+    mode = _lib.MASK_MODES[name]
+    tew = name in ("tw1m", "tw2m")
+    if g1percent is None:
+        g1percent = {"tw1m": 5, "tw2m": 1}.get(name, 0)     # the reference's defaults (prune_algo.py:180,187)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    sc = []
+    for s in scores:
+        t = s if isinstance(s, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(s))
+        if t.dim() != 2:
+            raise ValueError("scores must be 2-D (use img2col_forward for conv kernels)")
+        t = t.to(device=dev, dtype=torch.float32)
+        if t.stride(1) != 1:
+            t = t.contiguous()
+        sc.append(t)
+    n = len(sc)
+    masks = [torch.empty((t.shape[0], t.shape[1]), dtype=torch.uint8, device=dev) for t in sc]
+    resid = [torch.zeros((t.shape[0], t.shape[1]), dtype=torch.uint8, device=dev) for t in sc] \
+        if (tew and want_residual) else None
+    VP = C.c_void_p * n
+    IA = C.c_int * n
+    LA = C.c_int64 * n
+    handle = C.c_void_p()
+    with torch.cuda.device(dev):
+        check(lib.ts_build_tw_mask(
+            mode, n, VP(*[t.data_ptr() for t in sc]), IA(*[t.shape[0] for t in sc]), IA(*[t.shape[1] for t in sc]),
+            LA(*[t.stride(0) for t in sc]), int(granularity), float(sparsity), int(_is_f64(sparsity) or _is_f64(g1percent)),
+            float(g1percent), VP(*[m.data_ptr() for m in masks]), LA(*[m.stride(0) for m in masks]),
+            VP(*[r.data_ptr() for r in resid]) if resid else None, C.byref(handle),
+            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    try:
+        tiles = []
+        for l, t in enumerate(sc):
+            nt, nk, nn = C.c_int(), C.c_int(), C.c_int()
+            check(lib.ts_mask_result_layer(handle, l, C.byref(nt), C.byref(nk), C.byref(nn)))
+            b = np.zeros(nt.value + 1, np.int32)
+            kp = np.zeros(nt.value + 1, np.int32)
+            npz = np.zeros(nt.value + 1, np.int32)
+            kk = np.zeros(max(nk.value, 1), np.int32)
+            nn_a = np.zeros(max(nn.value, 1), np.int32)
+            p = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+            check(lib.ts_mask_result_copy(handle, l, p(b), p(kp), p(kk), p(npz), p(nn_a)))
+            tiles.append(TileSet(int(t.shape[0]), int(t.shape[1]), int(granularity), b, kp, kk[:nk.value], npz,
+                                 nn_a[:nn.value]))
+        thr = (C.c_double * 3)()
+        check(lib.ts_mask_result_thresholds(handle, thr))
+    finally:
+        lib.ts_mask_result_destroy(handle)
+    return MaskResult([m.bool() for m in masks], tiles, [r.bool() for r in resid] if resid else None, tuple(thr))
+
+
+def pruning_fun(pruning_type: str):
+    """Same dispatch as the reference (prune_algo.py:267-278) for the tile-wise algorithms.  The
+    returned function takes (scores, sparsity[, granularity][, g1percent]) and returns the masks as
+    NumPy bool arrays when given NumPy scores, as CUDA bool tensors otherwise."""
+    if pruning_type not in ("tw1", "tw2", "tw1m", "tw2m"):
+        raise KeyError(f"{pruning_type!r} is not a tile-wise algorithm (tw1, tw2, tw1m, tw2m)")
+
+    def fn(accumulated_scores, sparsity, granularity=128, g1percent=None):
+        res = build_mask(pruning_type, accumulated_scores, sparsity, granularity, g1percent)
+        if all(isinstance(s, np.ndarray) for s in accumulated_scores):
+            return [m.cpu().numpy() for m in res.masks]
+        return res.masks
+
+    return fn
+
+
+def percentile(values: torch.Tensor, q) -> float:
+    """np.percentile(values, q) of a float32 CUDA tensor, computed by the library's radix select."""
+    v = values.reshape(-1).contiguous()
+    if v.dtype != torch.float32 or not v.is_cuda:
+        raise ValueError("percentile takes a float32 CUDA tensor")
+    out = C.c_double()
+    with torch.cuda.device(v.device):
+        check(lib.ts_percentile_f32(C.c_void_p(v.data_ptr()), v.numel(), float(q), int(_is_f64(q)), C.byref(out),
+                                    C.c_void_p(torch.cuda.current_stream(v.device).cuda_stream)))
+    return out.value

@@ -47,6 +47,15 @@ class TileSet:
     def tile_cols(self, t: int) -> np.ndarray:
         return self.kept_n[self.tile_n_ptr[t]:self.tile_n_ptr[t + 1]]
 
+    def lists(self) -> list:
+        """Per-tile kept-row lists."""
+        return [self.tile_rows(t) for t in range(self.n_tiles)]
+
+    def col_mask(self) -> np.ndarray:
+        m = np.zeros(self.N, dtype=bool)
+        m[self.kept_n] = True
+        return m
+
     def kept_flops_per_row(self) -> int:
         return int(2 * np.sum(self.k_counts().astype(np.int64) * self.n_counts().astype(np.int64)))
 
