@@ -116,7 +116,7 @@ def make_kept_lists(name: str, K: int, N: int, W, masks: str):
         keep = int(round(K * (1 - SPARSITY / 100.0) / 8)) * 8
         return synth.random_kept_lists(K, n_tiles, keep, synth.BERT_SEEDS[name] + 100)
     from tilesparsity_b200 import masks as tsm
-    res = tsm.build_mask("tw1", [W], SPARSITY, G)
+    res = tsm.build_mask("tw1", [W.abs()], SPARSITY, G)
     return res.tiles[0].lists()
 
 
@@ -181,20 +181,29 @@ def time_loop(fn, steps: int, warmup: int, barrier=None, graph_span: int = 0):
     return e0.elapsed_time(e1)
 
 
-def cpu_reference_pass(sample_steps: int, budget_s: float):
+def cpu_reference_pass(sample_steps: int, budget_s: float, masks: str = "tw1"):
     """The reference's CPU path for the same step: NumPy `A @ (W * mask)` per GEMM on fp32
-    (Pruning/BERT/utils/modeling.py:992-1007), masks from the CPU oracle's tile lists."""
+    (Pruning/BERT/utils/modeling.py:992-1007) with the masks of the CPU oracle's tw1
+    (Pruning/VGG/prune_algo.py:113-148).  The mask build is timed separately."""
     from oracle import masked_gemm as og
+    from oracle import tw_masks as om
     from tilesparsity_b200 import synth
-    from tilesparsity_b200.tiles import tiles_from_lists
-    items, kept = [], 0
+    from tilesparsity_b200.tiles import tiles_from_lists, tiles_from_mask
+    items, kept, t_mask = [], 0, 0.0
     for name in GEMMS:
         A, W = synth.bert_gemm(name, M_ROWS)
         K, N = W.shape
-        keep = int(round(K * (1 - SPARSITY / 100.0) / 8)) * 8
-        lists = synth.random_kept_lists(K, (N + G - 1) // G, keep, synth.BERT_SEEDS[name] + 100)
-        ts = tiles_from_lists(K, N, G, lists)
-        items.append((A, W, ts.dense_mask()))
+        if masks == "random":
+            keep = int(round(K * (1 - SPARSITY / 100.0) / 8)) * 8
+            lists = synth.random_kept_lists(K, (N + G - 1) // G, keep, synth.BERT_SEEDS[name] + 100)
+            ts = tiles_from_lists(K, N, G, lists)
+            mask = ts.dense_mask()
+        else:
+            t0 = time.perf_counter()
+            mask = om.tw1([np.abs(W)], SPARSITY, G)[0]
+            t_mask += time.perf_counter() - t0
+            ts = tiles_from_mask(mask, G)
+        items.append((A, W, mask))
         kept += ts.kept_flops_per_row() * M_ROWS
     og.masked_matmul_dense(*items[1])  # warm the BLAS threads
     times = []
@@ -213,21 +222,21 @@ def cpu_reference_pass(sample_steps: int, budget_s: float):
         cores = os.cpu_count() or 1
     t = float(np.median(times))
     return {"value": kept / t / 1e12, "seconds_per_step": t, "steps_run": len(times), "cores": int(cores),
-            "kept_flops": kept}
+            "kept_flops": kept, "mask_build_seconds": t_mask}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    r = cpu_reference_pass(args.steps, budget_s=90.0)
+    r = cpu_reference_pass(args.steps, budget_s=90.0, masks=args.masks)
     sample = (f"{r['steps_run']} full steps (4 GEMMs, M={M_ROWS}) of numpy fp32 A@(W*mask) on the host, "
               f"median; requested steps={args.steps}")
     line = {
         "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": r["seconds_per_step"] * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
-        "config": {"workload": f"bert_base_layer_m{M_ROWS}_tw75_g{G}", "gemms": list(GEMMS), "masks": "random"},
+        "config": {"workload": f"bert_base_layer_m{M_ROWS}_tw75_g{G}", "gemms": list(GEMMS), "masks": args.masks},
         "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": sample},
         "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -305,6 +314,25 @@ def run_ours(args):
                              "ctas": sched["n_ctas"], "units": sched["n_units"], "balance": round(sched["balance"], 4)})
         ms_dense = time_loop(dense_step, sub_steps, 5, None, span) / sub_steps
 
+        # mask construction for the four weight matrices (tw1, 75 %), timed end to end on the GPU
+        mask_build = None
+        if args.masks == "tw1":
+            from tilesparsity_b200 import masks as tsm
+            scores = [g["W16"].float().abs() for g in work]
+            for sc in scores:
+                tsm.build_mask("tw1", [sc], SPARSITY, G)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            reps = 5
+            for _ in range(reps):
+                for sc in scores:
+                    tsm.build_mask("tw1", [sc], SPARSITY, G)
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) / reps
+            nbytes = sum(sc.numel() * 4 + sc.numel() for sc in scores)   # scores read once, dense masks written
+            mask_build = {"seconds": dt, "bytes": int(nbytes), "gbs": nbytes / dt / 1e9,
+                          "what": "ts_build_tw_mask(tw1) on the 4 weight matrices, host-synchronous call, wall clock"}
+
         # end to end: pinned host activations in, host outputs back, through ts_masked_gemm_host
         hA = [torch.empty((g["K"], M_ROWS), dtype=torch.float16).pin_memory() for g in work]
         hC = [torch.empty((g["N"], M_ROWS), dtype=torch.float16).pin_memory() for g in work]
@@ -322,10 +350,10 @@ def run_ours(args):
                "d2h_bytes_per_step": int(sum(h.numel() * 2 for h in hC)),
                "ms_per_step": ms_e2e, "n_gpus_timed": 1}
         if world == 1:
-            r = cpu_reference_pass(8, budget_s=25.0)
+            r = cpu_reference_pass(8, budget_s=25.0, masks=args.masks)
             cpu = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
                    "sample": f"{r['steps_run']} full steps of numpy fp32 A@(W*mask), 4 GEMMs at M={M_ROWS}, median",
-                   "seconds_per_step": r["seconds_per_step"]}
+                   "seconds_per_step": r["seconds_per_step"], "mask_build_seconds": r["mask_build_seconds"]}
 
     if rank == 0:
         t_launch = (sum(p["us"] for p in per_gemm) / len(per_gemm)) * 1e-6
@@ -354,6 +382,7 @@ def run_ours(args):
                          "kernel": "masked_gemm_kernel", "bytes_per_launch": bytes_launch,
                          "us_per_launch": t_launch * 1e6},
             "cpu_baseline": cpu,
+            "mask_build": mask_build,
             "e2e": e2e,
             "gpu_launches": len(work) * args.steps,
             "clocks": clocks,
@@ -371,7 +400,9 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--masks", choices=["tw1", "random"], default="random")
+    ap.add_argument("--masks", choices=["tw1", "random"], default="tw1",
+                    help="tw1: the reference's tile-wise masks of the synthetic weights, built on the GPU; "
+                         "random: the perf driver's random per-tile row subsets")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

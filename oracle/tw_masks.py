@@ -252,7 +252,7 @@ def percentile_exact(values, q):
     if virt >= n - 1:
         pi = ni = n - 1
     a, b = T(v[pi]), T(v[ni])
-    diff = T(b - a)
+    diff = T(_f32(v[ni] - v[pi]))        # b - a is a float32 operation in both paths (array elements)
     if gamma >= T(0.5):
         res = T(b - T(diff * T(T(1) - gamma)))
     else:
