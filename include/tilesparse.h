@@ -205,6 +205,29 @@ int ts_order_statistics(const float* vals_dev, int64_t n, int64_t rank_lo, int64
 /* np.percentile(vals, q) (method "linear") of n float32 values on the device; q_is_f64 as above. */
 int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, double* out, void* stream);
 
+/* Row stage of "tw1" for ONE weight matrix without any allocation: keep_dev[t*K + k] = 1 when row k
+ * of column tile t (tiles of G columns, narrow last tile) survives, i.e. when its L2 norm / width lies
+ * strictly above the `sparsity` percentile of all tile-row norms of the matrix -- the same flags
+ * ts_build_tw_mask(TS_MASK_TW1) derives its kept-row lists from.  This entry point has no counterpart
+ * in the reference; it exists for callers that must not allocate device memory while they run: a
+ * plugin living inside a host framework that owns the whole device heap through its own pool, or a
+ * serving process whose memory budget is fixed at start-up and where a cudaMalloc in steady state
+ * (an implicit device synchronisation, and a possible out-of-memory failure) is not acceptable.
+ *
+ * The norms, the tile boundaries and the radix-select counters live in a fixed array built into the
+ * library (about 4 MiB per GPU, held from library load until exit).  Limits: at most
+ * TS_NOALLOC_MAX_TILES column tiles and TS_NOALLOC_MAX_NORMS tile-rows (tiles x K); larger inputs are
+ * rejected with TS_ERR_UNSUPPORTED.  The function calls neither cudaMalloc nor cudaFree nor any
+ * allocating routine.  The first call on each device also looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on a device
+ * share the one array: the call clears the counters it needs and overwrites the norms, so sequential
+ * calls are independent, but two calls whose work overlaps on the GPU (different streams or host
+ * threads) race on it.  Synchronises `stream`; *threshold_out (optional) receives the threshold. */
+#define TS_NOALLOC_MAX_TILES 4096
+#define TS_NOALLOC_MAX_NORMS (1 << 20)
+int ts_tw1_row_keep_noalloc(const float* score_dev, int64_t ld, int K, int N, int G, double sparsity,
+                            int sparsity_is_f64, uint8_t* keep_dev, double* threshold_out, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Helpers
  * ------------------------------------------------------------------------------------------- */

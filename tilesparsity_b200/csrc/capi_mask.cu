@@ -568,6 +568,82 @@ int ts_order_statistics(const float* vals_dev, int64_t n, int64_t rank_lo, int64
   return order_statistics(vals_dev, n, rank_lo, rank_hi, &out2[0], &out2[1], sc.hist, sc.count, sc.min_gt, s);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the tw1 row stage
+// ---------------------------------------------------------------------------------------------
+}  // extern "C"
+
+namespace {
+
+// Everything ts_tw1_row_keep_noalloc needs beyond its inputs and outputs.  One copy per GPU that
+// loads the library, held until the process exits.
+struct NoAllocScratch {
+  unsigned int hist[256];              // radix-select digit histogram (cleared before every pass)
+  unsigned long long count_le;         // cleared before use
+  unsigned int min_gt;                 // reset before use
+  unsigned int pad_;
+  int bounds[TS_NOALLOC_MAX_TILES + 1];
+  float norms[TS_NOALLOC_MAX_NORMS];   // fully overwritten by every call before it is read
+};
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel could
+// use; the device address is looked up once per device, with that device current.
+NoAllocScratch* g_noalloc_dev_ptr[64] = {};
+
+int noalloc_scratch(NoAllocScratch** out) {
+  int dev = 0;
+  TSM_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return ts_internal_fail(TS_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  if (!g_noalloc_dev_ptr[dev]) {
+    void* p = nullptr;
+    TSM_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    g_noalloc_dev_ptr[dev] = static_cast<NoAllocScratch*>(p);
+  }
+  *out = g_noalloc_dev_ptr[dev];
+  return TS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ts_tw1_row_keep_noalloc(const float* score_dev, int64_t ld, int K, int N, int G, double sparsity,
+                            int sparsity_is_f64, uint8_t* keep_dev, double* threshold_out, void* stream) {
+  if (!score_dev || !keep_dev) return ts_internal_fail(TS_ERR_INVALID, "NULL argument");
+  if (K <= 0 || N <= 0 || G <= 0 || ld < N) return ts_internal_fail(TS_ERR_INVALID, "bad shape K=%d N=%d G=%d", K, N, G);
+  if (!(sparsity >= 0.0 && sparsity <= 100.0)) {
+    return ts_internal_fail(TS_ERR_INVALID, "sparsity=%g must be in [0, 100]", sparsity);
+  }
+  const long long n_tiles = (static_cast<long long>(N) + G - 1) / G;
+  const long long total = n_tiles * K;
+  if (n_tiles > TS_NOALLOC_MAX_TILES || total > TS_NOALLOC_MAX_NORMS) {
+    return ts_internal_fail(TS_ERR_UNSUPPORTED,
+                            "%lld tiles x %d rows = %lld tile-rows exceed the built-in scratch (%d tiles, %d "
+                            "tile-rows); use ts_build_tw_mask, which allocates what it needs",
+                            n_tiles, K, total, TS_NOALLOC_MAX_TILES, TS_NOALLOC_MAX_NORMS);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  NoAllocScratch* sc = nullptr;
+  TSM_OK(noalloc_scratch(&sc));
+  int bounds[TS_NOALLOC_MAX_TILES + 1];
+  for (long long t = 0; t < n_tiles; ++t) bounds[t] = static_cast<int>(t * G);
+  bounds[n_tiles] = N;
+  TSM_CUDA(cudaMemcpyAsync(sc->bounds, bounds, (n_tiles + 1) * sizeof(int), cudaMemcpyHostToDevice, s));
+  TSM_CUDA(cudaStreamSynchronize(s));  // `bounds` lives on this stack frame
+  TSM_CUDA(ts::tile_row_norms_launch(score_dev, ld, K, sc->bounds, static_cast<int>(n_tiles), nullptr, sc->norms, 1, s));
+  const Ranks r = percentile_ranks(total, sparsity, sparsity_is_f64 != 0);
+  float a = 0, b = 0;
+  // order_statistics clears the histogram before every digit pass and the two counters before use
+  TSM_OK(order_statistics(sc->norms, total, r.pi, r.ni, &a, &b, sc->hist, &sc->count_le, &sc->min_gt, s));
+  const double thr = percentile_lerp(a, b, r, sparsity_is_f64 != 0);
+  TSM_CUDA(ts::threshold_launch(sc->norms, total, thr, keep_dev, s));
+  TSM_CUDA(cudaStreamSynchronize(s));
+  if (threshold_out) *threshold_out = thr;
+  return TS_OK;
+}
+
 int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, double* out, void* stream) {
   if (!vals_dev || !out || n <= 0) return ts_internal_fail(TS_ERR_INVALID, "bad argument");
   if (!(q >= 0.0 && q <= 100.0)) return ts_internal_fail(TS_ERR_INVALID, "q=%g must be in [0, 100]", q);

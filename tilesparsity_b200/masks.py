@@ -129,3 +129,24 @@ def percentile(values: torch.Tensor, q) -> float:
         check(lib.ts_percentile_f32(C.c_void_p(v.data_ptr()), v.numel(), float(q), int(_is_f64(q)), C.byref(out),
                                     C.c_void_p(torch.cuda.current_stream(v.device).cuda_stream)))
     return out.value
+
+
+def tw1_row_keep_noalloc(score: torch.Tensor, sparsity, granularity: int = 128, out: torch.Tensor | None = None):
+    """tw1 keep flags of one matrix, [n_tiles, K] uint8, through the entry point that allocates no
+    device memory (its scratch is a fixed array inside the library).  Meant for callers that cannot
+    allocate while they run; `out` lets such a caller pass its own pre-allocated flags tensor.
+    Returns (flags, threshold).  Inputs beyond the built-in scratch raise TileSparseError."""
+    if score.dtype != torch.float32 or not score.is_cuda or score.dim() != 2 or score.stride(1) != 1:
+        raise ValueError("score must be a 2-D float32 CUDA tensor with contiguous rows")
+    K, N = score.shape
+    n_tiles = (N + granularity - 1) // granularity
+    if out is None:
+        out = torch.empty((n_tiles, K), dtype=torch.uint8, device=score.device)
+    if tuple(out.shape) != (n_tiles, K) or out.dtype != torch.uint8 or not out.is_contiguous() or out.device != score.device:
+        raise ValueError(f"out must be a contiguous uint8 [{n_tiles}, {K}] tensor on {score.device}")
+    thr = C.c_double()
+    with torch.cuda.device(score.device):
+        check(lib.ts_tw1_row_keep_noalloc(C.c_void_p(score.data_ptr()), score.stride(0), K, N, int(granularity),
+                                          float(sparsity), int(_is_f64(sparsity)), C.c_void_p(out.data_ptr()),
+                                          C.byref(thr), C.c_void_p(torch.cuda.current_stream(score.device).cuda_stream)))
+    return out, thr.value
