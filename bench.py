@@ -394,6 +394,73 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_square(args):
+    """Tile-sharded strong-scaling run: M = N = K = --size, bf16, tile-wise 75 % with per-tile kept-row
+    counts skewed ~Beta(2,5); the column tiles are sharded across the ranks by kept FLOPs
+    (tilesparsity_b200.sharding), every rank holds At and computes its own slab of Ct; with
+    --gather the slabs are all-gathered over NCCL inside the timed region."""
+    import torch
+    import torch.distributed as dist
+    from tilesparsity_b200 import sharding, synth
+    from tilesparsity_b200.tiles import tiles_from_lists
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    barrier = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        barrier = dist.barrier
+    n = args.size
+    nt = (n + G - 1) // G
+    counts = synth.beta_skewed_counts(n, nt, 1 - SPARSITY / 100.0, 5000 + int(np.log2(n)))
+    g = synth.rng(5000 + int(np.log2(n)))
+    lists = [np.sort(g.choice(n, size=int(c), replace=False)).astype(np.int32) for c in counts]
+    ts = tiles_from_lists(n, n, G, lists)
+    gen = torch.Generator(device=device).manual_seed(1234)
+    W = torch.randn((n, n), generator=gen, device=device, dtype=torch.float32)
+    shard = sharding.ShardedTWLayer(W, ts, rank, world, torch.bfloat16)
+    del W
+    n_sets = max(2, min(4, (3 * L2_BYTES) // (n * n * 2) + 1))
+    At = [torch.randn((n, n), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16) for _ in range(n_sets)]
+    Ct = [torch.zeros((shard.plan.n_pad, n), dtype=torch.bfloat16, device=device) for _ in range(n_sets)]
+    full = torch.empty((world * shard.plan.n_pad, n), dtype=torch.bfloat16, device=device) if args.gather else None
+
+    def step(i):
+        s = i % n_sets
+        shard.masked_gemm(At[s], out=Ct[s])
+        if args.gather and world > 1:
+            dist.all_gather_into_tensor(full, Ct[s])
+
+    sampler = ClockSampler(local_rank)
+    time_loop(step, 2, max(3, args.warmup), barrier)
+    sampler.start()
+    ms = time_loop(step, args.steps, max(3, args.warmup), barrier)
+    clocks = sampler.stop()
+    shard.layer.check()
+    ms_t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    kept = ts.kept_flops_per_row() * n
+    value = kept * args.steps / (float(ms_t.item()) * 1e-3) / 1e12
+    if rank == 0:
+        peaks = load_peaks()
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(3, args.warmup), "ms_per_step": float(ms_t.item()) / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": f"square_{n}_tw75_g{G}_beta25", "gather": bool(args.gather),
+                           "parallelism": f"tile-sharded x{world}", "shard_balance": round(shard.plan.balance(), 4),
+                           "l2": f"activations rotate over {n_sets} buffers of {n * n * 2 / 2**20:.0f} MiB"},
+                "tensor_frac_of_measured_peak": value / world / peaks["bf16_tflops_sustained"],
+                "gpu_launches": args.steps, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -404,7 +471,16 @@ def main():
                     help="tw1: the reference's tile-wise masks of the synthetic weights, built on the GPU; "
                          "random: the perf driver's random per-tile row subsets")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
+    ap.add_argument("--workload", choices=["bert", "square"], default="bert",
+                    help="bert: the headline BERT-base layer step; square: tile-sharded M=N=K=--size strong scaling")
+    ap.add_argument("--size", type=int, default=16384)
+    ap.add_argument("--gather", action="store_true", help="square workload: all-gather Ct inside the timed region")
     args = ap.parse_args()
+    if args.workload == "square" and args.impl == "ours":
+        if args.steps == 2000:
+            args.steps = 20
+        run_square(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

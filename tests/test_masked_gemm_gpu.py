@@ -142,3 +142,21 @@ def test_bad_arguments_are_rejected():
     with pytest.raises(TileSparseError):
         layer.masked_gemm(At[:, :60].contiguous())          # M = 60 is not a multiple of 8
     layer.close()
+
+
+def test_tile_sharded_layers_reproduce_the_unsharded_output():
+    """World of 3 emulated on one GPU: each rank's share runs by itself, slabs are joined by hand."""
+    from tilesparsity_b200 import TWLayer, sharding
+    layer, At, A16, W16 = _case(512, 1700, 512, lambda g, nt: synth.beta_skewed_counts(512, nt, 0.25, 3),
+                                torch.float16, 55, col_keep=0.85)
+    full = layer.masked_gemm(At)
+    Wd = torch.from_numpy(W16).cuda()
+    world = 3
+    slabs, shard = [], None
+    for r in range(world):
+        shard = sharding.ShardedTWLayer(Wd, layer.tiles, r, world, torch.float16)
+        slabs.append(shard.masked_gemm(At))
+        assert shard.plan.balance() > 0.8
+    joined = shard.assemble(torch.cat(slabs, 0))
+    assert torch.equal(joined, full)
+    layer.close()
