@@ -126,6 +126,16 @@ int ts_layer_check(ts_layer_t* layer, void* stream);
  * cta_cost == NULL to query *n_ctas. */
 int ts_layer_schedule_stats(ts_layer_t* layer, int M, int* n_ctas, float* cta_cost, int* n_units);
 
+/* Element-wise residual of a TEW mask as a sparse term, applied after ts_masked_gemm:
+ *     Ct[n][m] = (col_written[n] ? Ct[n][m] : 0) + alpha * sum_p val[p] * At[row_idx[p]][m]
+ * over the non-zeros p in col_ptr[n] .. col_ptr[n+1] of column n (device arrays; val is 16-bit in
+ * `dtype`; col_written_dev may be NULL when the tile-wise part wrote every column).  The reference's
+ * tw1m / tw2m masks (prune_algo.py:151-191) carry these elements only as extra ones in the dense 0/1
+ * mask; its GPU driver has no kernel for them. */
+int ts_residual_gemm(int dtype, int M, int N, const int32_t* col_ptr_dev, const int32_t* row_idx_dev,
+                     const void* val_dev, const uint8_t* col_written_dev, const void* At_dev, int64_t lda,
+                     void* Ct_dev, int64_t ldc, float alpha, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Reference-signature entry point.
  * ------------------------------------------------------------------------------------------- */

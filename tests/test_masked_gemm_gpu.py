@@ -160,3 +160,24 @@ def test_tile_sharded_layers_reproduce_the_unsharded_output():
     joined = shard.assemble(torch.cat(slabs, 0))
     assert torch.equal(joined, full)
     layer.close()
+
+
+@pytest.mark.parametrize("algo,shape,sparsity,g1", [("tw1m", (512, 1024), 75.0, 1.5), ("tw2m", (384, 768), 60.0, 2.0)])
+def test_tew_layer_matches_the_dense_masked_product(algo, shape, sparsity, g1):
+    """TW part on the tensor cores + residual as a sparse term == A @ (W * mask_tew)."""
+    from tilesparsity_b200 import TEWLayer, build_mask
+    g = synth.rng(sum(shape))
+    K, N = shape
+    M = 520
+    W = g.uniform(-0.1, 0.1, size=shape).astype(np.float32)
+    A = g.standard_normal((M, K), dtype=np.float32)
+    res = build_mask(algo, [np.abs(W)], sparsity, 128, g1, want_residual=True)
+    Wd = torch.from_numpy(W).cuda()
+    layer = TEWLayer(Wd, res.tiles[0], res.residuals[0], torch.float16)
+    assert layer.nnz > 0
+    At = torch.from_numpy(np.ascontiguousarray(A.T)).to(torch.float16).cuda()
+    out = layer.masked_gemm(At).float().cpu().numpy()
+    mask = res.masks[0].cpu().numpy()
+    ref = og.masked_matmul_dense(At.float().cpu().numpy().T, Wd.half().float().cpu().numpy(), mask).T
+    assert og.max_rel_error(out, ref) <= TOL
+    layer.close()

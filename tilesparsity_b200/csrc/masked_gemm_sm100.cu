@@ -18,18 +18,21 @@
 // the batch is its N dimension (MT = 128 or 256 columns per instruction), the kept rows are K.  The
 // packed weights are the K-major A operand, fetched by TMA with 128-byte swizzle; the gathered
 // activation rows are the MN-major B operand, fetched with 16-byte cp.async into the same swizzle
-// pattern (one kept row is one contiguous 2*MT-byte global segment).  The gather warps (four, or
-// three when only three stages fit) take the 64-row K blocks round-robin, one whole pipeline stage
-// each, so several stages fill concurrently and a warp's kept-row indices are fetched a full turn
-// ahead; each lane
+// pattern (one kept row is one contiguous 2*MT-byte global segment).  The four gather warps fill
+// each 64-row K block together; block descriptors and kept-row indices are prefetched into small
+// shared-memory rings; each lane
 // hands its copies to the stage's mbarrier with cp.async.mbarrier.arrive, so a stage is released to
 // the MMA warp the moment its bytes have landed.  Accumulators live in TMEM, double buffered: the
-// epilogue of one work unit overlaps the main loop of the next.  The epilogue thread that owns TMEM
-// lane j converts its row to 16 bit in shared memory; the four epilogue warps then write the rows
-// to Ct with 16-byte coalesced stores (an output row of a unit is one contiguous global segment).
+// epilogue of one work unit overlaps the main loop of the next.  Eight epilogue warps (two per TMEM
+// lane quarter, each taking half of the unit's batch columns) convert their rows to 16 bit into a
+// 128-byte-swizzled staging tile in shared memory.  When the tile's kept columns are consecutive
+// rows of Ct (no column pruning) the tile leaves with one TMA store per 64 batch columns; otherwise
+// the epilogue warps write the rows with 16-byte coalesced stores through the kept-column list.
 //
-// Warp roles (320 threads): warp 0 = weight TMA, warp 1 = TMEM allocation + MMA issue,
-// warps 2-5 = activation gather (warp 5 idles in the three-stage variant), warps 6-9 = epilogue.
+// Warp roles (448 threads): warp 0 = weight TMA, warp 1 = TMEM allocation + MMA issue,
+// warps 2-5 = activation gather, warps 6-13 = epilogue.
+#include <cstdlib>
+
 #include "ts_common.cuh"
 #include "ts_kernels.h"
 
@@ -40,7 +43,8 @@ namespace {
 constexpr int kNT = 128;                 // columns per tile (MMA M, TMEM lanes)
 constexpr int kKB = 64;                  // kept rows per pipeline stage
 constexpr int kWBytes = kNT * kKB * 2;   // 16 KiB of packed weights per stage
-constexpr int kThreads = 320;
+constexpr int kThreads = 448;
+constexpr int kEpiThreads = 256;
 constexpr uint32_t kASbo = 1024;         // bytes between 8-row K groups of the gathered operand
 constexpr uint32_t kALbo = kKB * 128;    // bytes between its 64-column batch groups
 constexpr uint32_t kWSbo = 1024;         // bytes between 8-row groups of the weight operand
@@ -52,14 +56,10 @@ struct Cfg {
   static constexpr int kStages = MT == 256 ? 3 : 5;
   static constexpr int kABytes = kKB * MT * 2;
   static constexpr int kStageBytes = kWBytes + kABytes;
-  static constexpr int kEpiRowBytes = MT * 2 + 16;  // +16: rows start in distinct bank groups
-  static constexpr int kEpiBytes = kNT * kEpiRowBytes;
+  static constexpr int kEpiGroupBytes = kNT * 128;   // staging: one 128-row x 64-column swizzled group
+  static constexpr int kEpiBytes = (MT / 64) * kEpiGroupBytes;
   static constexpr int kTmemCols = 2 * MT;          // two accumulators of MT fp32 columns
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 6144 + 1024;
-  // Gather warps take K blocks round-robin; a warp must never be more than one barrier phase
-  // ahead of the MMA warp (a parity wait cannot tell phase n from phase n+2), so its stride may
-  // not exceed the number of stages.
-  static constexpr int kGatherWarps = kStages < 4 ? kStages : 4;
   static constexpr int kLanesPerRow = MT / 8;       // 16-byte chunks in one gathered row
   static constexpr int kRowsPerInstr = 32 / kLanesPerRow;
 };
@@ -130,10 +130,12 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <int DT, int MT>
+template <int DT, int MT, int TMA_ROWS>
 __global__ void __launch_bounds__(kThreads, 1)
-masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* __restrict__ sched,
-                   int rounds, const BlockDesc* __restrict__ blocks, int blk_stride,
+masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+                   const __grid_constant__ CUtensorMap tmap_c, int use_tma_store,
+                   const WorkItem* __restrict__ sched,
+                   int rounds, const BlockDesc* __restrict__ blocks, int blk_stride, int K_oob,
                    const uint16_t* __restrict__ At, long long lda,
                    uint16_t* __restrict__ Ct, long long ldc, int M, float alpha, float beta,
                    int* __restrict__ status) {
@@ -159,12 +161,14 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(smem_u32(&bars->full[s]), 32 + 1);   // one gather warp + the TMA thread
+      // weight TMA thread + the gather leader's expect-tx arrival (rows fetched by TMA) + the 128
+      // cp.async lanes (rows fetched through the load/store unit)
+      mbar_init(smem_u32(&bars->full[s]), 1 + (TMA_ROWS > 0 ? 1 : 0) + (TMA_ROWS < kKB ? 128 : 0));
       mbar_init(smem_u32(&bars->empty[s]), 1);       // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars->acc_full[a]), 1);
-      mbar_init(smem_u32(&bars->acc_empty[a]), 128);
+      mbar_init(smem_u32(&bars->acc_empty[a]), kEpiThreads);
     }
     bars->abort_flag = 0;
     mbar_fence_init();
@@ -178,6 +182,9 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
   TS_TRACE(1, threadIdx.x == 0);
+  // The next kernel in the stream may begin its own set-up now (it cannot touch this kernel's
+  // outputs before its grid_dependency_wait, which returns only when this grid has completed).
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ weight TMA producer
@@ -257,19 +264,16 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
       ++acc_it;
       w = wn;
     }
-  } else if (warp < 2 + C::kGatherWarps) {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ activation gather
-    // This warp takes blocks gw, gw+kGW, gw+2*kGW, ... of the CTA's block stream; "j" counts its
-    // own blocks.  Everything it needs arrives by cp.async, requested ahead of use: the descriptor
-    // of block j+4 and the kept-row indices of block j+2 are requested while block j is copied, so
-    // no step of the loop waits on a dependent global read.
-    constexpr int kGW = C::kGatherWarps;
+    // The four gather warps fill every 64-row K block together, a quarter of its copies each, so a
+    // stage is occupied only briefly before the MMA warp can consume it.  Everything a warp needs
+    // arrives by cp.async, requested ahead of use: the descriptor of block j+4 and the kept-row
+    // indices of block j+2 are requested while block j is copied, so no step of the loop waits on
+    // a dependent global read.
+    constexpr int kGW = 4;
     const int gw = warp - 2;
-    const int chunk = lane % C::kLanesPerRow;      // 16-byte chunk of the row this lane copies
-    const int sub = lane / C::kLanesPerRow;        // row of the instruction this lane copies
-    const int g = chunk >> 3;                      // 64-column batch group of the chunk
-    const int c = chunk & 7;                       // chunk inside the 128-byte swizzled row
-    const BlockDesc* bd = blocks + static_cast<size_t>(cta) * blk_stride + gw;  // stride kGW
+    const BlockDesc* bd = blocks + static_cast<size_t>(cta) * blk_stride;
     BlockDesc* dring = bars->desc_ring[gw];
     int(*iring)[kKB] = bars->idx_ring[gw];
 
@@ -282,12 +286,15 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
       }
     };
     // prologue: descriptors of blocks 0..3 by plain loads, indices of blocks 0 and 1 requested
-    if (lane < 4) dring[lane] = bd[static_cast<size_t>(lane) * kGW];
+    if (lane < 4) dring[lane] = bd[lane];
     __syncwarp();
     request_indices(0);
     cp_async_commit();
     request_indices(1);
     cp_async_commit();
+    // The schedule and the index lists are static; the activations may be the previous kernel's
+    // output: wait for it before the first row is copied.
+    grid_dependency_wait();
 
     bool ok = true;
     for (int j = 0; ok; ++j) {
@@ -296,10 +303,10 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
       const BlockDesc d = dring[j & 7];
       if (d.meta == kBlockEnd) break;
       request_indices(j + 2);
-      if (lane == 0) cp_async_16_ca(smem_u32(&dring[(j + 4) & 7]), bd + static_cast<size_t>(j + 4) * kGW);
+      if (lane == 0) cp_async_16_ca(smem_u32(&dring[(j + 4) & 7]), bd + j + 4);
       cp_async_commit();
 
-      const uint32_t it = static_cast<uint32_t>(gw + j * kGW);
+      const uint32_t it = static_cast<uint32_t>(j);
       const uint32_t s = it % kStages;
       const uint32_t ph = (it / kStages) & 1u;
       if (j < 8) TS_TRACE(208 + j, lane == 0 && gw == 0);
@@ -308,53 +315,91 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
       if (j < 8) TS_TRACE(192 + j * 2, lane == 0 && gw == 0);
       const int nv = static_cast<int>(d.meta & 0x7fu);
       const int rel = (d.meta & 0x80u) ? static_cast<int>(d.meta >> 8) : -1;  // list position, if relative
-      const int m = d.m0 + chunk * 8;
-      const bool m_ok = m < M;
-      const uint16_t* src_col = At + (m_ok ? m : 0);
       const int* idx = iring[j & 3];
-      const uint32_t a_stage = smem_u32(smem + s * C::kStageBytes + kWBytes);
-      constexpr int kRpi = C::kRowsPerInstr;
-      constexpr int kCopies = kKB / kRpi;                     // copies per lane and block
-      // Every kept-row index this lane needs is read into registers before the first copy goes
-      // out: a shared-memory read between two copies would serialise the whole block.
-      long long krow[kCopies];
-#pragma unroll
-      for (int e = 0; e < kCopies; ++e) {
-        const int row = e * kRpi + sub;
-        krow[e] = (row < nv) ? idx[row] + (rel >= 0 ? rel + row : 0) : 0;
-      }
-      const uint32_t dst0 = a_stage + g * kALbo;
-      if (nv == kKB && d.m0 + MT <= M) {
-        // interior block: every row and every batch column is valid
-#pragma unroll
-        for (int e = 0; e < kCopies; ++e) {
-          const int row = e * kRpi + sub;
-          cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
-                           src_col + krow[e] * lda);
-        }
-      } else {
-        // ragged block: rows past the list and columns past M are zero-filled
-#pragma unroll
-        for (int e = 0; e < kCopies; ++e) {
-          const int row = e * kRpi + sub;
-          const bool valid = (row < nv) && m_ok;
-          cp_async_16(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
-                      valid ? src_col + krow[e] * lda : At, valid ? 16u : 0u);
+      const uint32_t a_base = smem_u32(smem + s * C::kStageBytes + kWBytes);
+      const uint32_t bar = smem_u32(&bars->full[s]);
+      // The block's first TMA_ROWS rows come through the copy engine (tile::gather4), the rest
+      // through the load/store unit (cp.async): the two paths run side by side.
+      if constexpr (TMA_ROWS > 0) {
+        // One gather4 per four kept rows and 64 batch columns (512 bytes).  Rows past the end of the
+        // list use a row index outside the tensor, which reads as zeros.
+        constexpr int kTmaBytes = TMA_ROWS * MT * 2;
+        if (gw == 0 && lane == 0) mbar_arrive_expect_tx(bar, kTmaBytes);
+        constexpr int kKg = TMA_ROWS / 4;                 // groups of four rows
+        constexpr int kOps = kKg * (MT / 64);
+        constexpr int kOpsPerWarp = (kOps + kGW - 1) / kGW;
+        static_assert(kOpsPerWarp <= 32, "one gather4 per lane");
+        const int qq = gw * kOpsPerWarp + lane;
+        if (lane < kOpsPerWarp && qq < kOps) {
+          const int kg = qq % kKg, mg = qq / kKg;
+          const int4 r4 = *reinterpret_cast<const int4*>(idx + kg * 4);
+          const int base = kg * 4;
+          const int add = rel >= 0 ? rel + base : 0;
+          const int step = rel >= 0 ? 1 : 0;
+          const int r0 = base + 0 < nv ? r4.x + add : K_oob;
+          const int r1 = base + 1 < nv ? r4.y + add + step : K_oob;
+          const int r2 = base + 2 < nv ? r4.z + add + 2 * step : K_oob;
+          const int r3 = base + 3 < nv ? r4.w + add + 3 * step : K_oob;
+          tma_gather4(a_base + mg * kALbo + (kg >> 1) * kASbo + (kg & 1) * 512, &tmap_a, d.m0 + mg * 64, r0,
+                      r1, r2, r3, bar);
         }
       }
-      cp_async_arrive_noinc(smem_u32(&bars->full[s]));
-      TS_TRACE(24 + (it < 4 ? it : 4), lane == 0);
+      if constexpr (TMA_ROWS < kKB) {
+        // 16-byte cp.async copies: this warp takes a quarter of the remaining rows.  Their indices
+        // are read into registers before the first copy goes out (a shared-memory read between two
+        // copies would serialise them).
+        constexpr int kLpr = C::kLanesPerRow, kRpi = C::kRowsPerInstr;
+        constexpr int kLsuRows = kKB - TMA_ROWS;
+        constexpr int kRowsPerWarp = kLsuRows / kGW;
+        static_assert(kLsuRows % (kGW * kRpi) == 0, "rows must split evenly over the gather warps");
+        constexpr int kCopies = kRowsPerWarp / kRpi;
+        const int chunk = lane % kLpr, sub = lane / kLpr;
+        const int g = chunk >> 3, c = chunk & 7;
+        const int m = d.m0 + chunk * 8;
+        const bool m_ok = m < M;
+        const uint16_t* src_col = At + (m_ok ? m : 0);
+        const int row0 = TMA_ROWS + gw * kRowsPerWarp;
+        int krow[kCopies];
+#pragma unroll
+        for (int e = 0; e < kCopies; ++e) {
+          const int row = row0 + e * kRpi + sub;
+          krow[e] = (row < nv) ? idx[row] + (rel >= 0 ? rel + row : 0) : 0;
+        }
+        const uint32_t dst0 = a_base + g * kALbo;
+        if (nv == kKB && d.m0 + MT <= M) {
+#pragma unroll
+          for (int e = 0; e < kCopies; ++e) {
+            const int row = row0 + e * kRpi + sub;
+            cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
+                             src_col + static_cast<long long>(krow[e]) * lda);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < kCopies; ++e) {
+            const int row = row0 + e * kRpi + sub;
+            const bool valid = (row < nv) && m_ok;
+            cp_async_16(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
+                        valid ? src_col + static_cast<long long>(krow[e]) * lda : At, valid ? 16u : 0u);
+          }
+        }
+        cp_async_arrive_noinc(bar);
+      }
+      TS_TRACE(24 + (it < 4 ? it : 4), lane == 0 && gw == 0);
       if (j < 8) TS_TRACE(193 + j * 2, lane == 0 && gw == 0);
     }
     cp_async_wait_all();  // nothing of this thread is in flight when the CTA retires
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ epilogue
-    constexpr int kChunks = MT / 32;
-    const int q = warp & 3;             // TMEM lane quarter this warp may read
-    const int j = q * 32 + lane;        // tile column owned by this thread
-    uint8_t* my_row = epi + j * C::kEpiRowBytes;
+    constexpr int kHalfCols = MT / 2;            // batch columns per epilogue thread
+    constexpr int kChunks = kHalfCols / 32;      // TMEM reads of 32 columns per thread
+    const int ew = warp - 6;                     // 0..7
+    const int half = ew >> 2;                    // which half of the batch columns
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int j = q * 32 + lane;                 // tile column owned by this thread
+    const bool leader = (warp == 6 && lane == 0);
     uint32_t acc_it = 0;
     bool ok = true;
+    grid_dependency_wait();   // Ct may still be read or written by the previous kernel
     for (int r = 0; ok && w.tile >= 0; ++r) {
       const WorkItem wn = fetch_item(sched, rounds, grid, cta, r + 1);
       const uint32_t a = acc_it & 1u;
@@ -362,6 +407,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
       const int m0 = w.mblock * MT;
       const int m_cnt = min(MT, M - m0);
       const bool active = j < w.n_count;
+      const bool tma_store = use_tma_store && w.pad_ != 0 && beta == 0.0f;   // consecutive Ct rows
       long long c_row = 0;
       if (active) {
         c_row = w.c_row0 + (w.n_list ? __ldg(w.n_list + j) + (w.relative ? j : 0) : j);
@@ -372,11 +418,11 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
       TS_TRACE(32, threadIdx.x == 192);
       TS_TRACE_U(3, acc_it, threadIdx.x == 192);
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + a * MT + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t taddr = tmem_base + a * MT + half * kHalfCols + (static_cast<uint32_t>(q * 32) << 16);
       const bool has_acc = w.k_count > 0;
-      // TMEM reads are issued four chunks (128 columns) at a time and awaited once: a read's
-      // latency is far longer than the conversion of one chunk, so they must overlap each other.
-      constexpr int kBatch = 4;
+      // TMEM reads are issued two chunks (64 columns) at a time and awaited once: a read's latency
+      // is far longer than the conversion of one chunk, so they must overlap each other.
+      constexpr int kBatch = 2;
 #pragma unroll
       for (int c0 = 0; c0 < kChunks; c0 += kBatch) {
         uint32_t v[kBatch][32];
@@ -395,17 +441,24 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bars->acc_empty[a]));
         }
+        if (c0 == 0) {
+          // the staging tile is free once the previous unit's TMA store has read it (the leader
+          // waits for that) and every thread has finished the previous copy-out
+          if (leader) bulk_wait_read_all();
+          named_barrier_sync(1, kEpiThreads);
+        }
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
-          const int cc = c0 + b;
+          const int cc = c0 + b;                         // chunk inside this thread's half
+          const int col0 = half * kHalfCols + cc * 32;   // first batch column of the chunk
           uint32_t(&cur)[32] = v[b];
           uint32_t o[16];
-          if (beta != 0.0f && active && (cc * 32 < m_cnt)) {
-            const uint4* cs = reinterpret_cast<const uint4*>(gdst + cc * 32);
+          if (beta != 0.0f && active && (col0 < m_cnt)) {
+            const uint4* cs = reinterpret_cast<const uint4*>(gdst + col0);
 #pragma unroll
             for (int e4 = 0; e4 < 4; ++e4) {
               uint4 old = make_uint4(0, 0, 0, 0);
-              if (cc * 32 + e4 * 8 < m_cnt) old = cs[e4];
+              if (col0 + e4 * 8 < m_cnt) old = cs[e4];
               const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
@@ -428,32 +481,50 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
                                alpha * __uint_as_float(cur[2 * e + 1]));
             }
           }
-          uint4* dst = reinterpret_cast<uint4*>(my_row + cc * 64);
+          // staging: [64-column group][tile column j][128 bytes], 16-byte chunks swizzled by j & 7
+          const int g16 = col0 >> 3;                     // first 16-byte chunk of these 32 columns
+          uint8_t* grp = epi + (g16 >> 3) * C::kEpiGroupBytes + j * 128;
 #pragma unroll
           for (int e4 = 0; e4 < 4; ++e4) {
-            dst[e4] = make_uint4(o[e4 * 4], o[e4 * 4 + 1], o[e4 * 4 + 2], o[e4 * 4 + 3]);
+            const int c = (g16 & 7) + e4;
+            *reinterpret_cast<uint4*>(grp + ((c ^ (j & 7)) << 4)) =
+                make_uint4(o[e4 * 4], o[e4 * 4 + 1], o[e4 * 4 + 2], o[e4 * 4 + 3]);
           }
         }
       }
-      bars->c_row[j] = active ? static_cast<int>(c_row) : -1;
+      if (half == 0) bars->c_row[j] = active ? static_cast<int>(c_row) : -1;
       TS_TRACE(33, threadIdx.x == 192);
       TS_TRACE_U(4, acc_it, threadIdx.x == 192);
-      named_barrier_sync(1, 128);       // all 128 rows are staged
+      if (tma_store) fence_proxy_async_smem();
+      named_barrier_sync(1, kEpiThreads);       // all rows are staged
       TS_TRACE_U(5, acc_it, threadIdx.x == 192);
-      {
+      if (tma_store) {
+        if (leader) {
+          const int row0 = w.c_row0 + (w.n_list ? __ldg(w.n_list) + 0 : 0);
+#pragma unroll
+          for (int mg = 0; mg < MT / 64; ++mg) {
+            if (mg * 64 < m_cnt) {
+              tma_store_2d(&tmap_c, smem_u32(epi + mg * C::kEpiGroupBytes), m0 + mg * 64, row0);
+            }
+          }
+          bulk_commit();
+        }
+      } else {
+        // copy-out through the kept-column list: 16 rows per warp, 16 bytes per lane
         constexpr int kLpr = C::kLanesPerRow, kRpi = C::kRowsPerInstr;
         const int chunk = lane % kLpr, sub = lane / kLpr;
         const bool m_ok = chunk * 8 < m_cnt;
 #pragma unroll
-        for (int r4 = 0; r4 < 32 / kRpi; r4 += 4) {
+        for (int r4 = 0; r4 < 16 / kRpi; r4 += 4) {
           // four rows per batch: shared-memory reads first, then the global stores
           int cr[4];
           uint4 val[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int row = q * 32 + (r4 + e) * kRpi + sub;
+            const int row = ew * 16 + (r4 + e) * kRpi + sub;
             cr[e] = bars->c_row[row];
-            val[e] = *reinterpret_cast<const uint4*>(epi + row * C::kEpiRowBytes + chunk * 16);
+            val[e] = *reinterpret_cast<const uint4*>(epi + (chunk >> 3) * C::kEpiGroupBytes + row * 128 +
+                                                     (((chunk & 7) ^ (row & 7)) << 4));
           }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -464,11 +535,10 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
         }
       }
       TS_TRACE_U(6, acc_it, threadIdx.x == 192);
-      named_barrier_sync(1, 128);       // the staging rows may be overwritten
-      TS_TRACE_U(7, acc_it, threadIdx.x == 192);
       ++acc_it;
       w = wn;
     }
+    if (leader) bulk_wait_all();                // the last TMA store has been written
     TS_TRACE(34, threadIdx.x == 192);
   }
 
@@ -480,11 +550,19 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const WorkItem* _
   TS_TRACE(2, threadIdx.x == 0);
 }
 
-template <int DT, int MT>
-cudaError_t launch_variant(const CUtensorMap& tmap_w, const WorkItem* sched, int rounds, int grid,
+template <int DT, int MT, int TMA_ROWS>
+cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const CUtensorMap& tmap_c,
+                           int use_tma_store, int K_oob,
+                           const WorkItem* sched, int rounds, int grid,
                            const BlockDesc* blocks, int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
                            float alpha, float beta, int* status, cudaStream_t stream) {
-  auto kern = masked_gemm_kernel<DT, MT>;
+  // Programmatic dependent launch lets this kernel's set-up overlap the tail of the kernel before
+  // it in the stream.  TS_PDL=0 turns it off.
+  static const bool pdl = [] {
+    const char* e = getenv("TS_PDL");
+    return !(e && e[0] == '0');
+  }();
+  auto kern = masked_gemm_kernel<DT, MT, TMA_ROWS>;
   // The dynamic shared-memory limit is a per-device, per-kernel attribute: set it once for each.
   static bool attr_set[64] = {};
   int dev = 0;
@@ -495,32 +573,49 @@ cudaError_t launch_variant(const CUtensorMap& tmap_w, const WorkItem* sched, int
     if (e != cudaSuccess) return e;
     if (dev < 64) attr_set[dev] = true;
   }
-  kern<<<grid, kThreads, Cfg<MT>::kSmemBytes, stream>>>(tmap_w, sched, rounds, blocks, blk_stride,
-                                                        static_cast<const uint16_t*>(At), lda,
-                                                        static_cast<uint16_t*>(Ct), ldc, M, alpha,
-                                                        beta, status);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Cfg<MT>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_a, tmap_c, use_tma_store, sched, rounds, blocks, blk_stride,
+                            K_oob, static_cast<const uint16_t*>(At), lda, static_cast<uint16_t*>(Ct), ldc, M,
+                            alpha, beta, status);
 }
 
 }  // namespace
 
-cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w,
-                               const WorkItem* sched, int rounds, int grid,
-                               const BlockDesc* blocks, int blk_stride, const void* At,
+cudaError_t masked_gemm_launch(int dtype, int unit_rows, int tma_rows, const CUtensorMap& tmap_w,
+                               const CUtensorMap* tmap_a, const CUtensorMap* tmap_c, int K_oob,
+                               const WorkItem* sched, int rounds,
+                               int grid, const BlockDesc* blocks, int blk_stride, const void* At,
                                long long lda, void* Ct, long long ldc, int M, float alpha,
                                float beta, int* status, cudaStream_t stream) {
+  if (tma_rows > 0 && !tmap_a) return cudaErrorInvalidValue;
+#define TS_LAUNCH(DT, MT, TR)                                                                        \
+  launch_variant<DT, MT, TR>(tmap_w, TR > 0 ? *tmap_a : tmap_w, tmap_c ? *tmap_c : tmap_w,            \
+                             tmap_c ? 1 : 0, K_oob, sched, rounds, grid, blocks,                      \
+                             blk_stride, At, lda, Ct, ldc, M, alpha, beta, status, stream)
+#define TS_BY_ROWS(DT, MT)                      \
+  switch (tma_rows) {                           \
+    case 0: return TS_LAUNCH(DT, MT, 0);        \
+    case 64: return TS_LAUNCH(DT, MT, 64);      \
+    default: return cudaErrorInvalidValue;      \
+  }
+  const bool bf = dtype == kBF16;
   if (unit_rows == 256) {
-    return dtype == kBF16 ? launch_variant<kBF16, 256>(tmap_w, sched, rounds, grid, blocks, blk_stride, At, lda, Ct, ldc,
-                                                       M, alpha, beta, status, stream)
-                          : launch_variant<kF16, 256>(tmap_w, sched, rounds, grid, blocks, blk_stride, At, lda, Ct, ldc,
-                                                      M, alpha, beta, status, stream);
+    if (bf) { TS_BY_ROWS(kBF16, 256) } else { TS_BY_ROWS(kF16, 256) }
   }
   if (unit_rows == 128) {
-    return dtype == kBF16 ? launch_variant<kBF16, 128>(tmap_w, sched, rounds, grid, blocks, blk_stride, At, lda, Ct, ldc,
-                                                       M, alpha, beta, status, stream)
-                          : launch_variant<kF16, 128>(tmap_w, sched, rounds, grid, blocks, blk_stride, At, lda, Ct, ldc,
-                                                      M, alpha, beta, status, stream);
+    if (bf) { TS_BY_ROWS(kBF16, 128) } else { TS_BY_ROWS(kF16, 128) }
   }
+#undef TS_BY_ROWS
+#undef TS_LAUNCH
   return cudaErrorInvalidValue;
 }
 

@@ -56,7 +56,7 @@ struct alignas(16) WorkItem {
   int relative;
   int mblock;
   int tile;  // < 0: no unit
-  int pad_;
+  int pad_;  // != 0: the tile's kept columns are consecutive rows of Ct and fill a 128-row store box
 };
 static_assert(sizeof(WorkItem) == 48, "WorkItem is read as three 16-byte words");
 
@@ -155,6 +155,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while the kernel before it in the stream is still running.  grid_dependency_wait() blocks
+// until that kernel has completed and its writes are visible; grid_launch_dependents() lets the
+// kernel after this one start early in turn.  Both are no-ops in an ordinary launch.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // Proxy / tcgen05 fences
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -224,8 +238,28 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// TMA gather: rows r0..r3 of a 2-D tensor, `box` columns starting at column x, land as four
+// consecutive rows at dst (the tensor map's box is {columns, 1}).  Rows or columns outside the
+// tensor read as zeros and still count towards the transaction bytes.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int x, int r0, int r1,
+                                            int r2, int r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// TMA tile store: the box of `map` leaves shared memory for the tensor at column x, row y.  Parts of
+// the box outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
 }
 
 __device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {

@@ -15,9 +15,15 @@ namespace ts {
 // number of batch rows per work unit the schedule was built for: 128 or 256.  `blocks` is the same
 // schedule at K-block granularity: CTA b's 64-row blocks in processing order at
 // blocks[b*blk_stride ...], terminated (and padded to blk_stride) by end markers.
-cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w,
-                               const WorkItem* sched, int rounds, int grid,
-                               const BlockDesc* blocks, int blk_stride, const void* At,
+// tma_rows of every 64-row K block are gathered by the copy engine (tile::gather4 through tmap_a, a
+// tensor map over At [K][lda] with box 64 x 1 and 128-byte swizzle; K_oob is a row index outside the
+// tensor, used for zero fill), the others by cp.async.  Supported: 0 (all cp.async) and 64 (all TMA).
+// tmap_c != nullptr enables TMA stores (tensor map over Ct [N][ldc], box 64 x 128, 128-byte swizzle)
+// for the work items whose pad_ flag says their kept columns are consecutive rows of Ct.
+cudaError_t masked_gemm_launch(int dtype, int unit_rows, int tma_rows, const CUtensorMap& tmap_w,
+                               const CUtensorMap* tmap_a, const CUtensorMap* tmap_c, int K_oob,
+                               const WorkItem* sched, int rounds,
+                               int grid, const BlockDesc* blocks, int blk_stride, const void* At,
                                long long lda, void* Ct, long long ldc, int M, float alpha,
                                float beta, int* status, cudaStream_t stream);
 
@@ -35,6 +41,12 @@ cudaError_t masked_gemm_simt_launch(int dtype, const TileDesc* tiles, int n_tile
 cudaError_t pack_weights_launch(int w_dtype, int out_dtype, const void* W, long long ld_w,
                                 const TileDesc* tiles, int n_tiles, int max_k, void* Wp,
                                 long long ldw, cudaStream_t stream);
+
+// Sparse residual term (residual.cu): Ct[n][m] = (col_written[n] ? Ct[n][m] : 0) + alpha * sum over the
+// non-zeros p of column n of val[p] * At[row_idx[p]][m].  col_written may be nullptr (all written).
+cudaError_t residual_spmm_launch(int dtype, const int* col_ptr, const int* row_idx, const void* val,
+                                 const uint8_t* col_written, const void* At, long long lda, void* Ct,
+                                 long long ldc, int M, int N, float alpha, cudaStream_t stream);
 
 // out[c][r] = in[r][c] for 16-bit elements (pack.cu).
 cudaError_t transpose16_launch(const void* in, long long ld_in, void* out, long long ld_out,

@@ -173,6 +173,47 @@ class TWLayer:
             check(lib.ts_layer_check(self._h, _stream_ptr(self.device)))
 
 
+class TEWLayer:
+    """A TEW layer: tile-wise part on the tensor cores plus the element-wise residual as a sparse term.
+
+    Built from the output of `build_mask("tw1m" | "tw2m", ..., want_residual=True)`: `tiles` is the
+    tile-wise structure, `residual` a bool [K, N] CUDA tensor marking the extra elements
+    (Pruning/VGG/prune_algo.py:171-175 adds them to the dense mask).
+    """
+
+    def __init__(self, W: torch.Tensor, tiles: TileSet, residual: torch.Tensor, dtype=torch.float16):
+        self.tw = TWLayer(tiles, dtype, W.device)
+        self.tw.pack(W)
+        self.dtype, self.device, self.K, self.N = dtype, W.device, tiles.K, tiles.N
+        nz = residual.t().nonzero()                       # sorted by (n, k)
+        cols, rows = nz[:, 0], nz[:, 1]
+        self.nnz = int(nz.shape[0])
+        counts = torch.bincount(cols, minlength=self.N)
+        self.col_ptr = torch.zeros(self.N + 1, dtype=torch.int32, device=W.device)
+        self.col_ptr[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        self.row_idx = rows.to(torch.int32).contiguous()
+        self.val = W[rows, cols].to(dtype).contiguous()
+        written = torch.zeros(self.N, dtype=torch.uint8, device=W.device)
+        written[torch.from_numpy(tiles.kept_n.astype(np.int64)).to(W.device)] = 1
+        self.col_written = written
+
+    def masked_gemm(self, At: torch.Tensor, out: torch.Tensor | None = None, alpha: float = 1.0) -> torch.Tensor:
+        """Ct[N, M] = alpha * (W .* mask_tew)^T @ At[K, M]."""
+        Ct = self.tw.masked_gemm(At, out=out, alpha=alpha)
+        M = At.shape[1]
+        if self.nnz:
+            with torch.cuda.device(self.device):
+                check(lib.ts_residual_gemm(_TS_DTYPE[self.dtype], M, self.N, C.c_void_p(self.col_ptr.data_ptr()),
+                                           C.c_void_p(self.row_idx.data_ptr()), C.c_void_p(self.val.data_ptr()),
+                                           C.c_void_p(self.col_written.data_ptr()), C.c_void_p(At.data_ptr()),
+                                           At.stride(0), C.c_void_p(Ct.data_ptr()), Ct.stride(0), alpha,
+                                           _stream_ptr(self.device)))
+        return Ct
+
+    def close(self) -> None:
+        self.tw.close()
+
+
 def transpose16(x: torch.Tensor) -> torch.Tensor:
     """[R, C] 16-bit tensor -> its transpose [C, R], materialised by the library's kernel."""
     if x.dim() != 2 or x.element_size() != 2 or x.stride(1) != 1 or not x.is_cuda:
