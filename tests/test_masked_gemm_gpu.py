@@ -107,7 +107,7 @@ def test_tensor_core_and_cuda_core_paths_agree_on_a_large_shape():
     layer.check()
     assert float((a - b).abs().max() / b.abs().max()) <= TOL
     st = layer.schedule_stats(4096)
-    assert st["n_units"] in (layer.tiles.n_tiles * 16, layer.tiles.n_tiles * 32) and 0.5 < st["balance"] <= 1.0
+    assert st["n_units"] >= layer.tiles.n_tiles * 16 and 0.5 < st["balance"] <= 1.0
     layer.close()
 
 

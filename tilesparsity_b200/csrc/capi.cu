@@ -166,48 +166,92 @@ int choose_unit_rows(int n_live_tiles, int M, int n_ctas) {
   return 2 * units256 >= n_ctas ? 256 : 128;
 }
 
-// Longest-processing-time list scheduling of (tile, batch block) units onto `n_ctas` persistent
-// CTAs.  Output: flat [rounds][grid] table; a CTA's units fill its column from round 0 without
-// gaps, tile = -1 marks the end.
+// Work distribution for the persistent kernel.  Units are (tile, run of batch rows); tiles are taken
+// in descending kept-K order and a tile's units are consecutive, so the CTAs that run at the same
+// time work on the same tile and the same kept rows of At (L2 and DRAM locality).  Full-width units
+// (`unit_rows` rows) fill as many complete waves of `n_ctas` units as there are; the rows that are
+// left would make a partial wave, so they are cut into narrower units (multiples of 64 rows) such
+// that every CTA gets at most one of them.  Assignment is longest-processing-time list scheduling.
+// Output: flat [rounds][grid] table; a CTA's units fill its column from round 0 without gaps,
+// tile = -1 marks the end.
 void build_schedule(const std::vector<ts::TileDesc>& tiles, int M, int unit_rows, int n_ctas,
                     std::vector<ts::WorkItem>* flat, int* rounds, int* grid, int* n_units,
                     std::vector<float>* cta_cost, std::vector<ts::BlockDesc>* blocks,
                     int* blk_stride) {
-  const int mblocks = (M + unit_rows - 1) / unit_rows;
   std::vector<int> order;
   for (int t = 0; t < static_cast<int>(tiles.size()); ++t) {
     if (tiles[t].n_count > 0) order.push_back(t);
   }
   std::stable_sort(order.begin(), order.end(),
                    [&](int a, int b) { return tiles[a].k_count > tiles[b].k_count; });
-  *n_units = static_cast<int>(order.size()) * mblocks;
+  struct U {
+    int tile, m_begin, m_len;
+    float cost;
+  };
+  const int gran_per_unit = unit_rows / 64;
+  const int granules = (M + 63) / 64;                       // 64-row granules per tile
+  const int full_per_tile = granules / gran_per_unit;       // full-width units per tile
+  const int tail_gran = granules - full_per_tile * gran_per_unit;
+  auto make = [&](int t, int g0, int glen) {
+    return U{t, g0 * 64, glen * 64, unit_cost(tiles[t].k_count) * glen / static_cast<float>(gran_per_unit)};
+  };
+  std::vector<U> units;
+  for (int t : order) {
+    for (int u = 0; u < full_per_tile; ++u) units.push_back(make(t, u * gran_per_unit, gran_per_unit));
+    if (tail_gran > 0) units.push_back(make(t, full_per_tile * gran_per_unit, tail_gran));
+  }
+  // the last partial wave of units is re-cut into narrower units
+  const int n_full_waves = static_cast<int>(units.size()) / std::max(1, n_ctas);
+  size_t keep = static_cast<size_t>(n_full_waves) * n_ctas;
+  if (keep < units.size() && n_ctas > 1) {
+    long long rest_gran = 0;
+    for (size_t i = keep; i < units.size(); ++i) rest_gran += units[i].m_len / 64;
+    int width = static_cast<int>((rest_gran + n_ctas - 1) / n_ctas);   // granules per narrow unit
+    width = std::max(1, std::min(width, gran_per_unit));
+    std::vector<U> rest(units.begin() + keep, units.end());
+    units.resize(keep);
+    // merge the left-over units into runs of consecutive rows of one tile, then cut every run
+    // into pieces of `width` granules
+    size_t i = 0;
+    while (i < rest.size()) {
+      const int t = rest[i].tile;
+      const int g_begin = rest[i].m_begin / 64;
+      int g_end = g_begin + rest[i].m_len / 64;
+      size_t k = i + 1;
+      while (k < rest.size() && rest[k].tile == t && rest[k].m_begin / 64 == g_end) {
+        g_end += rest[k].m_len / 64;
+        ++k;
+      }
+      for (int g0 = g_begin; g0 < g_end; g0 += width) units.push_back(make(t, g0, std::min(width, g_end - g0)));
+      i = k;
+    }
+  }
+  *n_units = static_cast<int>(units.size());
   const int g = std::max(1, std::min(n_ctas, *n_units));
   std::vector<std::vector<ts::WorkItem>> lists(g);
   typedef std::pair<float, int> Load;  // (load, cta), smallest load first, then lowest cta
   std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
   for (int b = 0; b < g; ++b) heap.push({0.0f, b});
   cta_cost->assign(g, 0.0f);
-  for (int t : order) {
-    const ts::TileDesc& td = tiles[t];
-    for (int mb = 0; mb < mblocks; ++mb) {
-      Load l = heap.top();
-      heap.pop();
-      ts::WorkItem w;
-      w.k_list = td.k_list;
-      w.n_list = td.n_list;
-      w.k_count = td.k_count;
-      w.n_count = td.n_count;
-      w.w_row0 = td.w_row0;
-      w.c_row0 = td.c_row0;
-      w.relative = td.relative;
-      w.mblock = mb;
-      w.tile = t;
-      w.pad_ = td.pad_;
-      lists[l.second].push_back(w);
-      l.first += unit_cost(td.k_count);
-      (*cta_cost)[l.second] = l.first;
-      heap.push(l);
-    }
+  for (const U& u : units) {
+    const ts::TileDesc& td = tiles[u.tile];
+    Load l = heap.top();
+    heap.pop();
+    ts::WorkItem w;
+    w.k_list = td.k_list;
+    w.n_list = td.n_list;
+    w.k_count = td.k_count;
+    w.n_count = td.n_count;
+    w.w_row0 = td.w_row0;
+    w.c_row0 = td.c_row0;
+    w.flags = (td.relative ? ts::kItemRelative : 0) | (td.pad_ ? ts::kItemDenseRows : 0);
+    w.m_begin = u.m_begin;
+    w.m_len = u.m_len;
+    w.tile = u.tile;
+    lists[l.second].push_back(w);
+    l.first += u.cost;
+    (*cta_cost)[l.second] = l.first;
+    heap.push(l);
   }
   int r = 0;
   for (const auto& l : lists) r = std::max<int>(r, static_cast<int>(l.size()));
@@ -241,9 +285,9 @@ void build_schedule(const std::vector<ts::TileDesc>& tiles, int M, int unit_rows
       for (int pos = 0; pos < w.k_count; pos += 64) {
         ts::BlockDesc d;
         d.idx = w.k_list + pos;
-        d.m0 = w.mblock * unit_rows;
-        d.meta = static_cast<uint32_t>(std::min(64, w.k_count - pos)) | (w.relative ? 0x80u : 0u) |
-                 (static_cast<uint32_t>(pos) << 8);
+        d.m0 = w.m_begin;
+        d.meta = static_cast<uint32_t>(std::min(64, w.k_count - pos)) | ((w.flags & ts::kItemRelative) ? 0x80u : 0u) |
+                 (static_cast<uint32_t>(w.m_len / 64 - 1) << 8) | (static_cast<uint32_t>(pos) << 10);
         (*blocks)[o++] = d;
       }
     }

@@ -118,9 +118,8 @@ __device__ __forceinline__ WorkItem fetch_item(const WorkItem* sched, int rounds
   WorkItem w;
   w.k_list = nullptr;
   w.n_list = nullptr;
-  w.k_count = w.n_count = w.w_row0 = w.c_row0 = w.relative = w.mblock = 0;
+  w.k_count = w.n_count = w.w_row0 = w.c_row0 = w.flags = w.m_begin = w.m_len = 0;
   w.tile = -1;
-  w.pad_ = 0;
   return w;
 }
 
@@ -210,7 +209,8 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    constexpr uint32_t idesc = umma_idesc_f16(DT == kBF16 ? 1 : 0, /*a_mn=*/0, /*b_mn=*/1, kNT, MT);
+    // the MMA's N dimension is the unit's batch-row count (a multiple of 64, at most MT)
+    constexpr uint32_t idesc0 = umma_idesc_f16(DT == kBF16 ? 1 : 0, /*a_mn=*/0, /*b_mn=*/1, kNT, 0);
     uint32_t it = 0, acc_it = 0;
     bool ok = true;
     for (int r = 0; ok && w.tile >= 0; ++r) {
@@ -223,6 +223,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       TS_TRACE_U(0, acc_it, lane == 0);
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + a * MT;
+      const uint32_t idesc = idesc0 | (static_cast<uint32_t>(w.m_len >> 3) << 17);
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const uint32_t s = it % kStages;
         const uint32_t ph = (it / kStages) & 1u;
@@ -314,7 +315,8 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       if (!ok) break;
       if (j < 8) TS_TRACE(192 + j * 2, lane == 0 && gw == 0);
       const int nv = static_cast<int>(d.meta & 0x7fu);
-      const int rel = (d.meta & 0x80u) ? static_cast<int>(d.meta >> 8) : -1;  // list position, if relative
+      const int rel = (d.meta & 0x80u) ? static_cast<int>(d.meta >> 10) : -1;  // list position, if relative
+      const int m_len = (static_cast<int>((d.meta >> 8) & 3u) + 1) * 64;        // batch rows of the unit
       const int* idx = iring[j & 3];
       const uint32_t a_base = smem_u32(smem + s * C::kStageBytes + kWBytes);
       const uint32_t bar = smem_u32(&bars->full[s]);
@@ -323,14 +325,13 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       if constexpr (TMA_ROWS > 0) {
         // One gather4 per four kept rows and 64 batch columns (512 bytes).  Rows past the end of the
         // list use a row index outside the tensor, which reads as zeros.
-        constexpr int kTmaBytes = TMA_ROWS * MT * 2;
-        if (gw == 0 && lane == 0) mbar_arrive_expect_tx(bar, kTmaBytes);
+        if (gw == 0 && lane == 0) mbar_arrive_expect_tx(bar, TMA_ROWS * m_len * 2);
         constexpr int kKg = TMA_ROWS / 4;                 // groups of four rows
         constexpr int kOps = kKg * (MT / 64);
         constexpr int kOpsPerWarp = (kOps + kGW - 1) / kGW;
         static_assert(kOpsPerWarp <= 32, "one gather4 per lane");
         const int qq = gw * kOpsPerWarp + lane;
-        if (lane < kOpsPerWarp && qq < kOps) {
+        if (lane < kOpsPerWarp && qq < kOps && (qq / kKg) * 64 < m_len) {
           const int kg = qq % kKg, mg = qq / kKg;
           const int4 r4 = *reinterpret_cast<const int4*>(idx + kg * 4);
           const int base = kg * 4;
@@ -366,14 +367,17 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           krow[e] = (row < nv) ? idx[row] + (rel >= 0 ? rel + row : 0) : 0;
         }
         const uint32_t dst0 = a_base + g * kALbo;
-        if (nv == kKB && d.m0 + MT <= M) {
+        const bool lane_live = chunk * 8 < m_len;           // columns past the unit are never read
+        if (nv == kKB && d.m0 + m_len <= M) {
+          if (lane_live) {
 #pragma unroll
-          for (int e = 0; e < kCopies; ++e) {
-            const int row = row0 + e * kRpi + sub;
-            cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
-                             src_col + static_cast<long long>(krow[e]) * lda);
+            for (int e = 0; e < kCopies; ++e) {
+              const int row = row0 + e * kRpi + sub;
+              cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
+                               src_col + static_cast<long long>(krow[e]) * lda);
+            }
           }
-        } else {
+        } else if (lane_live) {
 #pragma unroll
           for (int e = 0; e < kCopies; ++e) {
             const int row = row0 + e * kRpi + sub;
@@ -390,10 +394,9 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     cp_async_wait_all();  // nothing of this thread is in flight when the CTA retires
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ epilogue
-    constexpr int kHalfCols = MT / 2;            // batch columns per epilogue thread
-    constexpr int kChunks = kHalfCols / 32;      // TMEM reads of 32 columns per thread
+    constexpr int kGroups = MT / 128;            // 64-column groups per epilogue thread
     const int ew = warp - 6;                     // 0..7
-    const int half = ew >> 2;                    // which half of the batch columns
+    const int half = ew >> 2;                    // takes the 64-column groups half, half+2, ...
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int j = q * 32 + lane;                 // tile column owned by this thread
     const bool leader = (warp == 6 && lane == 0);
@@ -404,13 +407,13 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const WorkItem wn = fetch_item(sched, rounds, grid, cta, r + 1);
       const uint32_t a = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
-      const int m0 = w.mblock * MT;
-      const int m_cnt = min(MT, M - m0);
+      const int m0 = w.m_begin;
+      const int m_cnt = min(w.m_len, M - m0);
       const bool active = j < w.n_count;
-      const bool tma_store = use_tma_store && w.pad_ != 0 && beta == 0.0f;   // consecutive Ct rows
+      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f;   // consecutive Ct rows
       long long c_row = 0;
       if (active) {
-        c_row = w.c_row0 + (w.n_list ? __ldg(w.n_list + j) + (w.relative ? j : 0) : j);
+        c_row = w.c_row0 + (w.n_list ? __ldg(w.n_list + j) + ((w.flags & kItemRelative) ? j : 0) : j);
       }
       uint16_t* gdst = Ct + c_row * ldc + m0;
       ok = mbar_wait(smem_u32(&bars->acc_full[a]), aph, abort_flag);
@@ -418,39 +421,43 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       TS_TRACE(32, threadIdx.x == 192);
       TS_TRACE_U(3, acc_it, threadIdx.x == 192);
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + a * MT + half * kHalfCols + (static_cast<uint32_t>(q * 32) << 16);
+      const uint32_t taddr = tmem_base + a * MT + (static_cast<uint32_t>(q * 32) << 16);
       const bool has_acc = w.k_count > 0;
-      // TMEM reads are issued two chunks (64 columns) at a time and awaited once: a read's latency
-      // is far longer than the conversion of one chunk, so they must overlap each other.
+      // TMEM is read one 64-column group (two 32-column reads, one wait) at a time: a read's latency
+      // is far longer than the conversion of one chunk, so the two must overlap each other.
       constexpr int kBatch = 2;
 #pragma unroll
-      for (int c0 = 0; c0 < kChunks; c0 += kBatch) {
+      for (int gi = 0; gi < kGroups; ++gi) {
+        const int grp_col = (gi * 2 + half) * 64;        // first batch column of this thread's group
+        const bool grp_live = grp_col < m_cnt;           // uniform over the warp
         uint32_t v[kBatch][32];
-        if (has_acc) {
+        if (grp_live) {
+          if (has_acc) {
 #pragma unroll
-          for (int b = 0; b < kBatch; ++b) tmem_ld_32x32(taddr + (c0 + b) * 32, v[b]);
-          tmem_ld_wait();
-        } else {
+            for (int b = 0; b < kBatch; ++b) tmem_ld_32x32(taddr + grp_col + b * 32, v[b]);
+            tmem_ld_wait();
+          } else {
 #pragma unroll
-          for (int b = 0; b < kBatch; ++b)
+            for (int b = 0; b < kBatch; ++b)
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[b][e] = 0u;
+              for (int e = 0; e < 32; ++e) v[b][e] = 0u;
+          }
         }
-        if (c0 + kBatch == kChunks) {
+        if (gi == kGroups - 1) {
           // every TMEM read of this accumulator has completed: hand it back to the MMA warp
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bars->acc_empty[a]));
         }
-        if (c0 == 0) {
+        if (gi == 0) {
           // the staging tile is free once the previous unit's TMA store has read it (the leader
           // waits for that) and every thread has finished the previous copy-out
           if (leader) bulk_wait_read_all();
           named_barrier_sync(1, kEpiThreads);
         }
+        if (!grp_live) continue;
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
-          const int cc = c0 + b;                         // chunk inside this thread's half
-          const int col0 = half * kHalfCols + cc * 32;   // first batch column of the chunk
+          const int col0 = grp_col + b * 32;             // first batch column of the chunk
           uint32_t(&cur)[32] = v[b];
           uint32_t o[16];
           if (beta != 0.0f && active && (col0 < m_cnt)) {

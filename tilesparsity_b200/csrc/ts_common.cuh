@@ -43,9 +43,12 @@ struct TileDesc {
   int pad_;
 };
 
-// One unit of work of the persistent GEMM: one column tile x one block of batch rows.  Entries are
+// One unit of work of the persistent GEMM: one column tile x a run of batch rows.  Entries are
 // self-contained (they carry the tile's lists and counts) so a CTA reaches its first data request
 // with two dependent global reads: work item -> kept-row indices -> activation rows.
+//   flags bit 0: the index lists hold relative offsets (index - position)
+//   flags bit 1: the tile's kept columns are consecutive rows of Ct and fill a 128-row store box
+//   m_begin / m_len: the unit's batch rows; m_len is a multiple of 64, at most the kernel's MT
 struct alignas(16) WorkItem {
   const int* k_list;
   const int* n_list;
@@ -53,18 +56,21 @@ struct alignas(16) WorkItem {
   int n_count;
   int w_row0;
   int c_row0;
-  int relative;
-  int mblock;
+  int flags;
+  int m_begin;
+  int m_len;
   int tile;  // < 0: no unit
-  int pad_;  // != 0: the tile's kept columns are consecutive rows of Ct and fill a 128-row store box
 };
+constexpr int kItemRelative = 1;
+constexpr int kItemDenseRows = 2;
 static_assert(sizeof(WorkItem) == 48, "WorkItem is read as three 16-byte words");
 
 // One 64-row K block of a work unit, as the activation-gather warps consume it.  A CTA's blocks are
 // stored in processing order, so a gather warp addresses its descriptors by block number alone and
 // can request them, and the kept-row indices they point at, several blocks ahead.
-//   meta: bits 0-6 number of valid rows (1..64), bit 7 relative-offset lists, bits 8-31 position of
-//   the block's first row inside the tile's list; 0xFFFFFFFF marks the end of the CTA's stream.
+//   meta: bits 0-6 number of valid rows (1..64), bit 7 relative-offset lists, bits 8-9 the unit's
+//   batch rows in 64-row groups minus one, bits 10-31 position of the block's first row inside the
+//   tile's list; 0xFFFFFFFF marks the end of the CTA's stream.
 struct alignas(16) BlockDesc {
   const int* idx;  // the block's first kept-row index (tile list + position)
   int m0;          // first batch row of the unit
