@@ -167,14 +167,15 @@ int choose_unit_rows(int n_live_tiles, int M, int n_ctas) {
 }
 
 // Work distribution for the persistent kernel.  Units are (tile, run of batch rows); tiles are taken
-// in descending kept-K order and a tile's units are consecutive, so the CTAs that run at the same
-// time work on the same tile and the same kept rows of At (L2 and DRAM locality).  Full-width units
-// (`unit_rows` rows) fill as many complete waves of `n_ctas` units as there are; the rows that are
-// left would make a partial wave, so they are cut into narrower units (multiples of 64 rows) such
-// that every CTA gets at most one of them.  Assignment is longest-processing-time list scheduling.
+// in descending kept-K order and cut into units of `unit_rows` batch rows (the last unit of a tile
+// may be narrower, a multiple of 64 rows).  Assignment is longest-processing-time list scheduling.
+// Cutting the last, partial wave of units into narrower ones so that every SM gets a piece was
+// measured and dropped: narrow units keep fewer bytes in flight per SM and re-read the packed
+// weights more often, which cost as much as the better balance gained (BERT layer +-1 %, VGG conv5
+// shape -20 %).
 // Output: flat [rounds][grid] table; a CTA's units fill its column from round 0 without gaps,
 // tile = -1 marks the end.
-void build_schedule(const std::vector<ts::TileDesc>& tiles, int M, int unit_rows, int n_ctas,
+void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, int M, int unit_rows, int n_ctas,
                     std::vector<ts::WorkItem>* flat, int* rounds, int* grid, int* n_units,
                     std::vector<float>* cta_cost, std::vector<ts::BlockDesc>* blocks,
                     int* blk_stride) {
@@ -195,35 +196,28 @@ void build_schedule(const std::vector<ts::TileDesc>& tiles, int M, int unit_rows
   auto make = [&](int t, int g0, int glen) {
     return U{t, g0 * 64, glen * 64, unit_cost(tiles[t].k_count) * glen / static_cast<float>(gran_per_unit)};
   };
+  // Unit order = processing order.  While At fits in L2 the order is tile-major: the CTAs running at
+  // the same time work on one tile, i.e. on the same kept rows of At and the same packed weights.
+  // When At is much larger than L2 (K*M*2 bytes > 192 MiB) every tile's pass over At would come from
+  // HBM, so the tiles are taken in groups whose packed weights fit comfortably in L2 (32 MiB) and,
+  // inside a group, the batch blocks become the outer loop: concurrent CTAs then share one slab of
+  // At, whose rows are fetched from HBM once per group instead of once per tile.
+  const bool blocked = 2LL * at_rows * M > (192LL << 20);
+  long long wbytes = 0;
+  for (int t : order) wbytes += 2LL * tiles[t].k_count * 128;
+  const long long avg_tile = std::max<long long>(1, wbytes / std::max<size_t>(1, order.size()));
+  const int group = blocked ? static_cast<int>(std::max<long long>(8, std::min<long long>(order.size(), (32LL << 20) / avg_tile)))
+                            : 1;
   std::vector<U> units;
-  for (int t : order) {
-    for (int u = 0; u < full_per_tile; ++u) units.push_back(make(t, u * gran_per_unit, gran_per_unit));
-    if (tail_gran > 0) units.push_back(make(t, full_per_tile * gran_per_unit, tail_gran));
-  }
-  // the last partial wave of units is re-cut into narrower units
-  const int n_full_waves = static_cast<int>(units.size()) / std::max(1, n_ctas);
-  size_t keep = static_cast<size_t>(n_full_waves) * n_ctas;
-  if (keep < units.size() && n_ctas > 1) {
-    long long rest_gran = 0;
-    for (size_t i = keep; i < units.size(); ++i) rest_gran += units[i].m_len / 64;
-    int width = static_cast<int>((rest_gran + n_ctas - 1) / n_ctas);   // granules per narrow unit
-    width = std::max(1, std::min(width, gran_per_unit));
-    std::vector<U> rest(units.begin() + keep, units.end());
-    units.resize(keep);
-    // merge the left-over units into runs of consecutive rows of one tile, then cut every run
-    // into pieces of `width` granules
-    size_t i = 0;
-    while (i < rest.size()) {
-      const int t = rest[i].tile;
-      const int g_begin = rest[i].m_begin / 64;
-      int g_end = g_begin + rest[i].m_len / 64;
-      size_t k = i + 1;
-      while (k < rest.size() && rest[k].tile == t && rest[k].m_begin / 64 == g_end) {
-        g_end += rest[k].m_len / 64;
-        ++k;
+  const int blocks_per_tile = full_per_tile + (tail_gran > 0 ? 1 : 0);
+  for (size_t g0 = 0; g0 < order.size(); g0 += group) {
+    const size_t g1 = std::min(order.size(), g0 + group);
+    for (int u = 0; u < blocks_per_tile; ++u) {
+      for (size_t i = g0; i < g1; ++i) {
+        const int t = order[i];
+        if (u < full_per_tile) units.push_back(make(t, u * gran_per_unit, gran_per_unit));
+        else units.push_back(make(t, full_per_tile * gran_per_unit, tail_gran));
       }
-      for (int g0 = g_begin; g0 < g_end; g0 += width) units.push_back(make(t, g0, std::min(width, g_end - g0)));
-      i = k;
     }
   }
   *n_units = static_cast<int>(units.size());
@@ -365,7 +359,7 @@ int get_schedule(ts_layer* l, int M, Schedule** out) {
   int live = 0;
   for (int v : l->n_counts) live += v > 0;
   s.unit_rows = choose_unit_rows(live, M, l->sm_count);
-  build_schedule(l->h_tiles, M, s.unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
+  build_schedule(l->h_tiles, l->K, M, s.unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
                  &s.cta_cost, &blocks, &s.blk_stride);
   if (!flat.empty()) {
     TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkItem)));
@@ -745,7 +739,7 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   int rounds = 0, grid = 0, n_units = 0, live = 0, blk_stride = 0;
   for (int v : nc) live += v > 0;
   const int unit_rows = choose_unit_rows(live, M, sms);
-  build_schedule(td, M, unit_rows, sms, &flat, &rounds, &grid, &n_units, &cost, &blocks, &blk_stride);
+  build_schedule(td, K, M, unit_rows, sms, &flat, &rounds, &grid, &n_units, &cost, &blocks, &blk_stride);
   if (n_units == 0) return TS_OK;
   CUtensorMap tmap;
   rc = make_weight_tmap(&tmap, dtype, B, N, K);

@@ -1,0 +1,122 @@
+"""Sweep of the benchmark configurations: masked GEMM vs cuBLAS dense on one B200.
+
+    python -m tilesparsity_b200.sweep [--configs bert,vgg,lstm,square] [--iters 200]
+
+For every configuration the masks are built on the GPU from seeded synthetic weights (the reference's
+algorithms, tilesparsity_b200.masks), the layer is packed, and the tensor-core masked GEMM is timed
+from a CUDA graph next to `torch.matmul` (cuBLAS) on the same dense shapes, with activations and
+outputs rotating over enough buffers to exceed L2.  One JSON line per row.  Shapes and
+distributions stand in for the reference's models (BERT-base, VGG16 conv5, NMT LSTM), which are not
+available here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+import torch
+
+from . import synth
+from .layer import TEWLayer, TWLayer
+from .masks import build_mask
+from .tiles import tiles_from_lists
+
+L2_BYTES = 126 << 20
+
+
+def _time_graph(fn, n_sets: int, iters: int) -> float:
+    """Microseconds per call of fn(i), i cycling over n_sets buffer sets, replayed from a CUDA graph."""
+    for i in range(n_sets):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n_sets):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    reps = max(1, iters // n_sets)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * n_sets)
+
+
+def run_case(name, M, K, N, dtype, layer_fn, iters, note=""):
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(hash(name) % (2 ** 31))
+    W = torch.randn((K, N), generator=gen, device=dev, dtype=torch.float32) * 0.02
+    layer, kept_flops_per_row, extra = layer_fn(W)
+    per_set = (K * M + N * M) * 2
+    n_sets = int(max(2, min(8, (2 * L2_BYTES) // per_set + 1)))
+    At = [torch.randn((K, M), generator=gen, device=dev, dtype=torch.float32).to(dtype) for _ in range(n_sets)]
+    Ct = [torch.zeros((N, M), dtype=dtype, device=dev) for _ in range(n_sets)]
+    Wt = W.t().contiguous().to(dtype)
+    t_m = _time_graph(lambda i: layer.masked_gemm(At[i], out=Ct[i]), n_sets, iters)
+    t_d = _time_graph(lambda i: torch.matmul(Wt, At[i], out=Ct[i]), n_sets, iters)
+    kept = kept_flops_per_row * M
+    row = {"config": name, "M": M, "K": K, "N": N, "dtype": str(dtype).split(".")[-1], "masked_us": round(t_m, 2),
+           "cublas_dense_us": round(t_d, 2), "speedup_vs_cublas_dense": round(t_d / t_m, 3),
+           "kept_tflops": round(kept / t_m / 1e6, 1), "dense_tflops": round(2.0 * M * K * N / t_d / 1e6, 1),
+           "kept_fraction": round(kept / (2.0 * M * K * N), 4), "buffer_sets": n_sets, "note": note, **extra}
+    print(json.dumps(row), flush=True)
+    layer.close()
+    return row
+
+
+def tw_layer(sparsity, dtype, algo="tw1"):
+    def fn(W):
+        res = build_mask(algo, [W.abs()], sparsity, 128)
+        layer = TWLayer(res.tiles[0], dtype, W.device)
+        layer.pack(W)
+        return layer, res.tiles[0].kept_flops_per_row(), {"tiles": res.tiles[0].n_tiles}
+    return fn
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--configs", default="bert,vgg,lstm,square")
+    ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--sizes", default="4096,8192,16384")
+    a = ap.parse_args(argv)
+    want = set(a.configs.split(","))
+    rows = []
+    if "bert" in want:
+        for sp in (50.0, 75.0, 90.0):
+            for nm, (K, N) in synth.BERT_BASE_LAYER.items():
+                rows.append(run_case(f"bert_{nm}_tw{int(sp)}", 4096, K, N, torch.float16, tw_layer(sp, torch.float16), a.iters))
+    if "vgg" in want:
+        # conv5 as an implicit GEMM: tile-wise 75 % on K after 10 % column pruning.  The reference's
+        # tw2 ties both sparsities to one remapped value; the closest reference setting to (10 % columns,
+        # 75 % rows) is bert_type8-style independent stages, taken here as tw2 at the sparsity whose
+        # remap gives ~10 % per stage plus tw1-style row pruning is not expressible, so tw2 at 75 % is used.
+        rows.append(run_case("vgg16_conv5_tw2_75", 12544, 4608, 512, torch.bfloat16, tw_layer(75.0, torch.bfloat16, "tw2"),
+                             a.iters, "tw2 at 75 %: 50 % of columns x 50 % of rows per tile"))
+    if "lstm" in want:
+        def tew(W):
+            res = build_mask("tw1m", [W.abs()], 75.0, 128, 1.5, want_residual=True)
+            layer = TEWLayer(W, res.tiles[0], res.residuals[0], torch.float16)
+            return layer, res.tiles[0].kept_flops_per_row() + 2 * layer.nnz, {"residual_nnz": layer.nnz}
+        rows.append(run_case("nmt_lstm_tew_75_1.5", 6400, 2048, 4096, torch.float16, tew, a.iters))
+        rows.append(run_case("nmt_lstm_tw1_75", 6400, 2048, 4096, torch.float16, tw_layer(75.0, torch.float16), a.iters))
+    if "square" in want:
+        for n in [int(x) for x in a.sizes.split(",")]:
+            def sq(W, n=n):
+                nt = (n + 127) // 128
+                counts = synth.beta_skewed_counts(n, nt, 0.25, 5000 + int(np.log2(n)))
+                g = synth.rng(5000 + int(np.log2(n)))
+                lists = [np.sort(g.choice(n, size=int(c), replace=False)).astype(np.int32) for c in counts]
+                ts = tiles_from_lists(n, n, 128, lists)
+                layer = TWLayer(ts, torch.bfloat16, W.device)
+                layer.pack(W)
+                return layer, ts.kept_flops_per_row(), {"tiles": nt, "kept_k_min": int(counts.min()), "kept_k_max": int(counts.max())}
+            rows.append(run_case(f"square_{n}_beta25", n, n, n, torch.bfloat16, sq, max(20, a.iters // 4)))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
