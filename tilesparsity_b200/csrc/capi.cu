@@ -686,6 +686,10 @@ struct ShimWorkspace {
   size_t unit_cap = 0;
   ts::BlockDesc* d_blocks = nullptr;
   size_t block_cap = 0;
+  // The schedule of the previous call, reused when the next call describes the same tiles (a perf
+  // loop calls with identical arguments every iteration).
+  std::vector<long long> key;
+  int rounds = 0, grid = 0, blk_stride = 0, unit_rows = 0;
   int* d_status = nullptr;
 };
 std::mutex g_shim_mu;
@@ -733,14 +737,6 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   TS_CUDA(cudaGetDevice(&dev));
   int rc = current_sm_count(&sms);
   if (rc != TS_OK) return rc;
-  std::vector<ts::WorkItem> flat;
-  std::vector<float> cost;
-  std::vector<ts::BlockDesc> blocks;
-  int rounds = 0, grid = 0, n_units = 0, live = 0, blk_stride = 0;
-  for (int v : nc) live += v > 0;
-  const int unit_rows = choose_unit_rows(live, M, sms);
-  build_schedule(td, K, M, unit_rows, sms, &flat, &rounds, &grid, &n_units, &cost, &blocks, &blk_stride);
-  if (n_units == 0) return TS_OK;
   CUtensorMap tmap;
   rc = make_weight_tmap(&tmap, dtype, B, N, K);
   if (rc != TS_OK) return rc;
@@ -752,26 +748,48 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
     TS_CUDA(cudaMalloc(&ws.d_status, sizeof(int)));
     TS_CUDA(cudaMemset(ws.d_status, 0, sizeof(int)));
   }
-  if (flat.size() > ws.unit_cap) {
-    TS_CUDA(cudaStreamSynchronize(s));
-    cudaFree(ws.d_units);
-    ws.d_units = nullptr;
-    ws.unit_cap = 0;
-    TS_CUDA(cudaMalloc(&ws.d_units, flat.size() * sizeof(ts::WorkItem)));
-    ws.unit_cap = flat.size();
+  std::vector<long long> key = {M, N, K, block_num, dtype};
+  for (int t = 0; t < block_num; ++t) {
+    key.push_back(N_cal[t]);
+    key.push_back(K_cal[t]);
+    key.push_back(off_B[t]);
+    key.push_back(off_C[t]);
+    key.push_back(reinterpret_cast<long long>(mask_k[t]));
+    key.push_back(reinterpret_cast<long long>(mask_n[t]));
   }
-  if (blocks.size() > ws.block_cap) {
-    TS_CUDA(cudaStreamSynchronize(s));
-    cudaFree(ws.d_blocks);
-    ws.d_blocks = nullptr;
-    ws.block_cap = 0;
-    TS_CUDA(cudaMalloc(&ws.d_blocks, blocks.size() * sizeof(ts::BlockDesc)));
-    ws.block_cap = blocks.size();
+  if (key != ws.key) {
+    std::vector<ts::WorkItem> flat;
+    std::vector<float> cost;
+    std::vector<ts::BlockDesc> blocks;
+    int n_units = 0, live = 0;
+    for (int v : nc) live += v > 0;
+    ws.unit_rows = choose_unit_rows(live, M, sms);
+    build_schedule(td, K, M, ws.unit_rows, sms, &flat, &ws.rounds, &ws.grid, &n_units, &cost, &blocks, &ws.blk_stride);
+    ws.key.clear();
+    if (n_units == 0) return TS_OK;
+    if (flat.size() > ws.unit_cap) {
+      TS_CUDA(cudaStreamSynchronize(s));
+      cudaFree(ws.d_units);
+      ws.d_units = nullptr;
+      ws.unit_cap = 0;
+      TS_CUDA(cudaMalloc(&ws.d_units, flat.size() * sizeof(ts::WorkItem)));
+      ws.unit_cap = flat.size();
+    }
+    if (blocks.size() > ws.block_cap) {
+      TS_CUDA(cudaStreamSynchronize(s));
+      cudaFree(ws.d_blocks);
+      ws.d_blocks = nullptr;
+      ws.block_cap = 0;
+      TS_CUDA(cudaMalloc(&ws.d_blocks, blocks.size() * sizeof(ts::BlockDesc)));
+      ws.block_cap = blocks.size();
+    }
+    // Pageable sources: the runtime stages them before returning, so the vectors may die after this.
+    TS_CUDA(cudaMemcpyAsync(ws.d_units, flat.data(), flat.size() * sizeof(ts::WorkItem), cudaMemcpyHostToDevice, s));
+    TS_CUDA(cudaMemcpyAsync(ws.d_blocks, blocks.data(), blocks.size() * sizeof(ts::BlockDesc),
+                            cudaMemcpyHostToDevice, s));
+    ws.key = key;
   }
-  // Pageable sources: the runtime stages them before returning, so the vectors may die after this.
-  TS_CUDA(cudaMemcpyAsync(ws.d_units, flat.data(), flat.size() * sizeof(ts::WorkItem), cudaMemcpyHostToDevice, s));
-  TS_CUDA(cudaMemcpyAsync(ws.d_blocks, blocks.data(), blocks.size() * sizeof(ts::BlockDesc),
-                          cudaMemcpyHostToDevice, s));
+  const int rounds = ws.rounds, grid = ws.grid, blk_stride = ws.blk_stride, unit_rows = ws.unit_rows;
   CUtensorMap tmap_a;
   const int tr = tma_gather_rows();
   const bool tg = tr > 0;
