@@ -398,7 +398,8 @@ def run_square(args):
     """Tile-sharded strong-scaling run: M = N = K = --size, bf16, tile-wise 75 % with per-tile kept-row
     counts skewed ~Beta(2,5); the column tiles are sharded across the ranks by kept FLOPs
     (tilesparsity_b200.sharding), every rank holds At and computes its own slab of Ct; with
-    --gather the slabs are all-gathered over NCCL inside the timed region."""
+    --gather nccl the slabs are all-gathered over NCCL inside the timed region; with --gather fused the
+    GEMM's epilogue stores every kept row into all ranks' buffers (peer-mapped memory over NVLink)."""
     import torch
     import torch.distributed as dist
     from tilesparsity_b200 import sharding, synth
@@ -426,12 +427,16 @@ def run_square(args):
     n_sets = max(2, min(4, (3 * L2_BYTES) // (n * n * 2) + 1))
     At = [torch.randn((n, n), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16) for _ in range(n_sets)]
     Ct = [torch.zeros((shard.plan.n_pad, n), dtype=torch.bfloat16, device=device) for _ in range(n_sets)]
-    full = torch.empty((world * shard.plan.n_pad, n), dtype=torch.bfloat16, device=device) if args.gather else None
+    full = torch.empty((world * shard.plan.n_pad, n), dtype=torch.bfloat16, device=device) if args.gather == "nccl" else None
+    fused = shard.make_gather_buffer(n) if (args.gather == "fused" and world > 1) else None
 
     def step(i):
         s = i % n_sets
+        if fused is not None:
+            shard.masked_gemm_allgather(At[s], fused[0], fused[1])
+            return
         shard.masked_gemm(At[s], out=Ct[s])
-        if args.gather and world > 1:
+        if args.gather == "nccl" and world > 1:
             dist.all_gather_into_tensor(full, Ct[s])
 
     sampler = ClockSampler(local_rank)
@@ -450,7 +455,7 @@ def run_square(args):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": float(ms_t.item()) / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": f"square_{n}_tw75_g{G}_beta25", "gather": bool(args.gather),
+                "config": {"workload": f"square_{n}_tw75_g{G}_beta25", "gather": args.gather,
                            "parallelism": f"tile-sharded x{world}", "shard_balance": round(shard.plan.balance(), 4),
                            "l2": f"activations rotate over {n_sets} buffers of {n * n * 2 / 2**20:.0f} MiB"},
                 "tensor_frac_of_measured_peak": value / world / peaks["bf16_tflops_sustained"],
@@ -474,7 +479,9 @@ def main():
     ap.add_argument("--workload", choices=["bert", "square"], default="bert",
                     help="bert: the headline BERT-base layer step; square: tile-sharded M=N=K=--size strong scaling")
     ap.add_argument("--size", type=int, default=16384)
-    ap.add_argument("--gather", action="store_true", help="square workload: all-gather Ct inside the timed region")
+    ap.add_argument("--gather", choices=["none", "nccl", "fused"], default="none",
+                    help="square workload: all-gather Ct inside the timed region, with NCCL after the GEMM or "
+                         "by the GEMM's epilogue storing into the peers' buffers")
     args = ap.parse_args()
     if args.workload == "square" and args.impl == "ours":
         if args.steps == 2000:

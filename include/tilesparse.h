@@ -103,6 +103,30 @@ int ts_layer_stats(const ts_layer_t* layer, int64_t* kept_flops_per_row, int64_t
 int ts_masked_gemm(ts_layer_t* layer, int M, const void* At_dev, int64_t lda, void* Ct_dev,
                    int64_t ldc, float alpha, float beta, void* stream);
 
+/* Fused epilogue of ts_masked_gemm_ex:  Ct[n][m] = act(alpha * acc + beta * Ct[n][m] + bias[n]).
+ *   bias_dev     fp32 [N] on the device, indexed by the column of W (row of Ct), or NULL
+ *   activation   TS_ACT_NONE, TS_ACT_RELU, or TS_ACT_GELU (the tanh form of the reference's BERT,
+ *                Pruning/BERT/utils/modeling.py:264-277)
+ *   peer_ct      up to 7 further output buffers with the layout of Ct (same ldc): every kept row is also
+ *                stored there with plain stores.  Given the peer-mapped Ct buffers of the other GPUs
+ *                of a tile-sharded layer, the GEMM's epilogue performs the all-gather over NVLink.
+ * This is what the reference's mask_dense does after its matmul (bias add, modeling.py:1003-1007)
+ * folded into the GEMM; the reference has no multi-GPU path. */
+#define TS_ACT_NONE 0
+#define TS_ACT_RELU 1
+#define TS_ACT_GELU 2
+typedef struct ts_epilogue {
+  float alpha;
+  float beta;
+  const float* bias_dev;
+  int activation;
+  int n_peers;
+  void* peer_ct[7];
+} ts_epilogue_t;
+
+int ts_masked_gemm_ex(ts_layer_t* layer, int M, const void* At_dev, int64_t lda, void* Ct_dev,
+                      int64_t ldc, const ts_epilogue_t* epilogue, void* stream);
+
 /* Same operation on the CUDA cores in fp32 (the twin of the reference's CUDA_MODE build,
  * basic_nn.cu:55-71,239-246).  Cross-check path, not tuned. */
 int ts_masked_gemm_simt(ts_layer_t* layer, int M, const void* At_dev, int64_t lda, void* Ct_dev,

@@ -181,3 +181,33 @@ def test_tew_layer_matches_the_dense_masked_product(algo, shape, sparsity, g1):
     ref = og.masked_matmul_dense(At.float().cpu().numpy().T, Wd.half().float().cpu().numpy(), mask).T
     assert og.max_rel_error(out, ref) <= TOL
     layer.close()
+
+
+@pytest.mark.parametrize("act", [None, "relu", "gelu"])
+@pytest.mark.parametrize("col_keep", [None, 0.8])
+def test_fused_bias_and_activation(act, col_keep):
+    """y = act(x @ (W * mask) + bias): mask_dense's bias add (modeling.py:1003-1007) and the layer's
+    activation folded into the GEMM epilogue, on both store paths (TMA tile store / list-driven)."""
+    layer, At, A16, W16 = _case(384, 640, 520, 96, torch.float16, 77, col_keep=col_keep)
+    g = synth.rng(78)
+    bias = g.standard_normal(640).astype(np.float32)
+    ref = og.masked_matmul_compacted(A16, W16, layer.tiles) + bias[:, None]
+    if act == "relu":
+        ref = np.maximum(ref, 0)
+    elif act == "gelu":
+        ref = ref * 0.5 * (1.0 + np.tanh(np.sqrt(2 / np.pi) * (ref + 0.044715 * ref ** 3)))
+    kept = layer.tiles.col_mask()
+    out = layer.masked_gemm(At, bias=torch.from_numpy(bias).cuda(), activation=act).float().cpu().numpy()
+    assert og.max_rel_error(out[kept], ref[kept]) <= TOL
+    assert not out[~kept].any()
+    layer.close()
+
+
+def test_peer_copies_receive_the_same_rows():
+    """The epilogue's extra destinations (the all-gather of a sharded layer) on one GPU: two more
+    buffers must end up identical to the primary output."""
+    layer, At, A16, W16 = _case(256, 512, 520, 64, torch.bfloat16, 91, col_keep=0.7)
+    extra = [torch.zeros((512, 520), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    out = layer.masked_gemm(At, peers=[e.data_ptr() for e in extra])
+    assert torch.equal(extra[0], out) and torch.equal(extra[1], out)
+    layer.close()

@@ -37,6 +37,14 @@ def _load() -> C.CDLL:
 
 lib = _load()
 
+class Epilogue(C.Structure):
+    """ts_epilogue_t"""
+    _fields_ = [("alpha", C.c_float), ("beta", C.c_float), ("bias_dev", C.c_void_p), ("activation", C.c_int),
+                ("n_peers", C.c_int), ("peer_ct", C.c_void_p * 7)]
+
+
+ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "gelu": 2}
+
 _i32p = C.POINTER(C.c_int32)
 _i64p = C.POINTER(C.c_int64)
 _vp = C.c_void_p
@@ -52,6 +60,7 @@ SIGNATURES = {
     "ts_layer_get_packed": (C.c_int, [_vp, _vp, _i64p, _i64p]),
     "ts_layer_stats": (C.c_int, [_vp, _i64p, _i64p, _i64p, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "ts_masked_gemm": (C.c_int, [_vp, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.c_float, C.c_float, _vp]),
+    "ts_masked_gemm_ex": (C.c_int, [_vp, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.POINTER(Epilogue), _vp]),
     "ts_masked_gemm_simt": (C.c_int, [_vp, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.c_float, C.c_float, _vp]),
     "ts_masked_gemm_host": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_float, C.c_float, _vp]),
     "ts_layer_check": (C.c_int, [_vp, _vp]),

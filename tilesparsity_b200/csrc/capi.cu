@@ -578,10 +578,27 @@ int ts_layer_stats(const ts_layer_t* l, int64_t* kept_flops_per_row, int64_t* pa
   return TS_OK;
 }
 
-int ts_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
-                   float alpha, float beta, void* stream) {
+int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
+                      const ts_epilogue_t* epi, void* stream) {
   int rc = check_gemm_args(l, M, At, lda, Ct, ldc);
   if (rc != TS_OK) return rc;
+  if (!epi) return fail(TS_ERR_INVALID, "epilogue is NULL");
+  if (epi->activation < TS_ACT_NONE || epi->activation > TS_ACT_GELU) {
+    return fail(TS_ERR_INVALID, "unknown activation %d", epi->activation);
+  }
+  if (epi->n_peers < 0 || epi->n_peers > 7) return fail(TS_ERR_INVALID, "n_peers=%d out of [0, 7]", epi->n_peers);
+  ts::EpilogueArgs ep;
+  ep.alpha = epi->alpha;
+  ep.beta = epi->beta;
+  ep.bias = epi->bias_dev;
+  ep.act = epi->activation;
+  ep.n_peers = epi->n_peers;
+  for (int p = 0; p < 7; ++p) {
+    ep.peers[p] = p < epi->n_peers ? static_cast<uint16_t*>(epi->peer_ct[p]) : nullptr;
+    if (p < epi->n_peers && (!ep.peers[p] || (reinterpret_cast<uintptr_t>(ep.peers[p]) & 15u))) {
+      return fail(TS_ERR_INVALID, "peer buffer %d is NULL or not 16-byte aligned", p);
+    }
+  }
   if (M == 0 || l->n_tiles == 0) return TS_OK;
   Schedule* s = nullptr;
   rc = get_schedule(l, M, &s);
@@ -601,9 +618,18 @@ int ts_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, 
     if (rc != TS_OK) return rc;
   }
   TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, tr, l->tmap, tg ? &tmap_a : nullptr, tst ? &tmap_c : nullptr, l->K, s->d_units, s->rounds,
-                                 s->grid, s->d_blocks, s->blk_stride, At, lda, Ct, ldc, M, alpha, beta, l->d_status,
+                                 s->grid, s->d_blocks, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
                                  static_cast<cudaStream_t>(stream)));
   return TS_OK;
+}
+
+int ts_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
+                   float alpha, float beta, void* stream) {
+  ts_epilogue_t epi;
+  memset(&epi, 0, sizeof(epi));
+  epi.alpha = alpha;
+  epi.beta = beta;
+  return ts_masked_gemm_ex(l, M, At, lda, Ct, ldc, &epi, stream);
 }
 
 int ts_masked_gemm_simt(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
@@ -797,8 +823,12 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
     rc = make_act_tmap(&tmap_a, dtype, A, K, M, M);
     if (rc != TS_OK) return rc;
   }
+  ts::EpilogueArgs ep;
+  memset(&ep, 0, sizeof(ep));
+  ep.alpha = alpha;
+  ep.beta = beta;
   TS_CUDA(ts::masked_gemm_launch(dtype, unit_rows, tr, tmap, tg ? &tmap_a : nullptr, nullptr, K, ws.d_units, rounds, grid,
-                                 ws.d_blocks, blk_stride, A, M, C, M, M, alpha, beta, ws.d_status, s));
+                                 ws.d_blocks, blk_stride, A, M, C, M, M, ep, ws.d_status, s));
   return TS_OK;
 }
 

@@ -125,6 +125,21 @@ __device__ __forceinline__ WorkItem fetch_item(const WorkItem* sched, int rounds
 
 __device__ __forceinline__ int k_blocks(const WorkItem& w) { return (w.k_count + kKB - 1) / kKB; }
 
+// Ct row (global column of W) of tile column j of a work item.
+__device__ __forceinline__ long long c_row_of(const WorkItem& w, int j) {
+  return w.c_row0 + (w.n_list ? __ldg(w.n_list + j) + ((w.flags & kItemRelative) ? j : 0) : j);
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  if (act == kActRelu) return fmaxf(x, 0.0f);
+  if (act == kActGelu) {
+    // x * 0.5 * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))   (Pruning/BERT/utils/modeling.py:264-277)
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(u));
+  }
+  return x;
+}
+
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -136,8 +151,9 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
                    const WorkItem* __restrict__ sched,
                    int rounds, const BlockDesc* __restrict__ blocks, int blk_stride, int K_oob,
                    const uint16_t* __restrict__ At, long long lda,
-                   uint16_t* __restrict__ Ct, long long ldc, int M, float alpha, float beta,
+                   uint16_t* __restrict__ Ct, long long ldc, int M, const EpilogueArgs ep,
                    int* __restrict__ status) {
+  const float alpha = ep.alpha, beta = ep.beta;
   using C = Cfg<MT>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -410,11 +426,11 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const int m0 = w.m_begin;
       const int m_cnt = min(w.m_len, M - m0);
       const bool active = j < w.n_count;
-      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f;   // consecutive Ct rows
-      long long c_row = 0;
-      if (active) {
-        c_row = w.c_row0 + (w.n_list ? __ldg(w.n_list + j) + ((w.flags & kItemRelative) ? j : 0) : j);
-      }
+      // TMA store: consecutive Ct rows, nothing to read back, no peer copies
+      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f && ep.n_peers == 0;
+      const bool plain = beta == 0.0f && ep.bias == nullptr && ep.act == kActNone;
+      const long long c_row = active ? c_row_of(w, j) : 0;
+      const float bias_j = (ep.bias != nullptr && active) ? __ldg(ep.bias + c_row) : 0.0f;
       uint16_t* gdst = Ct + c_row * ldc + m0;
       ok = mbar_wait(smem_u32(&bars->acc_full[a]), aph, abort_flag);
       if (!ok) break;
@@ -460,32 +476,35 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           const int col0 = grp_col + b * 32;             // first batch column of the chunk
           uint32_t(&cur)[32] = v[b];
           uint32_t o[16];
-          if (beta != 0.0f && active && (col0 < m_cnt)) {
+          if (plain && alpha == 1.0f) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              o[e] = pack2<DT>(__uint_as_float(cur[2 * e]), __uint_as_float(cur[2 * e + 1]));
+            }
+          } else if (plain) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              o[e] = pack2<DT>(alpha * __uint_as_float(cur[2 * e]),
+                               alpha * __uint_as_float(cur[2 * e + 1]));
+            }
+          } else {
+            // general form: alpha * x + beta * Ct_old + bias, then the activation
+            const bool read_old = beta != 0.0f && active && (col0 < m_cnt);
             const uint4* cs = reinterpret_cast<const uint4*>(gdst + col0);
 #pragma unroll
             for (int e4 = 0; e4 < 4; ++e4) {
               uint4 old = make_uint4(0, 0, 0, 0);
-              if (col0 + e4 * 8 < m_cnt) old = cs[e4];
+              if (read_old && col0 + e4 * 8 < m_cnt) old = cs[e4];
               const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float c0f = unpack1<DT>(static_cast<uint16_t>(ow[e] & 0xffffu));
                 const float c1f = unpack1<DT>(static_cast<uint16_t>(ow[e] >> 16));
                 const int idx = e4 * 8 + e * 2;
-                o[e4 * 4 + e] = pack2<DT>(alpha * __uint_as_float(cur[idx]) + beta * c0f,
-                                          alpha * __uint_as_float(cur[idx + 1]) + beta * c1f);
+                const float y0 = alpha * __uint_as_float(cur[idx]) + beta * c0f + bias_j;
+                const float y1 = alpha * __uint_as_float(cur[idx + 1]) + beta * c1f + bias_j;
+                o[e4 * 4 + e] = pack2<DT>(apply_act(y0, ep.act), apply_act(y1, ep.act));
               }
-            }
-          } else if (alpha == 1.0f) {
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              o[e] = pack2<DT>(__uint_as_float(cur[2 * e]), __uint_as_float(cur[2 * e + 1]));
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              o[e] = pack2<DT>(alpha * __uint_as_float(cur[2 * e]),
-                               alpha * __uint_as_float(cur[2 * e + 1]));
             }
           }
           // staging: [64-column group][tile column j][128 bytes], 16-byte chunks swizzled by j & 7
@@ -536,7 +555,10 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             if (cr[e] >= 0 && m_ok) {
-              *reinterpret_cast<uint4*>(Ct + static_cast<long long>(cr[e]) * ldc + m0 + chunk * 8) = val[e];
+              const long long off = static_cast<long long>(cr[e]) * ldc + m0 + chunk * 8;
+              *reinterpret_cast<uint4*>(Ct + off) = val[e];
+              // tile-sharded layers: the same rows go to the other GPUs' copies of Ct over NVLink
+              for (int p = 0; p < ep.n_peers; ++p) *reinterpret_cast<uint4*>(ep.peers[p] + off) = val[e];
             }
           }
         }
@@ -562,7 +584,7 @@ cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
                            int use_tma_store, int K_oob,
                            const WorkItem* sched, int rounds, int grid,
                            const BlockDesc* blocks, int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
-                           float alpha, float beta, int* status, cudaStream_t stream) {
+                           const EpilogueArgs& ep, int* status, cudaStream_t stream) {
   // Programmatic dependent launch lets this kernel's set-up overlap the tail of the kernel before
   // it in the stream.  TS_PDL=0 turns it off.
   static const bool pdl = [] {
@@ -592,7 +614,7 @@ cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
   cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_a, tmap_c, use_tma_store, sched, rounds, blocks, blk_stride,
                             K_oob, static_cast<const uint16_t*>(At), lda, static_cast<uint16_t*>(Ct), ldc, M,
-                            alpha, beta, status);
+                            ep, status);
 }
 
 }  // namespace
@@ -601,13 +623,13 @@ cudaError_t masked_gemm_launch(int dtype, int unit_rows, int tma_rows, const CUt
                                const CUtensorMap* tmap_a, const CUtensorMap* tmap_c, int K_oob,
                                const WorkItem* sched, int rounds,
                                int grid, const BlockDesc* blocks, int blk_stride, const void* At,
-                               long long lda, void* Ct, long long ldc, int M, float alpha,
-                               float beta, int* status, cudaStream_t stream) {
+                               long long lda, void* Ct, long long ldc, int M, const EpilogueArgs& ep,
+                               int* status, cudaStream_t stream) {
   if (tma_rows > 0 && !tmap_a) return cudaErrorInvalidValue;
 #define TS_LAUNCH(DT, MT, TR)                                                                        \
   launch_variant<DT, MT, TR>(tmap_w, TR > 0 ? *tmap_a : tmap_w, tmap_c ? *tmap_c : tmap_w,            \
                              tmap_c ? 1 : 0, K_oob, sched, rounds, grid, blocks,                      \
-                             blk_stride, At, lda, Ct, ldc, M, alpha, beta, status, stream)
+                             blk_stride, At, lda, Ct, ldc, M, ep, status, stream)
 #define TS_BY_ROWS(DT, MT)                      \
   switch (tma_rows) {                           \
     case 0: return TS_LAUNCH(DT, MT, 0);        \

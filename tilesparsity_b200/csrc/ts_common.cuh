@@ -65,6 +65,20 @@ constexpr int kItemRelative = 1;
 constexpr int kItemDenseRows = 2;
 static_assert(sizeof(WorkItem) == 48, "WorkItem is read as three 16-byte words");
 
+// What the GEMM epilogue does with an accumulator value x of tile column n before it is stored:
+//     y = act(alpha * x + beta * Ct_old + bias[n])
+// and where the result goes besides Ct: up to 7 peer buffers with the same layout (other GPUs'
+// copies of Ct, written with plain stores over NVLink: the all-gather of a tile-sharded layer).
+enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
+struct EpilogueArgs {
+  float alpha;
+  float beta;
+  const float* bias;   // indexed by Ct row (global column of W), or nullptr
+  int act;
+  int n_peers;
+  uint16_t* peers[7];
+};
+
 // One 64-row K block of a work unit, as the activation-gather warps consume it.  A CTA's blocks are
 // stored in processing order, so a gather warp addresses its descriptors by block number alone and
 // can request them, and the kept-row indices they point at, several blocks ahead.

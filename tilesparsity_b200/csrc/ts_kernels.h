@@ -24,8 +24,8 @@ cudaError_t masked_gemm_launch(int dtype, int unit_rows, int tma_rows, const CUt
                                const CUtensorMap* tmap_a, const CUtensorMap* tmap_c, int K_oob,
                                const WorkItem* sched, int rounds,
                                int grid, const BlockDesc* blocks, int blk_stride, const void* At,
-                               long long lda, void* Ct, long long ldc, int M, float alpha,
-                               float beta, int* status, cudaStream_t stream);
+                               long long lda, void* Ct, long long ldc, int M, const EpilogueArgs& ep,
+                               int* status, cudaStream_t stream);
 
 #ifdef TS_KERNEL_TRACE
 cudaError_t masked_gemm_read_trace(long long* out64, bool clear);

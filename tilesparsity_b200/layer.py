@@ -129,11 +129,14 @@ class TWLayer:
 
     # ------------------------------------------------------------------ compute
     def masked_gemm(self, At: torch.Tensor, out: torch.Tensor | None = None, alpha: float = 1.0,
-                    beta: float = 0.0, simt: bool = False) -> torch.Tensor:
-        """Ct[N, M] = alpha * (W .* mask)^T @ At[K, M] + beta * Ct, kept columns only.
+                    beta: float = 0.0, simt: bool = False, bias: torch.Tensor | None = None,
+                    activation: str | None = None, peers=None) -> torch.Tensor:
+        """Ct[N, M] = act(alpha * (W .* mask)^T @ At[K, M] + beta * Ct + bias[:, None]), kept columns only.
 
         At is the reference's activation layout: [K, M] with M contiguous.  Without `out` a zeroed
-        [N, M] tensor is allocated, so pruned columns read as zero.
+        [N, M] tensor is allocated, so pruned columns read as zero.  bias is fp32 [N]; activation is
+        None, "relu" or "gelu"; peers are raw device addresses of further [N, M] buffers (same row
+        pitch as `out`) that receive the same rows, e.g. the other GPUs' copies of a sharded output.
         """
         if At.dim() != 2 or At.shape[0] != self.K or At.dtype != self.dtype or At.device != self.device:
             raise ValueError(f"At must be a [{self.K}, M] {self.dtype} tensor on {self.device}")
@@ -144,10 +147,31 @@ class TWLayer:
             out = torch.zeros((self.N, M), dtype=self.dtype, device=self.device)
         if tuple(out.shape) != (self.N, M) or out.dtype != self.dtype or out.stride(1) != 1 or out.device != self.device:
             raise ValueError(f"out must be a [{self.N}, {M}] {self.dtype} tensor with M contiguous")
-        fn = lib.ts_masked_gemm_simt if simt else lib.ts_masked_gemm
         with torch.cuda.device(self.device):
-            check(fn(self._h, M, C.c_void_p(At.data_ptr()), At.stride(0), C.c_void_p(out.data_ptr()),
-                     out.stride(0), alpha, beta, _stream_ptr(self.device)))
+            if simt:
+                if bias is not None or activation or peers:
+                    raise ValueError("the CUDA-core twin has no fused epilogue")
+                check(lib.ts_masked_gemm_simt(self._h, M, C.c_void_p(At.data_ptr()), At.stride(0),
+                                              C.c_void_p(out.data_ptr()), out.stride(0), alpha, beta,
+                                              _stream_ptr(self.device)))
+                return out
+            ep = _lib.Epilogue()
+            ep.alpha, ep.beta = alpha, beta
+            if bias is not None:
+                if bias.dtype != torch.float32 or bias.numel() != self.N or bias.device != self.device or not bias.is_contiguous():
+                    raise ValueError(f"bias must be a contiguous fp32 [{self.N}] tensor on {self.device}")
+                ep.bias_dev = bias.data_ptr()
+            if activation not in _lib.ACTIVATIONS:
+                raise ValueError(f"unknown activation {activation!r}")
+            ep.activation = _lib.ACTIVATIONS[activation]
+            peers = list(peers or [])
+            if len(peers) > 7:
+                raise ValueError("at most 7 peer buffers")
+            ep.n_peers = len(peers)
+            for i, p in enumerate(peers):
+                ep.peer_ct[i] = int(p)
+            check(lib.ts_masked_gemm_ex(self._h, M, C.c_void_p(At.data_ptr()), At.stride(0), C.c_void_p(out.data_ptr()),
+                                        out.stride(0), C.byref(ep), _stream_ptr(self.device)))
         return out
 
     def masked_gemm_host(self, At_host: torch.Tensor, Ct_host: torch.Tensor, alpha: float = 1.0,

@@ -120,6 +120,39 @@ class ShardedTWLayer:
         dist.all_gather_into_tensor(out, Ct_local.contiguous())
         return out
 
+    # ------------------------------------------------------------------ fused GEMM + all-gather
+    def make_gather_buffer(self, M: int, group=None):
+        """Allocates the gathered output [world * n_pad, M] in peer-mapped (symmetric) memory and
+        exchanges the mappings.  Collective: every rank of `group` must call it.  Returns
+        (buffer, handle); keep both alive while the buffer is in use."""
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        buf = symm_mem.empty((self.world * self.plan.n_pad, M), dtype=self.layer.dtype, device=self.layer.device)
+        buf.zero_()
+        handle = symm_mem.rendezvous(buf, group)
+        torch.cuda.current_stream(self.layer.device).synchronize()
+        handle.barrier()
+        return buf, handle
+
+    def masked_gemm_allgather(self, At, buf, handle):
+        """One kernel computes this rank's slab and stores every kept row into all ranks' gathered
+        buffers (plain stores to peer-mapped memory: the transfer over NVLink overlaps the tiles still
+        being computed).  The barriers around it are the only other communication: peers must have
+        finished with the buffer's previous contents before it is overwritten, and every rank's
+        stores must have landed before anyone reads it."""
+        import torch
+        row0 = self.rank * self.plan.n_pad
+        n_loc = self.local.N
+        pitch = buf.stride(0) * buf.element_size()
+        peers = [int(handle.buffer_ptrs[p]) + row0 * pitch for p in range(self.world) if p != self.rank]
+        handle.barrier()
+        self.layer.masked_gemm(At, out=buf[row0:row0 + n_loc], peers=peers)
+        torch.cuda.current_stream(self.layer.device).synchronize()
+        handle.barrier()
+        return buf
+
     def assemble(self, gathered):
         """Full Ct[N, M] in the original column order (pruned columns zero).  A consumer that can
         take the permuted rows should use `self.order` instead of paying for this copy."""
