@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstring>
 #include <limits>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -38,21 +39,58 @@ namespace {
     if (rc_ != TS_OK) return rc_; \
   } while (0)
 
-// Device allocations of one call, released together.
+// Device scratch of one call: carved out of a block that is kept between calls (one per device, grown
+// on demand), so a mask build in steady state makes no cudaMalloc / cudaFree calls (each of which
+// would synchronise the device).  Calls on one device take turns: the lock is held for the whole
+// call.  If a call needs more than the block holds, the extra allocations are individual and freed
+// at the end of the call, and the block is replaced by a larger one for the next call.
+struct ScratchBlock {
+  void* base = nullptr;
+  size_t cap = 0;
+  std::mutex mu;
+};
+ScratchBlock g_scratch[64];
+
 struct Arena {
-  std::vector<void*> ptrs;
+  ScratchBlock* blk = nullptr;
+  size_t used = 0, wanted = 0;
+  std::vector<void*> extra;
+  std::unique_lock<std::mutex> lock;
+
+  Arena() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+      blk = &g_scratch[dev];
+      lock = std::unique_lock<std::mutex>(blk->mu);
+    }
+  }
   ~Arena() {
-    for (void* p : ptrs) cudaFree(p);
+    for (void* p : extra) cudaFree(p);
+    if (blk && wanted > blk->cap) {   // grow the kept block for the next call
+      cudaFree(blk->base);
+      blk->base = nullptr;
+      blk->cap = 0;
+      const size_t want = wanted + wanted / 4 + (1 << 20);
+      if (cudaMalloc(&blk->base, want) == cudaSuccess) blk->cap = want;
+      else cudaGetLastError();
+    }
   }
   template <typename T>
   int alloc(T** out, size_t count) {
-    void* p = nullptr;
-    cudaError_t e = cudaMalloc(&p, std::max<size_t>(count, 1) * sizeof(T));
-    if (e != cudaSuccess) {
-      return ts_internal_fail(TS_ERR_NOMEM, "device allocation of %zu bytes failed: %s",
-                              count * sizeof(T), cudaGetErrorString(e));
+    const size_t bytes = (std::max<size_t>(count, 1) * sizeof(T) + 255) & ~static_cast<size_t>(255);
+    wanted += bytes;
+    if (blk && blk->base && used + bytes <= blk->cap) {
+      *out = reinterpret_cast<T*>(static_cast<char*>(blk->base) + used);
+      used += bytes;
+      return TS_OK;
     }
-    ptrs.push_back(p);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+      return ts_internal_fail(TS_ERR_NOMEM, "device allocation of %zu bytes failed: %s", bytes,
+                              cudaGetErrorString(e));
+    }
+    extra.push_back(p);
     *out = static_cast<T*>(p);
     return TS_OK;
   }
@@ -259,9 +297,13 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
     if (sel == 2) {
       TSM_CUDA(ts::tile_row_l1_launch(L[l].score, L[l].ld, L[l].K, bounds_dev[l], nt, norms + off[l], s));
     } else {
+      int uniform = 0;   // leading tiles that are exactly [128 t, 128 (t+1))
+      if (colkeep_dev.empty()) {
+        while (uniform < nt && bounds[l][uniform] == 128 * uniform && bounds[l][uniform + 1] == 128 * (uniform + 1)) ++uniform;
+      }
       TSM_CUDA(ts::tile_row_norms_launch(L[l].score, L[l].ld, L[l].K, bounds_dev[l], nt,
                                          colkeep_dev.empty() ? nullptr : colkeep_dev[l], norms + off[l],
-                                         sel == 0 ? 1 : 0, s));
+                                         sel == 0 ? 1 : 0, uniform, s));
     }
   }
   if (sel == 0) {
@@ -632,7 +674,8 @@ int ts_tw1_row_keep_noalloc(const float* score_dev, int64_t ld, int K, int N, in
   bounds[n_tiles] = N;
   TSM_CUDA(cudaMemcpyAsync(sc->bounds, bounds, (n_tiles + 1) * sizeof(int), cudaMemcpyHostToDevice, s));
   TSM_CUDA(cudaStreamSynchronize(s));  // `bounds` lives on this stack frame
-  TSM_CUDA(ts::tile_row_norms_launch(score_dev, ld, K, sc->bounds, static_cast<int>(n_tiles), nullptr, sc->norms, 1, s));
+  TSM_CUDA(ts::tile_row_norms_launch(score_dev, ld, K, sc->bounds, static_cast<int>(n_tiles), nullptr, sc->norms, 1,
+                                     G == 128 ? N / 128 : 0, s));
   const Ranks r = percentile_ranks(total, sparsity, sparsity_is_f64 != 0);
   float a = 0, b = 0;
   // order_statistics clears the histogram before every digit pass and the two counters before use

@@ -86,6 +86,53 @@ tile_row_norms_kernel(const float* __restrict__ score, long long ld, int K,
   if (k < K && j == 0) norms[static_cast<long long>(t) * K + k] = v;
 }
 
+// Fast path of the row norms for tiles that are exactly 128 columns wide and carry no column mask
+// (every tile of tw1 when N is a multiple of 128): a block stages 32 rows x 128 columns through
+// shared memory with fully coalesced 16-byte loads, then the same 8-lane groups reduce them in
+// NumPy's order (leaf of 128 elements: eight running sums, tree, no leftovers).
+// grid: (ceil(K / 32), n_tiles_128), block 256.
+__global__ void __launch_bounds__(256)
+tile_row_norms128_kernel(const float* __restrict__ score, long long ld, int K,
+                         float* __restrict__ norms, int divide) {
+  constexpr int kPitch = 136;   // floats per staged row: rows 8 banks apart, 16-byte aligned
+  __shared__ __align__(16) float tile[32 * kPitch];
+  const int t = blockIdx.y;
+  const int k0 = blockIdx.x * 32;
+  const float* base = score + static_cast<long long>(t) * 128;
+  const bool vec_ok = (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(score) & 15u) == 0);
+  for (int v = threadIdx.x; v < 32 * 32; v += 256) {   // 32 rows x 32 float4
+    const int r = v >> 5, c4 = v & 31;
+    const int k = k0 + r;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < K) {
+      const float* p = base + static_cast<long long>(k) * ld + c4 * 4;
+      if (vec_ok) {
+        x = __ldg(reinterpret_cast<const float4*>(p));
+      } else {
+        x = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+      }
+    }
+    *reinterpret_cast<float4*>(&tile[r * kPitch + c4 * 4]) = x;
+  }
+  __syncthreads();
+  const int group = threadIdx.x >> 3, j = threadIdx.x & 7;
+  const float* row = &tile[group * kPitch];
+  float x = row[j];
+  float r = __fmul_rn(x, x);
+#pragma unroll
+  for (int i = 8; i < 128; i += 8) {
+    x = row[i + j];
+    r = __fadd_rn(r, __fmul_rn(x, x));
+  }
+  r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 1));
+  r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 2));
+  r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 4));
+  float v = __fsqrt_rn(r);
+  if (divide) v = __fdiv_rn(v, 128.0f);
+  const int k = k0 + group;
+  if (k < K && j == 0) norms[static_cast<long long>(t) * K + k] = v;
+}
+
 // l1[t*K + k] = sum_c |score[k, c]| over the tile's columns, left to right.
 __global__ void __launch_bounds__(256)
 tile_row_l1_kernel(const float* __restrict__ score, long long ld, int K,
@@ -101,18 +148,64 @@ tile_row_l1_kernel(const float* __restrict__ score, long long ld, int K,
 }
 
 // out[n] = sqrt(sum_k score[k][n]^2 in row order) / K
-__global__ void __launch_bounds__(128)
+//
+// The sum of one column is a chain of K dependent additions (NumPy reduces axis 0 row by row), so
+// the only parallelism is across columns.  A block owns kColsPerBlock columns: all 256 threads fetch
+// the next kColRows x kColsPerBlock slab (global loads in flight) while the first kColsPerBlock
+// threads walk the previous slab in shared memory, so the chain waits on shared memory, never on DRAM.
+constexpr int kColsPerBlock = 16;
+constexpr int kColRows = 128;
+constexpr int kColPerThread = kColsPerBlock * kColRows / 256;  // 8
+
+__global__ void __launch_bounds__(256)
 col_norms_kernel(const float* __restrict__ score, long long ld, int K, int N,
                  float* __restrict__ out) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  if (n >= N) return;
-  float x = __ldg(score + n);
-  float acc = __fmul_rn(x, x);
-  for (int k = 1; k < K; ++k) {
-    x = __ldg(score + static_cast<long long>(k) * ld + n);
-    acc = __fadd_rn(acc, __fmul_rn(x, x));
+  __shared__ float slab[2][kColRows][kColsPerBlock];
+  const int n0 = blockIdx.x * kColsPerBlock;
+  const int tid = threadIdx.x;
+  const int lc = tid % kColsPerBlock;       // column inside the slab
+  const int lr = tid / kColsPerBlock;       // first row this thread fetches (stride 16 rows)
+  const bool col_ok = n0 + lc < N;
+  float reg[kColPerThread];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < kColPerThread; ++i) {
+      const int k = k0 + lr + i * (256 / kColsPerBlock);
+      reg[i] = (col_ok && k < K) ? __ldg(score + static_cast<long long>(k) * ld + n0 + lc) : 0.0f;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < kColPerThread; ++i) slab[buf][lr + i * (256 / kColsPerBlock)][lc] = reg[i];
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  float acc = 0.0f;
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += kColRows) {
+    const bool more = k0 + kColRows < K;
+    if (more) fetch(k0 + kColRows);
+    if (tid < kColsPerBlock) {
+      const int rows = min(kColRows, K - k0);
+      int r = 0;
+      if (k0 == 0) {
+        const float x = slab[buf][0][tid];
+        acc = __fmul_rn(x, x);
+        r = 1;
+      }
+#pragma unroll 8
+      for (; r < rows; ++r) {
+        const float x = slab[buf][r][tid];
+        acc = __fadd_rn(acc, __fmul_rn(x, x));
+      }
+    }
+    if (more) stash(buf ^ 1);
+    __syncthreads();
+    buf ^= 1;
   }
-  out[n] = __fdiv_rn(__fsqrt_rn(acc), static_cast<float>(K));
+  if (tid < kColsPerBlock && n0 + tid < N)
+    out[n0 + tid] = __fdiv_rn(__fsqrt_rn(acc), static_cast<float>(K));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -231,6 +324,55 @@ dense_mask_kernel(const uint8_t* __restrict__ rowkeep, const uint8_t* __restrict
   mask[static_cast<long long>(k) * ld_mask + n] = m;
 }
 
+// Same result, 16 mask bytes per thread and kDenseRows rows per block: needs N, ld_mask and the
+// mask pointer to be multiples of 16.  The column flags and tile ids of a thread's 16 columns are
+// read once and reused for every row; one row-keep byte serves the whole run when the 16 columns
+// share a tile.
+constexpr int kDenseRows = 16;
+
+__global__ void __launch_bounds__(256)
+dense_mask16_kernel(const uint8_t* __restrict__ rowkeep, const uint8_t* __restrict__ colkeep,
+                    const int* __restrict__ tile_of_col, int K, int N, uint8_t* __restrict__ mask,
+                    long long ld_mask) {
+  const int n0 = (blockIdx.x * blockDim.x + threadIdx.x) * 16;
+  if (n0 >= N) return;
+  int tile[16];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int4 v = *reinterpret_cast<const int4*>(tile_of_col + n0 + q * 4);
+    tile[q * 4 + 0] = v.x; tile[q * 4 + 1] = v.y; tile[q * 4 + 2] = v.z; tile[q * 4 + 3] = v.w;
+  }
+  bool same = true;
+#pragma unroll
+  for (int j = 1; j < 16; ++j) same &= tile[j] == tile[0];
+  uint32_t cmask[4] = {0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u};
+  if (colkeep) {
+    const uint4 c = *reinterpret_cast<const uint4*>(colkeep + n0);
+    cmask[0] = c.x; cmask[1] = c.y; cmask[2] = c.z; cmask[3] = c.w;
+  }
+  const int k_begin = blockIdx.y * kDenseRows;
+  const int k_end = min(K, k_begin + kDenseRows);
+  for (int k = k_begin; k < k_end; ++k) {
+    uint32_t w[4];
+    if (same) {
+      const uint32_t b = rowkeep[static_cast<long long>(tile[0]) * K + k] * 0x01010101u;
+      w[0] = w[1] = w[2] = w[3] = b;
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t x = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          x |= static_cast<uint32_t>(rowkeep[static_cast<long long>(tile[q * 4 + j]) * K + k]) << (8 * j);
+        w[q] = x;
+      }
+    }
+    uint4 o;
+    o.x = w[0] & cmask[0]; o.y = w[1] & cmask[1]; o.z = w[2] & cmask[2]; o.w = w[3] & cmask[3];
+    *reinterpret_cast<uint4*>(mask + static_cast<long long>(k) * ld_mask + n0) = o;
+  }
+}
+
 // TEW ranking values: v[k*N + n] = sqrt(w*w) - mask[k][n]   (prune_algo.py:156-159)
 __global__ void __launch_bounds__(256)
 tew_values_kernel(const float* __restrict__ score, long long ld, const uint8_t* __restrict__ mask,
@@ -311,10 +453,21 @@ int stream_grid(long long n) {
 
 cudaError_t tile_row_norms_launch(const float* score, long long ld, int K, const int* bounds_dev,
                                   int n_tiles, const uint8_t* colmask, float* norms, int divide,
-                                  cudaStream_t s) {
+                                  int n_uniform128, cudaStream_t s) {
   if (K <= 0 || n_tiles <= 0) return cudaSuccess;
-  dim3 grid((K + 31) / 32, n_tiles);
-  tile_row_norms_kernel<<<grid, 256, 0, s>>>(score, ld, K, bounds_dev, colmask, norms, divide);
+  // the first n_uniform128 tiles are known to be the fixed tiles [128 t, 128 (t+1)) without a
+  // column mask: they take the staged fast path, the others the general kernel
+  int first = 0;
+  if (!colmask && n_uniform128 > 0) {
+    first = n_uniform128 < n_tiles ? n_uniform128 : n_tiles;
+    dim3 grid((K + 31) / 32, first);
+    tile_row_norms128_kernel<<<grid, 256, 0, s>>>(score, ld, K, norms, divide);
+  }
+  if (first < n_tiles) {
+    dim3 grid((K + 31) / 32, n_tiles - first);
+    tile_row_norms_kernel<<<grid, 256, 0, s>>>(score, ld, K, bounds_dev + first, colmask,
+                                               norms + static_cast<long long>(first) * K, divide);
+  }
   return cudaGetLastError();
 }
 
@@ -329,7 +482,7 @@ cudaError_t tile_row_l1_launch(const float* score, long long ld, int K, const in
 cudaError_t col_norms_launch(const float* score, long long ld, int K, int N, float* out,
                              cudaStream_t s) {
   if (K <= 0 || N <= 0) return cudaSuccess;
-  col_norms_kernel<<<(N + 127) / 128, 128, 0, s>>>(score, ld, K, N, out);
+  col_norms_kernel<<<(N + kColsPerBlock - 1) / kColsPerBlock, 256, 0, s>>>(score, ld, K, N, out);
   return cudaGetLastError();
 }
 
@@ -370,6 +523,15 @@ cudaError_t segment_compact_launch(const uint8_t* keep, const long long* seg_ptr
 cudaError_t dense_mask_launch(const uint8_t* rowkeep, const uint8_t* colkeep, const int* tile_of_col,
                               int K, int N, uint8_t* mask, long long ld_mask, cudaStream_t s) {
   if (K <= 0 || N <= 0) return cudaSuccess;
+  const bool aligned = N % 16 == 0 && ld_mask % 16 == 0 && reinterpret_cast<uintptr_t>(mask) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(tile_of_col) % 16 == 0 &&
+                       (!colkeep || reinterpret_cast<uintptr_t>(colkeep) % 16 == 0);
+  if (aligned) {
+    const int threads = N / 16 >= 128 ? 128 : 64;
+    dim3 grid16((N / 16 + threads - 1) / threads, (K + kDenseRows - 1) / kDenseRows);
+    dense_mask16_kernel<<<grid16, threads, 0, s>>>(rowkeep, colkeep, tile_of_col, K, N, mask, ld_mask);
+    return cudaGetLastError();
+  }
   dim3 grid((N + 255) / 256, K);
   dense_mask_kernel<<<grid, 256, 0, s>>>(rowkeep, colkeep, tile_of_col, K, N, mask, ld_mask);
   return cudaGetLastError();

@@ -7,10 +7,11 @@
 namespace ts {
 
 // norms[t*K + k] = ||score[k, bounds[t]:bounds[t+1]] (.* colmask)||_2, divided by the tile width
-// when `divide` is set.  bounds_dev holds n_tiles+1 column indices on the device.
+// when `divide` is set.  bounds_dev holds n_tiles+1 column indices on the device.  n_uniform128 > 0
+// promises that the first n_uniform128 tiles are the fixed tiles [128 t, 128 (t+1)).
 cudaError_t tile_row_norms_launch(const float* score, long long ld, int K, const int* bounds_dev,
                                   int n_tiles, const uint8_t* colmask, float* norms, int divide,
-                                  cudaStream_t s);
+                                  int n_uniform128, cudaStream_t s);
 // out[t*K + k] = sum of |score[k, c]| over the tile's columns, left to right.
 cudaError_t tile_row_l1_launch(const float* score, long long ld, int K, const int* bounds_dev,
                                int n_tiles, float* out, cudaStream_t s);

@@ -77,6 +77,28 @@ def tw_layer(sparsity, dtype, algo="tw1"):
     return fn
 
 
+def run_mask_case(algo, K, N, sparsity, g1=None, reps=5):
+    """Wall-clock of the host-synchronous mask build (scores resident on the GPU) and its HBM-level
+    bytes: the scores read once per norm pass plus the dense 0/1 mask written."""
+    import time
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(K * 31 + N)
+    W = (torch.randn((K, N), generator=gen, device=dev, dtype=torch.float32) * 0.02).abs()
+    build_mask(algo, [W], sparsity, 128, g1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        res = build_mask(algo, [W], sparsity, 128, g1)
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / reps
+    passes = {"tw1": 1, "tw2": 2, "tw1m": 2, "tw2m": 3}[algo]
+    nbytes = K * N * (4 * passes + 1)
+    row = {"config": f"mask_{algo}_{K}x{N}", "K": K, "N": N, "sparsity": sparsity, "seconds": round(dt, 6),
+           "bytes": nbytes, "gbs": round(nbytes / dt / 1e9, 1), "density": round(float(res.masks[0].float().mean()), 4)}
+    print(json.dumps(row), flush=True)
+    return row
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--configs", default="bert,vgg,lstm,square")
@@ -85,6 +107,11 @@ def main(argv=None):
     a = ap.parse_args(argv)
     want = set(a.configs.split(","))
     rows = []
+    if "masks" in want:
+        for algo, K, N, sp, g1 in [("tw1", 768, 3072, 75.0, None), ("tw1", 2048, 4096, 75.0, None),
+                                    ("tw1", 8192, 8192, 75.0, None), ("tw2", 4608, 512, 75.0, None),
+                                    ("tw2", 8192, 8192, 75.0, None), ("tw1m", 2048, 4096, 75.0, 1.5)]:
+            rows.append(run_mask_case(algo, K, N, sp, g1))
     if "bert" in want:
         for sp in (50.0, 75.0, 90.0):
             for nm, (K, N) in synth.BERT_BASE_LAYER.items():
