@@ -84,24 +84,6 @@ int make_weight_tmap(CUtensorMap* map, int dtype, const void* base, long long ro
   return TS_OK;
 }
 
-// Tensor map over the activations At [K][lda] (16-bit, batch contiguous) for the TMA row gather:
-// box 64 batch columns x 1 row, 128-byte swizzle, zero fill outside the matrix.
-int make_act_tmap(CUtensorMap* map, int dtype, const void* At, long long K, long long M, long long lda) {
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(K)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(lda) * 2};
-  cuuint32_t box[2] = {64, 1};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, dtype == TS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                  2, const_cast<void*>(At), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled (activations) failed (%d)", (int)r);
-  return TS_OK;
-}
-
 // Tensor map over the output Ct [n_rows][ldc] for the epilogue's TMA stores: box 64 batch columns x 128
 // rows, 128-byte swizzle.
 int make_out_tmap(CUtensorMap* map, int dtype, const void* Ct, long long n_rows, long long M, long long ldc) {
@@ -126,22 +108,10 @@ bool use_tma_store() {
   return !(e && strcmp(e, "lsu") == 0);
 }
 
-// Rows of every 64-row K block that the copy engine gathers (tile::gather4): none by default, the
-// rows go through 16-byte cp.async copies.  Measured on B200 the cp.async gather delivers more bytes
-// per second (BERT layer 1.09x vs 1.03x cuBLAS dense, 8192^3 at 75 %: 800 vs 670 kept TFLOP/s), and
-// splitting a block between the two paths is slower than cp.async alone.  TS_TMA_ROWS=64 selects
-// the TMA gather.
-int tma_gather_rows() {
-  if (const char* e = getenv("TS_TMA_ROWS")) {
-    const int v = atoi(e);
-    if (v == 0 || v == 64) return v;
-  }
-  return 0;
-}
-
 struct Schedule {
   ts::WorkItem* d_units = nullptr;
   ts::BlockDesc* d_blocks = nullptr;
+  int* d_meta = nullptr;       // one resolved record (ts::kBlockMetaInts ints) per descriptor of d_blocks
   int blk_stride = 0;
   int rounds = 0;
   int grid = 0;
@@ -260,7 +230,8 @@ void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, i
   *grid = g;
 
   // The same lists at K-block granularity for the gather warps.  The stream of every CTA ends with
-  // end markers; 24 of them cover the deepest look-ahead (4 blocks x 4 warps) with room to spare.
+  // end markers; 24 of them cover the deepest look-ahead (every gather warp reads one block past its
+  // own end marker) with room to spare.
   size_t max_blocks = 0;
   for (const auto& l : lists) {
     size_t nb = 0;
@@ -334,6 +305,7 @@ void free_tiles(ts_layer* l) {
   for (auto& kv : l->schedules) {
     cudaFree(kv.second.d_units);
     cudaFree(kv.second.d_blocks);
+    cudaFree(kv.second.d_meta);
   }
   l->schedules.clear();
   l->packed = false;
@@ -350,6 +322,7 @@ int get_schedule(ts_layer* l, int M, Schedule** out) {
     for (auto& kv : l->schedules) {
       cudaFree(kv.second.d_units);
       cudaFree(kv.second.d_blocks);
+      cudaFree(kv.second.d_meta);
     }
     l->schedules.clear();
   }
@@ -368,6 +341,9 @@ int get_schedule(ts_layer* l, int M, Schedule** out) {
     TS_CUDA(cudaMalloc(&s.d_blocks, blocks.size() * sizeof(ts::BlockDesc)));
     TS_CUDA(cudaMemcpy(s.d_blocks, blocks.data(), blocks.size() * sizeof(ts::BlockDesc),
                        cudaMemcpyHostToDevice));
+    TS_CUDA(cudaMalloc(&s.d_meta, blocks.size() * ts::kBlockMetaInts * sizeof(int)));
+    TS_CUDA(ts::expand_block_meta_launch(s.d_blocks, static_cast<long long>(blocks.size()), s.d_meta, nullptr));
+    TS_CUDA(cudaStreamSynchronize(nullptr));
   }
   auto ins = l->schedules.emplace(M, s);
   *out = &ins.first->second;
@@ -604,21 +580,14 @@ int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* C
   rc = get_schedule(l, M, &s);
   if (rc != TS_OK) return rc;
   if (s->n_units == 0) return TS_OK;
-  CUtensorMap tmap_a;
-  const int tr = tma_gather_rows();
-  const bool tg = tr > 0;
-  if (tg) {
-    rc = make_act_tmap(&tmap_a, l->dtype, At, l->K, M, lda);
-    if (rc != TS_OK) return rc;
-  }
   CUtensorMap tmap_c;
   const bool tst = use_tma_store();
   if (tst) {
     rc = make_out_tmap(&tmap_c, l->dtype, Ct, l->N, M, ldc);
     if (rc != TS_OK) return rc;
   }
-  TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, tr, l->tmap, tg ? &tmap_a : nullptr, tst ? &tmap_c : nullptr, l->K, s->d_units, s->rounds,
-                                 s->grid, s->d_blocks, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
+  TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, l->tmap, tst ? &tmap_c : nullptr, s->d_units, s->rounds,
+                                 s->grid, s->d_meta, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
                                  static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
@@ -711,6 +680,8 @@ struct ShimWorkspace {
   ts::WorkItem* d_units = nullptr;
   size_t unit_cap = 0;
   ts::BlockDesc* d_blocks = nullptr;
+  int* d_meta = nullptr;
+  long long n_blocks = 0;
   size_t block_cap = 0;
   // The schedule of the previous call, reused when the next call describes the same tiles (a perf
   // loop calls with identical arguments every iteration).
@@ -804,9 +775,12 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
     if (blocks.size() > ws.block_cap) {
       TS_CUDA(cudaStreamSynchronize(s));
       cudaFree(ws.d_blocks);
+      cudaFree(ws.d_meta);
       ws.d_blocks = nullptr;
+      ws.d_meta = nullptr;
       ws.block_cap = 0;
       TS_CUDA(cudaMalloc(&ws.d_blocks, blocks.size() * sizeof(ts::BlockDesc)));
+      TS_CUDA(cudaMalloc(&ws.d_meta, blocks.size() * ts::kBlockMetaInts * sizeof(int)));
       ws.block_cap = blocks.size();
     }
     // Pageable sources: the runtime stages them before returning, so the vectors may die after this.
@@ -814,21 +788,18 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
     TS_CUDA(cudaMemcpyAsync(ws.d_blocks, blocks.data(), blocks.size() * sizeof(ts::BlockDesc),
                             cudaMemcpyHostToDevice, s));
     ws.key = key;
+    ws.n_blocks = static_cast<long long>(blocks.size());
   }
+  // The caller owns the offset lists and may have rewritten them since the schedule was cached:
+  // they are resolved again on every call.
+  TS_CUDA(ts::expand_block_meta_launch(ws.d_blocks, ws.n_blocks, ws.d_meta, s));
   const int rounds = ws.rounds, grid = ws.grid, blk_stride = ws.blk_stride, unit_rows = ws.unit_rows;
-  CUtensorMap tmap_a;
-  const int tr = tma_gather_rows();
-  const bool tg = tr > 0;
-  if (tg) {
-    rc = make_act_tmap(&tmap_a, dtype, A, K, M, M);
-    if (rc != TS_OK) return rc;
-  }
   ts::EpilogueArgs ep;
   memset(&ep, 0, sizeof(ep));
   ep.alpha = alpha;
   ep.beta = beta;
-  TS_CUDA(ts::masked_gemm_launch(dtype, unit_rows, tr, tmap, tg ? &tmap_a : nullptr, nullptr, K, ws.d_units, rounds, grid,
-                                 ws.d_blocks, blk_stride, A, M, C, M, M, ep, ws.d_status, s));
+  TS_CUDA(ts::masked_gemm_launch(dtype, unit_rows, tmap, nullptr, ws.d_units, rounds, grid,
+                                 ws.d_meta, blk_stride, A, M, C, M, M, ep, ws.d_status, s));
   return TS_OK;
 }
 
@@ -861,7 +832,7 @@ int ts_transpose16(const void* in_dev, int64_t ld_in, void* out_dev, int64_t ld_
 }
 
 #ifdef TS_KERNEL_TRACE
-// Debug builds only: cycle stamps of CTA 0 of the most recent traced launches.
+// Debug builds only: the time stamps (160 CTAs x 64 slots) of the most recent traced launch.
 int ts_debug_read_trace(long long* out64, int clear) {
   TS_CUDA(cudaDeviceSynchronize());
   TS_CUDA(ts::masked_gemm_read_trace(out64, clear != 0));

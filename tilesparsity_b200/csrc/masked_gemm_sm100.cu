@@ -18,16 +18,19 @@
 // the batch is its N dimension (MT = 128 or 256 columns per instruction), the kept rows are K.  The
 // packed weights are the K-major A operand, fetched by TMA with 128-byte swizzle; the gathered
 // activation rows are the MN-major B operand, fetched with 16-byte cp.async into the same swizzle
-// pattern (one kept row is one contiguous 2*MT-byte global segment).  The four gather warps fill
-// each 64-row K block together; block descriptors and kept-row indices are prefetched into small
-// shared-memory rings; each lane
+// pattern (one kept row is one contiguous 2*MT-byte global segment).
+//
+// Pipeline: four stages, one per gather warp.  Gather warp g copies the 64 rows of K blocks g, g+4,
+// g+8, ... of the CTA's block stream into stage g, so a warp's bookkeeping (one shared-memory record
+// per block: descriptor + 64 resolved row numbers, prefetched by cp.async one block ahead) is paid
+// once per block per warp while the other three warps keep the load/store unit busy.  Each lane
 // hands its copies to the stage's mbarrier with cp.async.mbarrier.arrive, so a stage is released to
 // the MMA warp the moment its bytes have landed.  Accumulators live in TMEM, double buffered: the
 // epilogue of one work unit overlaps the main loop of the next.  Eight epilogue warps (two per TMEM
-// lane quarter, each taking half of the unit's batch columns) convert their rows to 16 bit into a
-// 128-byte-swizzled staging tile in shared memory.  When the tile's kept columns are consecutive
-// rows of Ct (no column pruning) the tile leaves with one TMA store per 64 batch columns; otherwise
-// the epilogue warps write the rows with 16-byte coalesced stores through the kept-column list.
+// lane quarter; each half of them takes every other 64-column group of the unit) convert their rows
+// to 16 bit into a 128-byte-swizzled 16 KiB staging group per half.  When the tile's kept columns
+// are consecutive rows of Ct (no column pruning) a group leaves with one TMA store; otherwise each
+// warp writes its 32 rows with 16-byte coalesced stores through the kept-column list.
 //
 // Warp roles (448 threads): warp 0 = weight TMA, warp 1 = TMEM allocation + MMA issue,
 // warps 2-5 = activation gather, warps 6-13 = epilogue.
@@ -48,34 +51,31 @@ constexpr int kEpiThreads = 256;
 constexpr uint32_t kASbo = 1024;         // bytes between 8-row K groups of the gathered operand
 constexpr uint32_t kALbo = kKB * 128;    // bytes between its 64-column batch groups
 constexpr uint32_t kWSbo = 1024;         // bytes between 8-row groups of the weight operand
-constexpr int kMaxStages = 5;
+constexpr int kStages = 4;               // one per gather warp
+constexpr int kGW = 4;                   // gather warps
+constexpr int kMetaInts = kBlockMetaInts;  // one block record: {m0, meta, 0, 0} + 64 row numbers
 
-// Compile-time shape of one kernel variant: MT batch rows per work unit.
-template <int MT>
-struct Cfg {
-  static constexpr int kStages = MT == 256 ? 3 : 5;
-  static constexpr int kABytes = kKB * MT * 2;
-  static constexpr int kStageBytes = kWBytes + kABytes;
-  static constexpr int kEpiGroupBytes = kNT * 128;   // staging: one 128-row x 64-column swizzled group
-  static constexpr int kEpiBytes = (MT / 64) * kEpiGroupBytes;
-  static constexpr int kTmemCols = 2 * MT;          // two accumulators of MT fp32 columns
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 6144 + 1024;
-  static constexpr int kLanesPerRow = MT / 8;       // 16-byte chunks in one gathered row
-  static constexpr int kRowsPerInstr = 32 / kLanesPerRow;
-};
-
-// Optional cycle-stamp trace of CTA 0 (debug builds only: -DTS_KERNEL_TRACE).  Slot i receives
-// clock64() the first time the kernel passes trace point i.
+// Optional time-stamp trace (debug builds only: -DTS_KERNEL_TRACE).  Every CTA keeps 64 stamps in
+// shared memory (globaltimer nanoseconds; slot i is written the first time the CTA passes trace
+// point i) and copies them to g_trace[cta][64] when it retires, so tracing adds no global access
+// to the loops it observes.
 #ifdef TS_KERNEL_TRACE
-__device__ long long g_trace[256];
-#define TS_TRACE(id, leader)                                                       \
-  do {                                                                             \
-    if (blockIdx.x == 0 && (leader) && g_trace[id] == 0) g_trace[id] = clock64();  \
+constexpr int kTraceSlots = 64;
+constexpr int kTraceCtas = 160;
+__device__ long long g_trace[kTraceCtas * kTraceSlots];
+__device__ __forceinline__ long long trace_now() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TS_TRACE(id, leader)                                                                   \
+  do {                                                                                         \
+    if ((leader) && (id) < kTraceSlots && bars->trace[id] == 0) bars->trace[id] = trace_now(); \
   } while (0)
-// Per-unit stamps: slot 64 + kind*8 + unit for the CTA's first eight units.
-#define TS_TRACE_U(kind, unit, leader)                                              \
-  do {                                                                             \
-    if ((unit) < 8) TS_TRACE(64 + (kind)*8 + (unit), leader);                       \
+// Per-unit stamps: slot 8 + kind*4 + unit for the CTA's first four units (kinds 0..4).
+#define TS_TRACE_U(kind, unit, leader)                       \
+  do {                                                       \
+    if ((unit) < 4) TS_TRACE(8 + (kind)*4 + (unit), leader); \
   } while (0)
 #else
 #define TS_TRACE(id, leader) \
@@ -87,16 +87,33 @@ __device__ long long g_trace[256];
 #endif
 
 struct Barriers {
-  uint64_t full[kMaxStages];
-  uint64_t empty[kMaxStages];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int c_row[kNT];  // Ct row of each tile column of the unit in the epilogue (-1: not kept)
-  // Per gather warp: ring of block descriptors (8 slots) and of kept-row indices (4 slots x 64).
-  BlockDesc desc_ring[4][8];
-  int idx_ring[4][4][kKB];
+  // Per gather warp: two block records (the one being copied, the one being prefetched).
+  alignas(16) int meta_ring[kGW][2][kMetaInts];
+#ifdef TS_KERNEL_TRACE
+  long long trace[64];
+#endif
+};
+
+// Compile-time shape of one kernel variant: MT batch rows per work unit.
+template <int MT>
+struct Cfg {
+  static constexpr int kABytes = kKB * MT * 2;
+  static constexpr int kStageBytes = kWBytes + kABytes;
+  static constexpr int kEpiGroupBytes = kNT * 128;   // staging: one 128-row x 64-column swizzled group
+  static constexpr int kEpiBytes = 2 * kEpiGroupBytes;  // one group per half of the epilogue warps
+  static constexpr int kTmemCols = 2 * MT;          // two accumulators of MT fp32 columns
+  // stages + staging + barriers/records + what the 1024-byte alignment of the first stage may skip
+  static constexpr int kUsedBytes = kStages * kStageBytes + kEpiBytes + static_cast<int>(sizeof(Barriers));
+  static constexpr int kSmemBytes = (kUsedBytes + 1023 + 1023) / 1024 * 1024 > 232448 ? 232448
+                                                                                      : (kUsedBytes + 1023 + 1023) / 1024 * 1024;
+  static constexpr int kLanesPerRow = MT / 8;       // 16-byte chunks in one gathered row
+  static constexpr int kRowsPerInstr = 32 / kLanesPerRow;
 };
 
 __device__ __forceinline__ WorkItem load_item(const WorkItem* p) {
@@ -144,22 +161,26 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <int DT, int MT, int TMA_ROWS>
+template <int DT, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
-masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
+masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_c, int use_tma_store,
-                   const WorkItem* __restrict__ sched,
-                   int rounds, const BlockDesc* __restrict__ blocks, int blk_stride, int K_oob,
+                   const WorkItem* __restrict__ sched, int rounds,
+                   const int* __restrict__ block_meta, int blk_stride,
                    const uint16_t* __restrict__ At, long long lda,
                    uint16_t* __restrict__ Ct, long long ldc, int M, const EpilogueArgs ep,
                    int* __restrict__ status) {
   const float alpha = ep.alpha, beta = ep.beta;
   using C = Cfg<MT>;
-  constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  if (static_cast<int>(smem - smem_raw) + C::kUsedBytes > C::kSmemBytes) {
+    // the dynamic shared-memory window starts at an address this layout was not sized for
+    if (threadIdx.x == 0) atomicExch(status, kErrUnsupported);
+    return;
+  }
   uint8_t* epi = smem + kStages * C::kStageBytes;
   Barriers* bars = reinterpret_cast<Barriers*>(epi + C::kEpiBytes);
   volatile int* abort_flag = &bars->abort_flag;
@@ -168,17 +189,26 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   const int lane = threadIdx.x & 31;
   const int grid = gridDim.x;
   const int cta = blockIdx.x;
+#ifdef TS_KERNEL_TRACE
+  if (threadIdx.x < 64) bars->trace[threadIdx.x] = 0;
+  __syncthreads();
+#endif
   TS_TRACE(0, threadIdx.x == 0);
 
-  // First work item (and, for the gather warps, its first kept-row indices): requested before the
-  // set-up below so their latency overlaps it.
+  // First work item, and for the gather warps the record of their first block: requested before
+  // the set-up below so their latency overlaps it.  The schedule is static data.
   WorkItem w = fetch_item(sched, rounds, grid, cta, 0);
+  const int gw = warp - 2;                                  // gather warp number (warps 2..5)
+  const int* recs = block_meta + static_cast<size_t>(cta) * blk_stride * kMetaInts;
+  if (warp >= 2 && warp < 6) {
+    if (lane < kMetaInts / 4) cp_async_16_ca(smem_u32(&bars->meta_ring[gw][0][lane * 4]), recs + gw * kMetaInts + lane * 4);
+    cp_async_commit();
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      // weight TMA thread + the gather leader's expect-tx arrival (rows fetched by TMA) + the 128
-      // cp.async lanes (rows fetched through the load/store unit)
-      mbar_init(smem_u32(&bars->full[s]), 1 + (TMA_ROWS > 0 ? 1 : 0) + (TMA_ROWS < kKB ? 128 : 0));
+      // weight TMA thread + the 32 cp.async lanes of the stage's gather warp
+      mbar_init(smem_u32(&bars->full[s]), 1 + 32);
       mbar_init(smem_u32(&bars->empty[s]), 1);       // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -245,7 +275,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         const uint32_t ph = (it / kStages) & 1u;
         ok = mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag);
         if (!ok) break;
-        TS_TRACE(8 + (it < 4 ? it : 4), lane == 0);
+        TS_TRACE(40 + it, lane == 0);   // full barrier of block `it` passed
         if (kb == 0) TS_TRACE_U(1, acc_it, lane == 0);
         if (kb == nkb - 1) TS_TRACE_U(2, acc_it, lane == 0);
         // The gathered rows were written through the generic proxy; the MMA reads them through
@@ -277,135 +307,99 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
         }
       }
       __syncwarp();
-      TS_TRACE(16, lane == 0);
       ++acc_it;
       w = wn;
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ activation gather
-    // The four gather warps fill every 64-row K block together, a quarter of its copies each, so a
-    // stage is occupied only briefly before the MMA warp can consume it.  Everything a warp needs
-    // arrives by cp.async, requested ahead of use: the descriptor of block j+4 and the kept-row
-    // indices of block j+2 are requested while block j is copied, so no step of the loop waits on
-    // a dependent global read.
-    constexpr int kGW = 4;
-    const int gw = warp - 2;
-    const BlockDesc* bd = blocks + static_cast<size_t>(cta) * blk_stride;
-    BlockDesc* dring = bars->desc_ring[gw];
-    int(*iring)[kKB] = bars->idx_ring[gw];
-
-    auto request_indices = [&](int jj) {
-      const BlockDesc d = dring[jj & 7];
-      if (d.meta != kBlockEnd) {
-        const int nv = static_cast<int>(d.meta & 0x7fu);
-        if (lane < nv) cp_async_4(smem_u32(&iring[jj & 3][lane]), d.idx + lane);
-        if (lane + 32 < nv) cp_async_4(smem_u32(&iring[jj & 3][lane + 32]), d.idx + lane + 32);
-      }
-    };
-    // prologue: descriptors of blocks 0..3 by plain loads, indices of blocks 0 and 1 requested
-    if (lane < 4) dring[lane] = bd[lane];
-    __syncwarp();
-    request_indices(0);
-    cp_async_commit();
-    request_indices(1);
-    cp_async_commit();
-    // The schedule and the index lists are static; the activations may be the previous kernel's
-    // output: wait for it before the first row is copied.
+    // Warp gw owns stage gw and the blocks gw, gw+4, ... of the CTA's stream.  Per block: wait for
+    // its record (prefetched during the previous block), wait for the stage, issue the 64 rows in
+    // four batches of 16 (row numbers read from the record into registers before the batch goes
+    // out: a shared-memory read between two copies would serialise them), hand the copies to the
+    // stage's barrier.  One cp.async group is committed per block, made of the previous block's row
+    // copies and the next record's request; "all but the latest group have completed" therefore
+    // says that this block's record has landed while the previous block's rows may still be in
+    // flight.
+    constexpr int kLpr = C::kLanesPerRow, kRpi = C::kRowsPerInstr;
+    const int chunk = lane % kLpr, sub = lane / kLpr;
+    const int g = chunk >> 3, c = chunk & 7;
+    const uint32_t s = static_cast<uint32_t>(gw);
+    const uint32_t dst0 = smem_u32(smem + s * C::kStageBytes + kWBytes) + g * kALbo;
+    const uint32_t bar = smem_u32(&bars->full[s]);
+    const uint32_t empty_bar = smem_u32(&bars->empty[s]);
+    // The schedule is static; the activations may be the previous kernel's output: wait for it
+    // before the first row is copied.
     grid_dependency_wait();
 
-    bool ok = true;
-    for (int j = 0; ok; ++j) {
-      cp_async_wait_group<1>();   // indices of block j and descriptor of block j+2 have landed
-      __syncwarp();
-      const BlockDesc d = dring[j & 7];
-      if (d.meta == kBlockEnd) break;
-      request_indices(j + 2);
-      if (lane == 0) cp_async_16_ca(smem_u32(&dring[(j + 4) & 7]), bd + j + 4);
+    for (uint32_t it = 0;; ++it) {
+      const int j = gw + static_cast<int>(it) * kGW;
+      if (lane < kMetaInts / 4) {
+        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][(it + 1) & 1][lane * 4]),
+                       recs + static_cast<size_t>(j + kGW) * kMetaInts + lane * 4);
+      }
       cp_async_commit();
-
-      const uint32_t it = static_cast<uint32_t>(j);
-      const uint32_t s = it % kStages;
-      const uint32_t ph = (it / kStages) & 1u;
-      if (j < 8) TS_TRACE(208 + j, lane == 0 && gw == 0);
-      ok = mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag);
-      if (!ok) break;
-      if (j < 8) TS_TRACE(192 + j * 2, lane == 0 && gw == 0);
-      const int nv = static_cast<int>(d.meta & 0x7fu);
-      const int rel = (d.meta & 0x80u) ? static_cast<int>(d.meta >> 10) : -1;  // list position, if relative
-      const int m_len = (static_cast<int>((d.meta >> 8) & 3u) + 1) * 64;        // batch rows of the unit
-      const int* idx = iring[j & 3];
-      const uint32_t a_base = smem_u32(smem + s * C::kStageBytes + kWBytes);
-      const uint32_t bar = smem_u32(&bars->full[s]);
-      // The block's first TMA_ROWS rows come through the copy engine (tile::gather4), the rest
-      // through the load/store unit (cp.async): the two paths run side by side.
-      if constexpr (TMA_ROWS > 0) {
-        // One gather4 per four kept rows and 64 batch columns (512 bytes).  Rows past the end of the
-        // list use a row index outside the tensor, which reads as zeros.
-        if (gw == 0 && lane == 0) mbar_arrive_expect_tx(bar, TMA_ROWS * m_len * 2);
-        constexpr int kKg = TMA_ROWS / 4;                 // groups of four rows
-        constexpr int kOps = kKg * (MT / 64);
-        constexpr int kOpsPerWarp = (kOps + kGW - 1) / kGW;
-        static_assert(kOpsPerWarp <= 32, "one gather4 per lane");
-        const int qq = gw * kOpsPerWarp + lane;
-        if (lane < kOpsPerWarp && qq < kOps && (qq / kKg) * 64 < m_len) {
-          const int kg = qq % kKg, mg = qq / kKg;
-          const int4 r4 = *reinterpret_cast<const int4*>(idx + kg * 4);
-          const int base = kg * 4;
-          const int add = rel >= 0 ? rel + base : 0;
-          const int step = rel >= 0 ? 1 : 0;
-          const int r0 = base + 0 < nv ? r4.x + add : K_oob;
-          const int r1 = base + 1 < nv ? r4.y + add + step : K_oob;
-          const int r2 = base + 2 < nv ? r4.z + add + 2 * step : K_oob;
-          const int r3 = base + 3 < nv ? r4.w + add + 3 * step : K_oob;
-          tma_gather4(a_base + mg * kALbo + (kg >> 1) * kASbo + (kg & 1) * 512, &tmap_a, d.m0 + mg * 64, r0,
-                      r1, r2, r3, bar);
-        }
+      cp_async_wait_group<1>();
+      __syncwarp();
+      const int* rec = bars->meta_ring[gw][it & 1];
+      const int m0 = rec[0];
+      const uint32_t meta = static_cast<uint32_t>(rec[1]);
+      if (meta == kBlockEnd) break;
+      const int nv = static_cast<int>(meta & 0x7fu);
+      const int m_len = (static_cast<int>((meta >> 8) & 3u) + 1) * 64;          // batch rows of the unit
+      const int m = m0 + chunk * 8;
+      const bool m_ok = m < M;
+      const uint16_t* src_col = At + (m_ok ? m : 0);
+      const bool lane_live = chunk * 8 < m_len;             // columns past the unit are never read
+      const bool full_block = nv == kKB && m0 + m_len <= M;
+      if (!mbar_wait(empty_bar, (it & 1u) ^ 1u, abort_flag)) break;
+      TS_TRACE(52 + j, lane == 0);   // stage acquired for block j
+      // All 64 row numbers go to registers before the first copy is issued: a shared-memory read
+      // between two copies stalls the warp until the copies before it have been taken by the
+      // load/store unit.
+      int rr[kKB];
+#pragma unroll
+      for (int q4 = 0; q4 < kKB / 4; ++q4) {
+        const int4 v = reinterpret_cast<const int4*>(rec + 4)[q4];
+        rr[q4 * 4] = v.x;
+        rr[q4 * 4 + 1] = v.y;
+        rr[q4 * 4 + 2] = v.z;
+        rr[q4 * 4 + 3] = v.w;
       }
-      if constexpr (TMA_ROWS < kKB) {
-        // 16-byte cp.async copies: this warp takes a quarter of the remaining rows.  Their indices
-        // are read into registers before the first copy goes out (a shared-memory read between two
-        // copies would serialise them).
-        constexpr int kLpr = C::kLanesPerRow, kRpi = C::kRowsPerInstr;
-        constexpr int kLsuRows = kKB - TMA_ROWS;
-        constexpr int kRowsPerWarp = kLsuRows / kGW;
-        static_assert(kLsuRows % (kGW * kRpi) == 0, "rows must split evenly over the gather warps");
-        constexpr int kCopies = kRowsPerWarp / kRpi;
-        const int chunk = lane % kLpr, sub = lane / kLpr;
-        const int g = chunk >> 3, c = chunk & 7;
-        const int m = d.m0 + chunk * 8;
-        const bool m_ok = m < M;
-        const uint16_t* src_col = At + (m_ok ? m : 0);
-        const int row0 = TMA_ROWS + gw * kRowsPerWarp;
-        int krow[kCopies];
+      // Two separate bursts: mixing the zero-fill form into the loop of plain copies makes every
+      // copy as slow as the zero-fill form.
+      if (full_block) {
+        if (lane_live) {
 #pragma unroll
-        for (int e = 0; e < kCopies; ++e) {
-          const int row = row0 + e * kRpi + sub;
-          krow[e] = (row < nv) ? idx[row] + (rel >= 0 ? rel + row : 0) : 0;
-        }
-        const uint32_t dst0 = a_base + g * kALbo;
-        const bool lane_live = chunk * 8 < m_len;           // columns past the unit are never read
-        if (nv == kKB && d.m0 + m_len <= M) {
-          if (lane_live) {
-#pragma unroll
-            for (int e = 0; e < kCopies; ++e) {
-              const int row = row0 + e * kRpi + sub;
-              cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
-                               src_col + static_cast<long long>(krow[e]) * lda);
+          for (int e = 0; e < kKB / kRpi; ++e) {
+            const int row = e * kRpi + sub;
+            int kr;
+            if constexpr (kRpi == 1) {
+              kr = rr[e];
+            } else {
+              kr = sub ? rr[e * 2 + 1] : rr[e * 2];
             }
-          }
-        } else if (lane_live) {
-#pragma unroll
-          for (int e = 0; e < kCopies; ++e) {
-            const int row = row0 + e * kRpi + sub;
-            const bool valid = (row < nv) && m_ok;
-            cp_async_16(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
-                        valid ? src_col + static_cast<long long>(krow[e]) * lda : At, valid ? 16u : 0u);
+            cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
+                             src_col + static_cast<long long>(kr) * lda);
+            if ((e & 15) == 15) TS_TRACE(4 + (e >> 4), lane == 0 && gw == 0 && it == 0);
           }
         }
-        cp_async_arrive_noinc(bar);
+      } else if (lane_live) {
+#pragma unroll
+        for (int e = 0; e < kKB / kRpi; ++e) {
+          const int row = e * kRpi + sub;
+          int kr;
+          if constexpr (kRpi == 1) {
+            kr = rr[e];
+          } else {
+            kr = sub ? rr[e * 2 + 1] : rr[e * 2];
+          }
+          const bool valid = (row < nv) && m_ok;
+          cp_async_16(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
+                      valid ? src_col + static_cast<long long>(kr) * lda : At, valid ? 16u : 0u);
+        }
       }
-      TS_TRACE(24 + (it < 4 ? it : 4), lane == 0 && gw == 0);
-      if (j < 8) TS_TRACE(193 + j * 2, lane == 0 && gw == 0);
+      cp_async_arrive_noinc(bar);
+      TS_TRACE(28 + j, lane == 0 && j < 8);   // copies of block j issued
     }
     cp_async_wait_all();  // nothing of this thread is in flight when the CTA retires
   } else if (warp >= 6) {
@@ -415,7 +409,9 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     const int half = ew >> 2;                    // takes the 64-column groups half, half+2, ...
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int j = q * 32 + lane;                 // tile column owned by this thread
-    const bool leader = (warp == 6 && lane == 0);
+    const bool leader = ((ew & 3) == 0 && lane == 0);   // one per half
+    uint8_t* stage_grp = epi + half * C::kEpiGroupBytes;
+    const int half_bar = 1 + half;               // named barrier of this half (128 threads)
     uint32_t acc_it = 0;
     bool ok = true;
     grid_dependency_wait();   // Ct may still be read or written by the previous kernel
@@ -430,11 +426,12 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
       const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f && ep.n_peers == 0;
       const bool plain = beta == 0.0f && ep.bias == nullptr && ep.act == kActNone;
       const long long c_row = active ? c_row_of(w, j) : 0;
+      const int c_row_or_none = active ? static_cast<int>(c_row) : -1;
       const float bias_j = (ep.bias != nullptr && active) ? __ldg(ep.bias + c_row) : 0.0f;
       uint16_t* gdst = Ct + c_row * ldc + m0;
+      const int tile_row0 = w.c_row0 + ((tma_store && w.n_list) ? __ldg(w.n_list) : 0);
       ok = mbar_wait(smem_u32(&bars->acc_full[a]), aph, abort_flag);
       if (!ok) break;
-      TS_TRACE(32, threadIdx.x == 192);
       TS_TRACE_U(3, acc_it, threadIdx.x == 192);
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + a * MT + (static_cast<uint32_t>(q * 32) << 16);
@@ -445,7 +442,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
 #pragma unroll
       for (int gi = 0; gi < kGroups; ++gi) {
         const int grp_col = (gi * 2 + half) * 64;        // first batch column of this thread's group
-        const bool grp_live = grp_col < m_cnt;           // uniform over the warp
+        const bool grp_live = grp_col < m_cnt;           // uniform over the half
         uint32_t v[kBatch][32];
         if (grp_live) {
           if (has_acc) {
@@ -464,13 +461,11 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
           tc_fence_before_sync();
           mbar_arrive(smem_u32(&bars->acc_empty[a]));
         }
-        if (gi == 0) {
-          // the staging tile is free once the previous unit's TMA store has read it (the leader
-          // waits for that) and every thread has finished the previous copy-out
-          if (leader) bulk_wait_read_all();
-          named_barrier_sync(1, kEpiThreads);
-        }
         if (!grp_live) continue;
+        // The half's staging group is free once its previous TMA store has read it (the leader
+        // waits for that) and every warp of the half has finished its previous copy-out.
+        if (leader) bulk_wait_read_all();
+        named_barrier_sync(half_bar, 128);
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
           const int col0 = grp_col + b * 32;             // first batch column of the chunk
@@ -507,68 +502,61 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
               }
             }
           }
-          // staging: [64-column group][tile column j][128 bytes], 16-byte chunks swizzled by j & 7
-          const int g16 = col0 >> 3;                     // first 16-byte chunk of these 32 columns
-          uint8_t* grp = epi + (g16 >> 3) * C::kEpiGroupBytes + j * 128;
+          // staging: [tile column j][128 bytes], 16-byte chunks swizzled by j & 7
+          uint8_t* row_ptr = stage_grp + j * 128;
 #pragma unroll
           for (int e4 = 0; e4 < 4; ++e4) {
-            const int c = (g16 & 7) + e4;
-            *reinterpret_cast<uint4*>(grp + ((c ^ (j & 7)) << 4)) =
+            const int cc = b * 4 + e4;
+            *reinterpret_cast<uint4*>(row_ptr + ((cc ^ (j & 7)) << 4)) =
                 make_uint4(o[e4 * 4], o[e4 * 4 + 1], o[e4 * 4 + 2], o[e4 * 4 + 3]);
           }
         }
-      }
-      if (half == 0) bars->c_row[j] = active ? static_cast<int>(c_row) : -1;
-      TS_TRACE(33, threadIdx.x == 192);
-      TS_TRACE_U(4, acc_it, threadIdx.x == 192);
-      if (tma_store) fence_proxy_async_smem();
-      named_barrier_sync(1, kEpiThreads);       // all rows are staged
-      TS_TRACE_U(5, acc_it, threadIdx.x == 192);
-      if (tma_store) {
-        if (leader) {
-          const int row0 = w.c_row0 + (w.n_list ? __ldg(w.n_list) + 0 : 0);
+        TS_TRACE_U(4, acc_it, threadIdx.x == 192);
+        if (tma_store) {
+          fence_proxy_async_smem();
+          named_barrier_sync(half_bar, 128);     // the whole group is staged
+          if (leader) {
+            tma_store_2d(&tmap_c, smem_u32(stage_grp), m0 + grp_col, tile_row0);
+            bulk_commit();
+          }
+        } else {
+          // copy-out through the kept-column list: this warp's own 32 rows, four rows per
+          // instruction, 16 bytes per lane
+          __syncwarp();
+          const int cchunk = lane & 7, rsub = lane >> 3;
+          const bool m_ok = grp_col + cchunk * 8 < m_cnt;
 #pragma unroll
-          for (int mg = 0; mg < MT / 64; ++mg) {
-            if (mg * 64 < m_cnt) {
-              tma_store_2d(&tmap_c, smem_u32(epi + mg * C::kEpiGroupBytes), m0 + mg * 64, row0);
+          for (int r4 = 0; r4 < 32; r4 += 16) {
+            int cr[4];
+            uint4 val[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int lrow = r4 + e * 4 + rsub;           // row inside the warp's quarter
+              const int row = q * 32 + lrow;
+              cr[e] = __shfl_sync(0xffffffffu, c_row_or_none, lrow);
+              val[e] = *reinterpret_cast<const uint4*>(stage_grp + row * 128 + ((cchunk ^ (row & 7)) << 4));
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (cr[e] >= 0 && m_ok) {
+                const long long off = static_cast<long long>(cr[e]) * ldc + m0 + grp_col + cchunk * 8;
+                *reinterpret_cast<uint4*>(Ct + off) = val[e];
+                // tile-sharded layers: the same rows go to the other GPUs' copies of Ct over NVLink
+                for (int p = 0; p < ep.n_peers; ++p) *reinterpret_cast<uint4*>(ep.peers[p] + off) = val[e];
+              }
             }
           }
-          bulk_commit();
+          __syncwarp();
         }
-      } else {
-        // copy-out through the kept-column list: 16 rows per warp, 16 bytes per lane
-        constexpr int kLpr = C::kLanesPerRow, kRpi = C::kRowsPerInstr;
-        const int chunk = lane % kLpr, sub = lane / kLpr;
-        const bool m_ok = chunk * 8 < m_cnt;
-#pragma unroll
-        for (int r4 = 0; r4 < 16 / kRpi; r4 += 4) {
-          // four rows per batch: shared-memory reads first, then the global stores
-          int cr[4];
-          uint4 val[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int row = ew * 16 + (r4 + e) * kRpi + sub;
-            cr[e] = bars->c_row[row];
-            val[e] = *reinterpret_cast<const uint4*>(epi + (chunk >> 3) * C::kEpiGroupBytes + row * 128 +
-                                                     (((chunk & 7) ^ (row & 7)) << 4));
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            if (cr[e] >= 0 && m_ok) {
-              const long long off = static_cast<long long>(cr[e]) * ldc + m0 + chunk * 8;
-              *reinterpret_cast<uint4*>(Ct + off) = val[e];
-              // tile-sharded layers: the same rows go to the other GPUs' copies of Ct over NVLink
-              for (int p = 0; p < ep.n_peers; ++p) *reinterpret_cast<uint4*>(ep.peers[p] + off) = val[e];
-            }
-          }
-        }
+        TS_TRACE(36 + acc_it, threadIdx.x == 192 && acc_it < 4);   // group stored
       }
-      TS_TRACE_U(6, acc_it, threadIdx.x == 192);
       ++acc_it;
       w = wn;
     }
-    if (leader) bulk_wait_all();                // the last TMA store has been written
-    TS_TRACE(34, threadIdx.x == 192);
+    // The CTA may retire once its last TMA stores have read the staging groups; the stores
+    // themselves complete before the grid does.
+    if (leader) bulk_wait_read_all();
+    TS_TRACE(3, threadIdx.x == 192);
   }
 
   tc_fence_before_sync();
@@ -577,13 +565,35 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
   if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, kErrTimeout);
   TS_TRACE(2, threadIdx.x == 0);
+#ifdef TS_KERNEL_TRACE
+  __syncthreads();
+  if (threadIdx.x < 64 && blockIdx.x < kTraceCtas) g_trace[blockIdx.x * 64 + threadIdx.x] = bars->trace[threadIdx.x];
+#endif
 }
 
-template <int DT, int MT, int TMA_ROWS>
-cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a, const CUtensorMap& tmap_c,
-                           int use_tma_store, int K_oob,
-                           const WorkItem* sched, int rounds, int grid,
-                           const BlockDesc* blocks, int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
+// One record per K block of a schedule: {first batch row of the unit, meta word, 0, 0} followed by
+// the 64 rows of At the block gathers (0 past the block's last row): the kept row number itself,
+// or list position + offset for lists in the reference's relative form.
+__global__ void __launch_bounds__(256)
+expand_block_meta_kernel(const BlockDesc* __restrict__ blocks, long long n_blocks, int* __restrict__ meta) {
+  const long long b = blockIdx.x * 4LL + (threadIdx.x >> 6);
+  const int r = threadIdx.x & 63;
+  if (b >= n_blocks) return;
+  const BlockDesc d = blocks[b];
+  int v = 0;
+  if (d.meta != kBlockEnd && r < static_cast<int>(d.meta & 0x7fu)) {
+    v = __ldg(d.idx + r);
+    if (d.meta & 0x80u) v += static_cast<int>(d.meta >> 10) + r;
+  }
+  int* rec = meta + b * kMetaInts;
+  rec[4 + r] = v;
+  if (r < 4) rec[r] = r == 0 ? d.m0 : (r == 1 ? static_cast<int>(d.meta) : 0);
+}
+
+template <int DT, int MT>
+cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_c, int use_tma_store,
+                           const WorkItem* sched, int rounds, int grid, const int* block_meta, int blk_stride,
+                           const void* At, long long lda, void* Ct, long long ldc, int M,
                            const EpilogueArgs& ep, int* status, cudaStream_t stream) {
   // Programmatic dependent launch lets this kernel's set-up overlap the tail of the kernel before
   // it in the stream.  TS_PDL=0 turns it off.
@@ -591,7 +601,7 @@ cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
     const char* e = getenv("TS_PDL");
     return !(e && e[0] == '0');
   }();
-  auto kern = masked_gemm_kernel<DT, MT, TMA_ROWS>;
+  auto kern = masked_gemm_kernel<DT, MT>;
   // The dynamic shared-memory limit is a per-device, per-kernel attribute: set it once for each.
   static bool attr_set[64] = {};
   int dev = 0;
@@ -612,48 +622,40 @@ cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_a,
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_a, tmap_c, use_tma_store, sched, rounds, blocks, blk_stride,
-                            K_oob, static_cast<const uint16_t*>(At), lda, static_cast<uint16_t*>(Ct), ldc, M,
+  return cudaLaunchKernelEx(&cfg, kern, tmap_w, tmap_c, use_tma_store, sched, rounds, block_meta, blk_stride,
+                            static_cast<const uint16_t*>(At), lda, static_cast<uint16_t*>(Ct), ldc, M,
                             ep, status);
 }
 
 }  // namespace
 
-cudaError_t masked_gemm_launch(int dtype, int unit_rows, int tma_rows, const CUtensorMap& tmap_w,
-                               const CUtensorMap* tmap_a, const CUtensorMap* tmap_c, int K_oob,
-                               const WorkItem* sched, int rounds,
-                               int grid, const BlockDesc* blocks, int blk_stride, const void* At,
-                               long long lda, void* Ct, long long ldc, int M, const EpilogueArgs& ep,
-                               int* status, cudaStream_t stream) {
-  if (tma_rows > 0 && !tmap_a) return cudaErrorInvalidValue;
-#define TS_LAUNCH(DT, MT, TR)                                                                        \
-  launch_variant<DT, MT, TR>(tmap_w, TR > 0 ? *tmap_a : tmap_w, tmap_c ? *tmap_c : tmap_w,            \
-                             tmap_c ? 1 : 0, K_oob, sched, rounds, grid, blocks,                      \
-                             blk_stride, At, lda, Ct, ldc, M, ep, status, stream)
-#define TS_BY_ROWS(DT, MT)                      \
-  switch (tma_rows) {                           \
-    case 0: return TS_LAUNCH(DT, MT, 0);        \
-    case 64: return TS_LAUNCH(DT, MT, 64);      \
-    default: return cudaErrorInvalidValue;      \
-  }
+cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w, const CUtensorMap* tmap_c,
+                               const WorkItem* sched, int rounds, int grid, const int* block_meta,
+                               int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
+                               const EpilogueArgs& ep, int* status, cudaStream_t stream) {
+#define TS_LAUNCH(DT, MT)                                                                                  \
+  launch_variant<DT, MT>(tmap_w, tmap_c ? *tmap_c : tmap_w, tmap_c ? 1 : 0, sched, rounds, grid, block_meta, \
+                         blk_stride, At, lda, Ct, ldc, M, ep, status, stream)
   const bool bf = dtype == kBF16;
-  if (unit_rows == 256) {
-    if (bf) { TS_BY_ROWS(kBF16, 256) } else { TS_BY_ROWS(kF16, 256) }
-  }
-  if (unit_rows == 128) {
-    if (bf) { TS_BY_ROWS(kBF16, 128) } else { TS_BY_ROWS(kF16, 128) }
-  }
-#undef TS_BY_ROWS
+  if (unit_rows == 256) return bf ? TS_LAUNCH(kBF16, 256) : TS_LAUNCH(kF16, 256);
+  if (unit_rows == 128) return bf ? TS_LAUNCH(kBF16, 128) : TS_LAUNCH(kF16, 128);
 #undef TS_LAUNCH
   return cudaErrorInvalidValue;
 }
 
+cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, cudaStream_t stream) {
+  if (n_blocks <= 0) return cudaSuccess;
+  expand_block_meta_kernel<<<static_cast<unsigned>((n_blocks + 3) / 4), 256, 0, stream>>>(blocks, n_blocks, meta);
+  return cudaGetLastError();
+}
+
 #ifdef TS_KERNEL_TRACE
-cudaError_t masked_gemm_read_trace(long long* out64, bool clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(out64, g_trace, sizeof(long long) * 256);
+cudaError_t masked_gemm_read_trace(long long* out, bool clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
   if (e == cudaSuccess && clear) {
-    long long z[256] = {};
-    e = cudaMemcpyToSymbol(g_trace, z, sizeof(z));
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_trace);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(g_trace));
   }
   return e;
 }

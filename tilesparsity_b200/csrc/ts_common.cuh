@@ -79,9 +79,8 @@ struct EpilogueArgs {
   uint16_t* peers[7];
 };
 
-// One 64-row K block of a work unit, as the activation-gather warps consume it.  A CTA's blocks are
-// stored in processing order, so a gather warp addresses its descriptors by block number alone and
-// can request them, and the kept-row indices they point at, several blocks ahead.
+// One 64-row K block of a work unit.  A CTA's blocks are stored in processing order; the host
+// builds these descriptors and a small kernel resolves them into the records the gather warps read.
 //   meta: bits 0-6 number of valid rows (1..64), bit 7 relative-offset lists, bits 8-9 the unit's
 //   batch rows in 64-row groups minus one, bits 10-31 position of the block's first row inside the
 //   tile's list; 0xFFFFFFFF marks the end of the CTA's stream.
@@ -92,6 +91,9 @@ struct alignas(16) BlockDesc {
 };
 static_assert(sizeof(BlockDesc) == 16, "BlockDesc is copied as one 16-byte word");
 constexpr uint32_t kBlockEnd = 0xFFFFFFFFu;
+// The gather warps read a block as one resolved record of kBlockMetaInts ints: {m0, meta, 0, 0}
+// followed by the 64 rows of At the block gathers.
+constexpr int kBlockMetaInts = 4 + 64;
 
 // ---------------------------------------------------------------------------------------------
 // Generic helpers
@@ -255,18 +257,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
       "%3}], [%4];" ::"r"(dst),
       "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-
-// TMA gather: rows r0..r3 of a 2-D tensor, `box` columns starting at column x, land as four
-// consecutive rows at dst (the tensor map's box is {columns, 1}).  Rows or columns outside the
-// tensor read as zeros and still count towards the transaction bytes.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int x, int r0, int r1,
-                                            int r2, int r3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
       : "memory");
 }
 

@@ -12,20 +12,20 @@ namespace ts {
 
 // Tensor-core masked GEMM (masked_gemm_sm100.cu).  `sched` holds rounds*grid work items; entry
 // r*grid + b is the r-th unit of CTA b (tile < 0: none, and none after it).  unit_rows is the
-// number of batch rows per work unit the schedule was built for: 128 or 256.  `blocks` is the same
-// schedule at K-block granularity: CTA b's 64-row blocks in processing order at
-// blocks[b*blk_stride ...], terminated (and padded to blk_stride) by end markers.
-// tma_rows of every 64-row K block are gathered by the copy engine (tile::gather4 through tmap_a, a
-// tensor map over At [K][lda] with box 64 x 1 and 128-byte swizzle; K_oob is a row index outside the
-// tensor, used for zero fill), the others by cp.async.  Supported: 0 (all cp.async) and 64 (all TMA).
+// number of batch rows per work unit the schedule was built for: 128 or 256.  `block_meta` is the
+// same schedule at K-block granularity: CTA b's 64-row blocks in processing order, one record of
+// kBlockMetaInts ints each, at block_meta[b*blk_stride*kBlockMetaInts ...], terminated (and padded
+// to blk_stride records) by end markers; expand_block_meta_launch writes it from the descriptors.
 // tmap_c != nullptr enables TMA stores (tensor map over Ct [N][ldc], box 64 x 128, 128-byte swizzle)
-// for the work items whose pad_ flag says their kept columns are consecutive rows of Ct.
-cudaError_t masked_gemm_launch(int dtype, int unit_rows, int tma_rows, const CUtensorMap& tmap_w,
-                               const CUtensorMap* tmap_a, const CUtensorMap* tmap_c, int K_oob,
-                               const WorkItem* sched, int rounds,
-                               int grid, const BlockDesc* blocks, int blk_stride, const void* At,
-                               long long lda, void* Ct, long long ldc, int M, const EpilogueArgs& ep,
-                               int* status, cudaStream_t stream);
+// for the work items whose flags say their kept columns are consecutive rows of Ct.
+cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w, const CUtensorMap* tmap_c,
+                               const WorkItem* sched, int rounds, int grid, const int* block_meta,
+                               int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
+                               const EpilogueArgs& ep, int* status, cudaStream_t stream);
+
+// meta[b*kBlockMetaInts ...] = record of block b, for all n_blocks (= grid*blk_stride) descriptors:
+// resolves the kept-row lists, relative or absolute, into row numbers of At.
+cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, cudaStream_t stream);
 
 #ifdef TS_KERNEL_TRACE
 cudaError_t masked_gemm_read_trace(long long* out64, bool clear);
