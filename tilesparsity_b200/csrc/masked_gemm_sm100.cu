@@ -20,12 +20,11 @@
 // activation rows are the MN-major B operand, fetched with 16-byte cp.async into the same swizzle
 // pattern (one kept row is one contiguous 2*MT-byte global segment).
 //
-// Pipeline: four stages, one per gather warp.  Gather warp g copies the 64 rows of K blocks g, g+4,
-// g+8, ... of the CTA's block stream into stage g, so a warp's bookkeeping (one shared-memory record
-// per block: descriptor + 64 resolved row numbers, prefetched by cp.async one block ahead) is paid
-// once per block per warp while the other three warps keep the load/store unit busy.  Each lane
-// hands its copies to the stage's mbarrier with cp.async.mbarrier.arrive, so a stage is released to
-// the MMA warp the moment its bytes have landed.  Accumulators live in TMEM, double buffered: the
+// Pipeline: four stages of 64 kept rows (six for 128-row units).  The four gather warps fill every
+// block together, a quarter of its rows each; all a warp needs to know about a block is one
+// shared-memory record (descriptor + 64 resolved row numbers) that it prefetched by cp.async during
+// the block before.  Each lane hands its copies to the stage's mbarrier with
+// cp.async.mbarrier.arrive, so a stage is released to the MMA warp the moment its bytes have landed.  Accumulators live in TMEM, double buffered: the
 // epilogue of one work unit overlaps the main loop of the next.  Eight epilogue warps (two per TMEM
 // lane quarter; each half of them takes every other 64-column group of the unit) convert their rows
 // to 16 bit into a 128-byte-swizzled 16 KiB staging group per half.  When the tile's kept columns
@@ -51,9 +50,20 @@ constexpr int kEpiThreads = 256;
 constexpr uint32_t kASbo = 1024;         // bytes between 8-row K groups of the gathered operand
 constexpr uint32_t kALbo = kKB * 128;    // bytes between its 64-column batch groups
 constexpr uint32_t kWSbo = 1024;         // bytes between 8-row groups of the weight operand
-constexpr int kStages = 4;               // one per gather warp
+constexpr int kMaxStages = 6;
 constexpr int kGW = 4;                   // gather warps
+// Gather warps that share one K block (1, 2 or 4).  Measured on B200: 4 is best or within 3 % of the
+// best on every workload tried (1 loses up to 30 % where the activations stream from DRAM, because
+// the blocks of different warps then land out of order and the MMA warp consumes them in order).
+#ifndef TS_WARPS_PER_BLOCK
+#define TS_WARPS_PER_BLOCK 4
+#endif
+constexpr int kWarpsPerBlock = TS_WARPS_PER_BLOCK;
+constexpr int kWarpGroups = kGW / kWarpsPerBlock;    // group p of warps takes blocks p, p+kWarpGroups, ...
+constexpr int kRowsPerWarp = kKB / kWarpsPerBlock;
 constexpr int kMetaInts = kBlockMetaInts;  // one block record: {m0, meta, 0, 0} + 64 row numbers
+constexpr int kAhead = 4;                // a warp requests its part of a record this many of its blocks ahead
+constexpr int kMetaSlots = 6;            // ring slots per warp (> kAhead)
 
 // Optional time-stamp trace (debug builds only: -DTS_KERNEL_TRACE).  Every CTA keeps 64 stamps in
 // shared memory (globaltimer nanoseconds; slot i is written the first time the CTA passes trace
@@ -87,14 +97,15 @@ __device__ __forceinline__ long long trace_now() {
 #endif
 
 struct Barriers {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  // Per gather warp: two block records (the one being copied, the one being prefetched).
-  alignas(16) int meta_ring[kGW][2][kMetaInts];
+  // Per gather warp: ring of the parts of the coming blocks' records that the warp needs: the
+  // descriptor words and the row numbers of its slice.
+  alignas(16) int meta_ring[kGW][kMetaSlots][4 + kRowsPerWarp];
 #ifdef TS_KERNEL_TRACE
   long long trace[64];
 #endif
@@ -103,6 +114,11 @@ struct Barriers {
 // Compile-time shape of one kernel variant: MT batch rows per work unit.
 template <int MT>
 struct Cfg {
+  // As many stages as fit beside the staging groups in 227 KiB.  A warp group must never run two
+  // phases of one stage ahead of the MMA warp (the parity wait could not tell them apart), which
+  // holds as long as there are at least as many stages as warp groups.
+  static constexpr int kStages = MT == 256 ? 4 : 6;
+  static_assert(kStages <= kMaxStages && kStages >= kWarpGroups, "stage count");
   static constexpr int kABytes = kKB * MT * 2;
   static constexpr int kStageBytes = kWBytes + kABytes;
   static constexpr int kEpiGroupBytes = kNT * 128;   // staging: one 128-row x 64-column swizzled group
@@ -172,6 +188,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    int* __restrict__ status) {
   const float alpha = ep.alpha, beta = ep.beta;
   using C = Cfg<MT>;
+  constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the swizzle pattern is a function of the shared-memory address bits.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -200,15 +217,24 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   WorkItem w = fetch_item(sched, rounds, grid, cta, 0);
   const int gw = warp - 2;                                  // gather warp number (warps 2..5)
   const int* recs = block_meta + static_cast<size_t>(cta) * blk_stride * kMetaInts;
+  // lanes 0..: one 16-byte piece each: the descriptor, then the warp's slice of the row numbers
+  const int meta_piece = lane == 0 ? 0 : 4 + (gw % kWarpsPerBlock) * kRowsPerWarp + (lane - 1) * 4;
+  constexpr int kMetaLanes = 1 + kRowsPerWarp / 4;
   if (warp >= 2 && warp < 6) {
-    if (lane < kMetaInts / 4) cp_async_16_ca(smem_u32(&bars->meta_ring[gw][0][lane * 4]), recs + gw * kMetaInts + lane * 4);
-    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      if (lane < kMetaLanes) {
+        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][i][lane * 4]),
+                       recs + static_cast<size_t>(gw / kWarpsPerBlock + i * kWarpGroups) * kMetaInts + meta_piece);
+      }
+      cp_async_commit();
+    }
   }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      // weight TMA thread + the 32 cp.async lanes of the stage's gather warp
-      mbar_init(smem_u32(&bars->full[s]), 1 + 32);
+      // weight TMA thread + the cp.async lanes of the warps that fill the stage
+      mbar_init(smem_u32(&bars->full[s]), 1 + 32 * kWarpsPerBlock);
       mbar_init(smem_u32(&bars->empty[s]), 1);       // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
@@ -312,35 +338,29 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ activation gather
-    // Warp gw owns stage gw and the blocks gw, gw+4, ... of the CTA's stream.  Per block: wait for
-    // its record (prefetched during the previous block), wait for the stage, issue the 64 rows in
-    // four batches of 16 (row numbers read from the record into registers before the batch goes
-    // out: a shared-memory read between two copies would serialise them), hand the copies to the
-    // stage's barrier.  One cp.async group is committed per block, made of the previous block's row
-    // copies and the next record's request; "all but the latest group have completed" therefore
-    // says that this block's record has landed while the previous block's rows may still be in
-    // flight.
+    // kWarpsPerBlock warps share one block (a slice of its rows each); group p of warps takes the
+    // blocks p, p+kWarpGroups, ... of the CTA's stream, block j lives in stage j % kStages.  Per block: wait
+    // for its record (requested kAhead blocks earlier), wait for the stage, issue the
+    // warp's rows in one burst (row numbers read from the record into registers first: a
+    // shared-memory read between two copies stalls the warp until the load/store unit has taken the
+    // copies before it), hand the copies to the stage's barrier.  One cp.async group is committed
+    // per block, made of the block's row copies and the request for the record kAhead blocks on;
+    // "all but the latest kAhead - 1 groups have completed" therefore says that this block's
+    // record has landed while the rows of the kAhead - 1 blocks before it may still be in flight.
     constexpr int kLpr = C::kLanesPerRow, kRpi = C::kRowsPerInstr;
     const int chunk = lane % kLpr, sub = lane / kLpr;
     const int g = chunk >> 3, c = chunk & 7;
-    const uint32_t s = static_cast<uint32_t>(gw);
-    const uint32_t dst0 = smem_u32(smem + s * C::kStageBytes + kWBytes) + g * kALbo;
-    const uint32_t bar = smem_u32(&bars->full[s]);
-    const uint32_t empty_bar = smem_u32(&bars->empty[s]);
+    const int grp = gw / kWarpsPerBlock;                    // group of warps this warp belongs to
+    const int row_base = (gw % kWarpsPerBlock) * kRowsPerWarp;   // first row of the warp's slice
     // The schedule is static; the activations may be the previous kernel's output: wait for it
     // before the first row is copied.
     grid_dependency_wait();
 
     for (uint32_t it = 0;; ++it) {
-      const int j = gw + static_cast<int>(it) * kGW;
-      if (lane < kMetaInts / 4) {
-        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][(it + 1) & 1][lane * 4]),
-                       recs + static_cast<size_t>(j + kGW) * kMetaInts + lane * 4);
-      }
-      cp_async_commit();
-      cp_async_wait_group<1>();
+      const int j = grp + static_cast<int>(it) * kWarpGroups;
+      cp_async_wait_group<kAhead - 1>();
       __syncwarp();
-      const int* rec = bars->meta_ring[gw][it & 1];
+      const int* rec = bars->meta_ring[gw][it % kMetaSlots];
       const int m0 = rec[0];
       const uint32_t meta = static_cast<uint32_t>(rec[1]);
       if (meta == kBlockEnd) break;
@@ -351,14 +371,15 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const uint16_t* src_col = At + (m_ok ? m : 0);
       const bool lane_live = chunk * 8 < m_len;             // columns past the unit are never read
       const bool full_block = nv == kKB && m0 + m_len <= M;
-      if (!mbar_wait(empty_bar, (it & 1u) ^ 1u, abort_flag)) break;
-      TS_TRACE(52 + j, lane == 0);   // stage acquired for block j
-      // All 64 row numbers go to registers before the first copy is issued: a shared-memory read
-      // between two copies stalls the warp until the copies before it have been taken by the
-      // load/store unit.
-      int rr[kKB];
+      const uint32_t s = static_cast<uint32_t>(j) % kStages;
+      const uint32_t ph = (static_cast<uint32_t>(j) / kStages) & 1u;
+      const uint32_t dst0 = smem_u32(smem + s * C::kStageBytes + kWBytes) + g * kALbo;
+      const uint32_t bar = smem_u32(&bars->full[s]);
+      if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag)) break;
+      TS_TRACE(52 + j, lane == 0 && row_base == 0);   // stage acquired for block j
+      int rr[kRowsPerWarp];
 #pragma unroll
-      for (int q4 = 0; q4 < kKB / 4; ++q4) {
+      for (int q4 = 0; q4 < kRowsPerWarp / 4; ++q4) {
         const int4 v = reinterpret_cast<const int4*>(rec + 4)[q4];
         rr[q4 * 4] = v.x;
         rr[q4 * 4 + 1] = v.y;
@@ -370,8 +391,8 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       if (full_block) {
         if (lane_live) {
 #pragma unroll
-          for (int e = 0; e < kKB / kRpi; ++e) {
-            const int row = e * kRpi + sub;
+          for (int e = 0; e < kRowsPerWarp / kRpi; ++e) {
+            const int row = row_base + e * kRpi + sub;
             int kr;
             if constexpr (kRpi == 1) {
               kr = rr[e];
@@ -380,13 +401,12 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             }
             cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
                              src_col + static_cast<long long>(kr) * lda);
-            if ((e & 15) == 15) TS_TRACE(4 + (e >> 4), lane == 0 && gw == 0 && it == 0);
           }
         }
       } else if (lane_live) {
 #pragma unroll
-        for (int e = 0; e < kKB / kRpi; ++e) {
-          const int row = e * kRpi + sub;
+        for (int e = 0; e < kRowsPerWarp / kRpi; ++e) {
+          const int row = row_base + e * kRpi + sub;
           int kr;
           if constexpr (kRpi == 1) {
             kr = rr[e];
@@ -399,7 +419,13 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
       }
       cp_async_arrive_noinc(bar);
-      TS_TRACE(28 + j, lane == 0 && j < 8);   // copies of block j issued
+      // request the warp's part of the record kAhead of its blocks ahead; one group per block
+      if (lane < kMetaLanes) {
+        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][(it + kAhead) % kMetaSlots][lane * 4]),
+                       recs + static_cast<size_t>(j + kAhead * kWarpGroups) * kMetaInts + meta_piece);
+      }
+      cp_async_commit();
+      TS_TRACE(28 + j, lane == 0 && j < 8 && row_base == 0);   // copies of block j issued
     }
     cp_async_wait_all();  // nothing of this thread is in flight when the CTA retires
   } else if (warp >= 6) {
