@@ -588,7 +588,7 @@ int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* C
   }
   TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, l->tmap, tst ? &tmap_c : nullptr, s->d_units, s->rounds,
                                  s->grid, s->d_meta, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
-                                 static_cast<cudaStream_t>(stream)));
+                                 /*early_start=*/true, static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
 
@@ -799,7 +799,7 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   ep.alpha = alpha;
   ep.beta = beta;
   TS_CUDA(ts::masked_gemm_launch(dtype, unit_rows, tmap, nullptr, ws.d_units, rounds, grid,
-                                 ws.d_meta, blk_stride, A, M, C, M, M, ep, ws.d_status, s));
+                                 ws.d_meta, blk_stride, A, M, C, M, M, ep, ws.d_status, /*early_start=*/false, s));
   return TS_OK;
 }
 

@@ -17,11 +17,13 @@ namespace ts {
 // kBlockMetaInts ints each, at block_meta[b*blk_stride*kBlockMetaInts ...], terminated (and padded
 // to blk_stride records) by end markers; expand_block_meta_launch writes it from the descriptors.
 // tmap_c != nullptr enables TMA stores (tensor map over Ct [N][ldc], box 64 x 128, 128-byte swizzle)
-// for the work items whose flags say their kept columns are consecutive rows of Ct.
+// for the work items whose flags say their kept columns are consecutive rows of Ct.  early_start
+// allows programmatic dependent launch: the kernel reads sched and block_meta before it waits for the
+// kernel before it in the stream, so it must be false when that kernel wrote them.
 cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w, const CUtensorMap* tmap_c,
                                const WorkItem* sched, int rounds, int grid, const int* block_meta,
                                int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
-                               const EpilogueArgs& ep, int* status, cudaStream_t stream);
+                               const EpilogueArgs& ep, int* status, bool early_start, cudaStream_t stream);
 
 // meta[b*kBlockMetaInts ...] = record of block b, for all n_blocks (= grid*blk_stride) descriptors:
 // resolves the kept-row lists, relative or absolute, into row numbers of At.

