@@ -221,8 +221,20 @@ def cpu_reference_pass(sample_steps: int, budget_s: float, masks: str = "tw1"):
     except Exception:
         cores = os.cpu_count() or 1
     t = float(np.median(times))
+    # one step with the BLAS pool limited to a single thread, for a per-core figure
+    t_one = None
+    try:
+        from threadpoolctl import threadpool_limits
+        with threadpool_limits(limits=1):
+            t0 = time.perf_counter()
+            for A, W, mask in items:
+                og.masked_matmul_dense(A, W, mask)
+            t_one = time.perf_counter() - t0
+    except Exception:
+        t_one = None
     return {"value": kept / t / 1e12, "seconds_per_step": t, "steps_run": len(times), "cores": int(cores),
-            "kept_flops": kept, "mask_build_seconds": t_mask}
+            "kept_flops": kept, "mask_build_seconds": t_mask,
+            "value_one_thread": (kept / t_one / 1e12) if t_one else None}
 
 
 def run_reference(args):
@@ -237,7 +249,8 @@ def run_reference(args):
         "warmup": args.warmup, "ms_per_step": r["seconds_per_step"] * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
         "config": {"workload": f"bert_base_layer_m{M_ROWS}_tw75_g{G}", "gemms": list(GEMMS), "masks": args.masks},
-        "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port", "sample": sample,
+                         "value_one_thread": r["value_one_thread"], "host_cpus": os.cpu_count()},
         "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -353,7 +366,8 @@ def run_ours(args):
             r = cpu_reference_pass(8, budget_s=25.0, masks=args.masks)
             cpu = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
                    "sample": f"{r['steps_run']} full steps of numpy fp32 A@(W*mask), 4 GEMMs at M={M_ROWS}, median",
-                   "seconds_per_step": r["seconds_per_step"], "mask_build_seconds": r["mask_build_seconds"]}
+                   "seconds_per_step": r["seconds_per_step"], "mask_build_seconds": r["mask_build_seconds"],
+                   "value_one_thread": r["value_one_thread"], "host_cpus": os.cpu_count()}
 
     if rank == 0:
         t_launch = (sum(p["us"] for p in per_gemm) / len(per_gemm)) * 1e-6

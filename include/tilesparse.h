@@ -239,6 +239,23 @@ int ts_order_statistics(const float* vals_dev, int64_t n, int64_t rank_lo, int64
 /* np.percentile(vals, q) (method "linear") of n float32 values on the device; q_is_f64 as above. */
 int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, double* out, void* stream);
 
+/* The reference's baseline patterns next to the tile-wise ones (pruning_fun names "ew" and "vw",
+ * Pruning/VGG/prune_algo.py:267-278).  "bw" (block-wise, :229-264) is not offered: its block norms
+ * come out of BLAS sdot, whose summation order depends on the host CPU, so there is nothing fixed to
+ * be identical to. */
+#define TS_PATTERN_EW 0 /* element_wise, prune_algo.py:38-53: |score| above one percentile of all layers */
+#define TS_PATTERN_VW 1 /* vector_vise, prune_algo.py:196-227: top-k inside blocks of 16 rows of a column */
+
+/* Builds element-wise or vector-wise masks on the GPU, bit-identical to
+ * pruning_fun("ew" | "vw")(scores, sparsity) of the reference with NumPy 2.3.
+ *   scores_dev[l]  float32 [Ks[l]][lds[l]] (lds NULL: dense rows)
+ *   masks_dev[l]   uint8 [Ks[l]][ld_masks[l]] (ld_masks NULL: dense rows), receives 0/1
+ *   threshold_out  optional: the element-wise threshold (NaN for vector-wise)
+ * Allocates device scratch for "ew", synchronises `stream`, returns when the masks are complete. */
+int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                          const int64_t* lds, double sparsity, uint8_t* const* masks_dev, const int64_t* ld_masks,
+                          double* threshold_out, void* stream);
+
 /* Row stage of "tw1" for ONE weight matrix without any allocation: keep_dev[t*K + k] = 1 when row k
  * of column tile t (tiles of G columns, narrow last tile) survives, i.e. when its L2 norm / width lies
  * strictly above the `sparsity` percentile of all tile-row norms of the matrix -- the same flags

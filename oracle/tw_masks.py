@@ -171,11 +171,60 @@ def topk_l1(score, sparsity, granularity=128):
     return _broadcast_rows(keep, bounds, K)
 
 
-ALGOS = {"tw1": tw1, "tw2": tw2, "tw1m": tw1m, "tw2m": tw2m}
+def ew(scores, sparsity):
+    """Element-wise baseline (prune_algo.py:38-53): one percentile over |score| of all layers.  The
+    reference flattens through Python lists, so the percentile runs on float64 copies of the float32
+    values and the threshold is a float64; `abs(layer) > threshold` compares exactly."""
+    flat = np.concatenate([np.abs(np.asarray(l)).reshape(-1).astype(np.float64) for l in scores])
+    thr = percentile_f64(flat, float(sparsity))
+    return [np.abs(np.asarray(l)) > thr for l in scores]
+
+
+def vw(scores, sparsity):
+    """Vector-wise baseline (prune_algo.py:196-227): along K, in blocks of 16 rows of one column,
+    keep what exceeds the block's (topk+1)-th largest value, topk = int((1 - sparsity/100) * 16); a
+    block no longer than topk+1 keeps what exceeds 0.  Returns float64 0/1 arrays like the reference."""
+    block = 16
+    topk = int((1 - sparsity / 100) * block)
+    out = []
+    for layer in scores:
+        sc = np.asarray(layer)
+        K, N = sc.shape
+        mask = np.zeros((K, N))
+        for k0 in range(0, K, block):
+            blk = sc[k0:k0 + block]                              # [len, N]
+            if topk + 1 < blk.shape[0]:
+                thr = np.sort(blk, axis=0)[-(topk + 1)]          # per column
+            else:
+                thr = np.zeros(N, dtype=sc.dtype)
+            mask[k0:k0 + block] = blk > thr[None, :]
+        out.append(mask)
+    return out
+
+
+def percentile_f64(values, q):
+    """np.percentile(float64 array, Python float q), method 'linear', step by step in double."""
+    v = np.sort(np.asarray(values, dtype=np.float64))
+    n = len(v)
+    virt = np.float64(n - 1) * (np.float64(q) / np.float64(100))
+    prev = np.floor(virt)
+    gamma = np.float64(virt - prev)
+    pi, ni = int(prev), int(prev) + 1
+    if virt >= n - 1:
+        pi = ni = n - 1
+    a, b = v[pi], v[ni]
+    diff = np.float64(b - a)
+    if gamma >= 0.5:
+        return np.float64(b - diff * (np.float64(1) - gamma))
+    return np.float64(a + diff * gamma)
+
+
+ALGOS = {"tw1": tw1, "tw2": tw2, "tw1m": tw1m, "tw2m": tw2m, "ew": ew, "vw": vw}
 
 
 def pruning_fun(name):
-    """Same dispatch as the reference (prune_algo.py:267-278), TW/TEW names only."""
+    """Same dispatch as the reference (prune_algo.py:267-278); `bw` is not restated (its block
+    norms go through BLAS sdot, whose summation order depends on the host CPU)."""
     return ALGOS[name]
 
 

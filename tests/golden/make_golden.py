@@ -33,6 +33,13 @@ CASES = {
     "tw1m_small":       ("tw1m", [(96, 320)], 70.0, 128, 5.0, 31, "normal"),
     "tw1m_lstm":        ("tw1m", [(256, 512), (128, 512)], 75.0, 128, 1.5, 32, "uniform"),
     "tw2m_small":       ("tw2m", [(96, 384)], 70.0, 128, 1.0, 41, "normal"),
+    # baseline patterns (no granularity argument): element-wise and vector-wise
+    "ew_small":         ("ew", [(96, 320)], 75.0, None, None, 51, "normal"),
+    "ew_group":         ("ew", [(64, 256), (80, 200), (48, 130)], 62.5, None, None, 52, "normal"),
+    "ew_bert_attn":     ("ew", [(768, 768)], 90.0, None, None, 2002, "bert"),
+    "vw_small":         ("vw", [(96, 320)], 75.0, None, None, 61, "normal"),
+    "vw_ragged":        ("vw", [(70, 130), (16, 40), (9, 33)], 50.0, None, None, 62, "uniform"),
+    "vw_90":            ("vw", [(128, 96)], 90.0, None, None, 63, "normal"),
 }
 
 
@@ -67,7 +74,10 @@ def main():
     for name, (algo, shapes, sparsity, gran, g1, seed, dist) in CASES.items():
         scores = case_inputs(name)
         fn = prune_algo.pruning_fun(algo)
-        masks = fn(scores, sparsity, gran) if g1 is None else fn(scores, sparsity, gran, g1)
+        if gran is None:
+            masks = fn(scores, sparsity)
+        else:
+            masks = fn(scores, sparsity, gran) if g1 is None else fn(scores, sparsity, gran, g1)
         for i, m in enumerate(masks):
             m = np.asarray(m).astype(bool)
             store[f"{name}/{i}/shape"] = np.asarray(m.shape, dtype=np.int32)

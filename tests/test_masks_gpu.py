@@ -14,7 +14,46 @@ def _gpu_masks(algo, scores, sparsity, gran, g1):
     return tm.build_mask(algo, scores, sparsity, gran, g1, want_residual=algo.endswith("m"))
 
 
-@pytest.mark.parametrize("name", sorted(CASES))
+TILE_CASES = sorted(n for n in CASES if CASES[n][0] not in ("ew", "vw"))
+PATTERN_CASES = sorted(n for n in CASES if CASES[n][0] in ("ew", "vw"))
+
+
+@pytest.mark.parametrize("name", PATTERN_CASES)
+def test_pattern_masks_match_reference_golden(name):
+    """Element-wise and vector-wise baselines: bit for bit the reference's masks, through the same
+    pruning_fun(name)(scores, sparsity) call the reference's hooks make."""
+    from tilesparsity_b200 import masks as tm
+    algo, shapes, sparsity, _, _, _, _ = CASES[name]
+    scores = case_inputs(name)
+    got = tm.pruning_fun(algo)(scores, sparsity)
+    gold = load_golden(name)
+    assert len(got) == len(gold)
+    for m, g in zip(got, gold):
+        assert m.shape == g.shape
+        assert m.dtype == (np.float64 if algo == "vw" else np.bool_)
+        assert np.array_equal(m.astype(bool), g), f"{name}: {int((m.astype(bool) != g).sum())} mask bits differ"
+
+
+@pytest.mark.parametrize("algo,sparsity,shapes,seed", [
+    ("ew", 75.0, [(256, 1024)], 71), ("ew", 33.3, [(100, 257), (64, 96)], 72), ("ew", 0.0, [(32, 48)], 73),
+    ("ew", 100.0, [(32, 48)], 74), ("vw", 75.0, [(256, 1024)], 75), ("vw", 87.5, [(100, 257)], 76),
+    ("vw", 10.0, [(40, 64)], 77), ("vw", 50.0, [(5, 33)], 78),
+])
+def test_pattern_masks_match_oracle(algo, sparsity, shapes, seed):
+    from tilesparsity_b200 import masks as tm
+    g = np.random.Generator(np.random.PCG64(seed))
+    scores = [np.abs(g.standard_normal(s, dtype=np.float32)) for s in shapes]
+    scores[0][:3, :5] = scores[0][0, 0]              # duplicates around the ranks
+    ref = om.pruning_fun(algo)(scores, sparsity)
+    got, thr = tm.build_pattern_mask(algo, scores, sparsity)
+    for a, b in zip(got, ref):
+        assert np.array_equal(a.cpu().numpy(), np.asarray(b).astype(bool))
+    if algo == "ew":
+        flat = np.concatenate([s.reshape(-1).astype(np.float64) for s in scores])
+        assert thr == float(np.percentile(flat, sparsity))
+
+
+@pytest.mark.parametrize("name", TILE_CASES)
 def test_matches_reference_golden(name):
     algo, shapes, sparsity, gran, g1, seed, dist = CASES[name]
     scores = case_inputs(name)
@@ -27,7 +66,7 @@ def test_matches_reference_golden(name):
         assert np.array_equal(got, g), f"{name}: {int((got != g).sum())} mask bits differ from the reference"
 
 
-@pytest.mark.parametrize("name", sorted(CASES))
+@pytest.mark.parametrize("name", TILE_CASES)
 def test_tile_lists_describe_the_mask(name):
     algo, shapes, sparsity, gran, g1, seed, dist = CASES[name]
     scores = case_inputs(name)

@@ -14,7 +14,10 @@ def test_oracle_reproduces_reference_masks(name):
     algo, shapes, sparsity, gran, g1, seed, dist = CASES[name]
     scores = case_inputs(name)
     fn = om.pruning_fun(algo)
-    mine = fn(scores, sparsity, gran) if g1 is None else fn(scores, sparsity, gran, g1)
+    if gran is None:
+        mine = fn(scores, sparsity)
+    else:
+        mine = fn(scores, sparsity, gran) if g1 is None else fn(scores, sparsity, gran, g1)
     gold = load_golden(name)
     assert len(mine) == len(gold)
     for a, b in zip(mine, gold):

@@ -21,6 +21,9 @@ MASK_MODES = {"tw1": 0, "tw2": 1, "tw1m": 2, "tw2m": 3, "bert_type2": 4, "bert_t
               "topk_l1": 7}
 
 
+PATTERN_MODES = {"ew": 0, "vw": 1}
+
+
 class TileSparseError(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"libtilesparse error {code}: {message}")
@@ -76,6 +79,8 @@ SIGNATURES = {
     "ts_mask_result_thresholds": (C.c_int, [_vp, C.POINTER(C.c_double)]),
     "ts_mask_result_destroy": (C.c_int, [_vp]),
     "ts_order_statistics": (C.c_int, [_vp, C.c_int64, C.c_int64, C.c_int64, C.POINTER(C.c_float), _vp]),
+    "ts_build_pattern_mask": (C.c_int, [C.c_int, C.c_int, C.POINTER(_vp), C.POINTER(C.c_int), C.POINTER(C.c_int), _i64p,
+                                        C.c_double, C.POINTER(_vp), _i64p, C.POINTER(C.c_double), _vp]),
     "ts_percentile_f32": (C.c_int, [_vp, C.c_int64, C.c_double, C.c_int, C.POINTER(C.c_double), _vp]),
     "ts_tw1_row_keep_noalloc": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_double, C.c_int, _vp,
                                           C.POINTER(C.c_double), _vp]),

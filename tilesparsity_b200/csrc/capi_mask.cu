@@ -687,6 +687,76 @@ int ts_tw1_row_keep_noalloc(const float* score_dev, int64_t ld, int K, int N, in
   return TS_OK;
 }
 
+int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                          const int64_t* lds, double sparsity, uint8_t* const* masks_dev, const int64_t* ld_masks,
+                          double* threshold_out, void* stream) {
+  if (pattern != TS_PATTERN_EW && pattern != TS_PATTERN_VW) return ts_internal_fail(TS_ERR_INVALID, "unknown pattern %d", pattern);
+  if (n_layers <= 0 || !scores_dev || !Ks || !Ns || !masks_dev) return ts_internal_fail(TS_ERR_INVALID, "NULL or empty argument");
+  if (!(sparsity >= 0.0 && sparsity <= 100.0)) return ts_internal_fail(TS_ERR_INVALID, "sparsity=%g must be in [0, 100]", sparsity);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  long long total = 0;
+  for (int l = 0; l < n_layers; ++l) {
+    if (!scores_dev[l] || !masks_dev[l] || Ks[l] <= 0 || Ns[l] <= 0) return ts_internal_fail(TS_ERR_INVALID, "layer %d: bad argument", l);
+    if ((lds && lds[l] < Ns[l]) || (ld_masks && ld_masks[l] < Ns[l])) return ts_internal_fail(TS_ERR_INVALID, "layer %d: leading dimension too small", l);
+    total += static_cast<long long>(Ks[l]) * Ns[l];
+  }
+  if (threshold_out) *threshold_out = std::nan("");
+  if (pattern == TS_PATTERN_VW) {
+    // topk = int((1 - sparsity/100) * 16), in the double arithmetic of the Python expression
+    volatile double frac = 1.0 - sparsity / 100.0;
+    volatile double scaled = frac * 16.0;
+    const int topk = static_cast<int>(scaled);
+    for (int l = 0; l < n_layers; ++l) {
+      TSM_CUDA(ts::vw_mask_launch(static_cast<const float*>(scores_dev[l]), lds ? lds[l] : Ns[l], Ks[l], Ns[l], topk,
+                                  masks_dev[l], ld_masks ? ld_masks[l] : Ns[l], s));
+    }
+    TSM_CUDA(cudaStreamSynchronize(s));
+    return TS_OK;
+  }
+  // element-wise: one percentile over |score| of all layers.  The reference flattens through Python
+  // lists, so the values are float64 copies of the float32 elements and every step of the
+  // percentile, the difference of the two order statistics included, is a double operation.
+  Arena arena;
+  Scratch sc;
+  TSM_OK(arena.alloc(&sc.hist, 256));
+  TSM_OK(arena.alloc(&sc.count, 1));
+  TSM_OK(arena.alloc(&sc.min_gt, 1));
+  float* vals = nullptr;
+  TSM_OK(arena.alloc(&vals, static_cast<size_t>(total)));
+  long long off = 0;
+  for (int l = 0; l < n_layers; ++l) {
+    TSM_CUDA(ts::abs_values_launch(static_cast<const float*>(scores_dev[l]), lds ? lds[l] : Ns[l], Ks[l], Ns[l],
+                                   vals + off, s));
+    off += static_cast<long long>(Ks[l]) * Ns[l];
+  }
+  const Ranks r = percentile_ranks(total, sparsity, /*wide=*/true);
+  float a = 0, b = 0;
+  TSM_OK(order_statistics(vals, total, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s));
+  volatile double diff = static_cast<double>(b) - static_cast<double>(a);
+  volatile double thr = static_cast<double>(a) + diff * r.gamma_d;
+  if (r.gamma_d >= 0.5) {
+    volatile double omt = 1.0 - r.gamma_d;
+    thr = static_cast<double>(b) - diff * omt;
+  }
+  if (threshold_out) *threshold_out = thr;
+  off = 0;
+  for (int l = 0; l < n_layers; ++l) {
+    const long long n_el = static_cast<long long>(Ks[l]) * Ns[l];
+    const long long ldm = ld_masks ? ld_masks[l] : Ns[l];
+    if (ldm == Ns[l]) {
+      TSM_CUDA(ts::threshold_launch(vals + off, n_el, thr, masks_dev[l], s));
+    } else {
+      for (int k = 0; k < Ks[l]; ++k) {
+        TSM_CUDA(ts::threshold_launch(vals + off + static_cast<long long>(k) * Ns[l], Ns[l], thr,
+                                      masks_dev[l] + static_cast<long long>(k) * ldm, s));
+      }
+    }
+    off += n_el;
+  }
+  TSM_CUDA(cudaStreamSynchronize(s));
+  return TS_OK;
+}
+
 int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, double* out, void* stream) {
   if (!vals_dev || !out || n <= 0) return ts_internal_fail(TS_ERR_INVALID, "bad argument");
   if (!(q >= 0.0 && q <= 100.0)) return ts_internal_fail(TS_ERR_INVALID, "q=%g must be in [0, 100]", q);

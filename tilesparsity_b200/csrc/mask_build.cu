@@ -373,6 +373,55 @@ dense_mask16_kernel(const uint8_t* __restrict__ rowkeep, const uint8_t* __restri
   }
 }
 
+// vals[k*N + n] = |score[k][n]|   (element-wise baseline, prune_algo.py:38-46)
+__global__ void __launch_bounds__(256)
+abs_values_kernel(const float* __restrict__ score, long long ld, int K, int N, float* __restrict__ vals) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k = blockIdx.y;
+  if (n >= N) return;
+  vals[static_cast<long long>(k) * N + n] = fabsf(__ldg(score + static_cast<long long>(k) * ld + n));
+}
+
+// Vector-wise baseline (prune_algo.py:196-227): one thread per (block of 16 rows, column) keeps the
+// elements above the block's (topk+1)-th largest value (duplicates counted), or above 0 when the
+// block has at most topk+1 rows.
+constexpr int kVwBlock = 16;
+
+__global__ void __launch_bounds__(256)
+vw_mask_kernel(const float* __restrict__ score, long long ld, int K, int N, int topk,
+               uint8_t* __restrict__ mask, long long ld_mask) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k0 = blockIdx.y * kVwBlock;
+  if (n >= N) return;
+  const int len = min(kVwBlock, K - k0);
+  float v[kVwBlock];
+#pragma unroll
+  for (int i = 0; i < kVwBlock; ++i) {
+    v[i] = i < len ? __ldg(score + static_cast<long long>(k0 + i) * ld + n) : 0.0f;
+  }
+  float thr = 0.0f;
+  if (topk + 1 < len) {
+#pragma unroll
+    for (int i = 0; i < kVwBlock; ++i) {
+      if (i < len) {
+        int gt = 0, ge = 0;
+#pragma unroll
+        for (int j = 0; j < kVwBlock; ++j) {
+          if (j < len) {
+            gt += v[j] > v[i];
+            ge += v[j] >= v[i];
+          }
+        }
+        if (gt <= topk && topk < ge) thr = v[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kVwBlock; ++i) {
+    if (i < len) mask[static_cast<long long>(k0 + i) * ld_mask + n] = v[i] > thr ? 1 : 0;
+  }
+}
+
 // TEW ranking values: v[k*N + n] = sqrt(w*w) - mask[k][n]   (prune_algo.py:156-159)
 __global__ void __launch_bounds__(256)
 tew_values_kernel(const float* __restrict__ score, long long ld, const uint8_t* __restrict__ mask,
@@ -534,6 +583,21 @@ cudaError_t dense_mask_launch(const uint8_t* rowkeep, const uint8_t* colkeep, co
   }
   dim3 grid((N + 255) / 256, K);
   dense_mask_kernel<<<grid, 256, 0, s>>>(rowkeep, colkeep, tile_of_col, K, N, mask, ld_mask);
+  return cudaGetLastError();
+}
+
+cudaError_t abs_values_launch(const float* score, long long ld, int K, int N, float* vals, cudaStream_t s) {
+  if (K <= 0 || N <= 0) return cudaSuccess;
+  dim3 grid((N + 255) / 256, K);
+  abs_values_kernel<<<grid, 256, 0, s>>>(score, ld, K, N, vals);
+  return cudaGetLastError();
+}
+
+cudaError_t vw_mask_launch(const float* score, long long ld, int K, int N, int topk, uint8_t* mask,
+                           long long ld_mask, cudaStream_t s) {
+  if (K <= 0 || N <= 0) return cudaSuccess;
+  dim3 grid((N + 127) / 128, (K + kVwBlock - 1) / kVwBlock);
+  vw_mask_kernel<<<grid, 128, 0, s>>>(score, ld, K, N, topk, mask, ld_mask);
   return cudaGetLastError();
 }
 

@@ -33,6 +33,13 @@ cudaError_t segment_compact_launch(const uint8_t* keep, const long long* seg_ptr
                                    const int* out_ptr, int* list, cudaStream_t s);
 cudaError_t dense_mask_launch(const uint8_t* rowkeep, const uint8_t* colkeep, const int* tile_of_col,
                               int K, int N, uint8_t* mask, long long ld_mask, cudaStream_t s);
+// |score| of one layer into a dense [K][N] float array (element-wise baseline).
+cudaError_t abs_values_launch(const float* score, long long ld, int K, int N, float* vals, cudaStream_t s);
+
+// Vector-wise baseline mask: blocks of 16 rows of one column, keep above the (topk+1)-th largest.
+cudaError_t vw_mask_launch(const float* score, long long ld, int K, int N, int topk, uint8_t* mask,
+                           long long ld_mask, cudaStream_t s);
+
 cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* mask, long long ld_mask,
                               int K, int N, float* vals, cudaStream_t s);
 cudaError_t tew_apply_launch(const float* vals, double thr, int K, int N, uint8_t* mask,

@@ -103,12 +103,50 @@ def build_mask(name: str, scores, sparsity, granularity: int = 128, g1percent=No
     return MaskResult([m.bool() for m in masks], tiles, [r.bool() for r in resid] if resid else None, tuple(thr))
 
 
+def build_pattern_mask(name: str, scores, sparsity, device=None):
+    """The reference's baseline patterns on the GPU: "ew" (element-wise, prune_algo.py:38-53) and "vw"
+    (vector-wise, prune_algo.py:196-227).  Returns (list of CUDA bool masks, threshold or NaN)."""
+    if name not in _lib.PATTERN_MODES:
+        raise KeyError(f"unknown pattern {name!r} (ew, vw)")
+    if not torch.cuda.is_available():
+        raise RuntimeError("build_pattern_mask needs a CUDA device (there is no CPU fallback)")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    sc = []
+    for s in scores:
+        t = s if isinstance(s, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(s))
+        if t.dim() != 2:
+            raise ValueError("scores must be 2-D (use img2col_forward for conv kernels)")
+        t = t.to(device=dev, dtype=torch.float32)
+        sc.append(t if t.stride(1) == 1 else t.contiguous())
+    n = len(sc)
+    masks = [torch.empty((t.shape[0], t.shape[1]), dtype=torch.uint8, device=dev) for t in sc]
+    VP, IA, LA = C.c_void_p * n, C.c_int * n, C.c_int64 * n
+    thr = C.c_double()
+    with torch.cuda.device(dev):
+        check(lib.ts_build_pattern_mask(
+            _lib.PATTERN_MODES[name], n, VP(*[t.data_ptr() for t in sc]), IA(*[t.shape[0] for t in sc]),
+            IA(*[t.shape[1] for t in sc]), LA(*[t.stride(0) for t in sc]), float(sparsity),
+            VP(*[m.data_ptr() for m in masks]), LA(*[m.stride(0) for m in masks]), C.byref(thr),
+            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+    return [m.bool() for m in masks], thr.value
+
+
 def pruning_fun(pruning_type: str):
-    """Same dispatch as the reference (prune_algo.py:267-278) for the tile-wise algorithms.  The
-    returned function takes (scores, sparsity[, granularity][, g1percent]) and returns the masks as
-    NumPy bool arrays when given NumPy scores, as CUDA bool tensors otherwise."""
+    """Same dispatch as the reference (prune_algo.py:267-278): the tile-wise algorithms and the
+    element-wise / vector-wise baselines ("bw" is not offered: its block norms depend on the host
+    BLAS).  The returned function takes (scores, sparsity[, granularity][, g1percent]) and returns
+    the masks as NumPy arrays when given NumPy scores (bool; float64 0/1 for "vw", as the reference
+    does), as CUDA bool tensors otherwise."""
+    if pruning_type in ("ew", "vw"):
+        def pattern_fn(accumulated_scores, sparsity):
+            masks, _ = build_pattern_mask(pruning_type, accumulated_scores, sparsity)
+            if all(isinstance(s, np.ndarray) for s in accumulated_scores):
+                out = [m.cpu().numpy() for m in masks]
+                return [m.astype(np.float64) for m in out] if pruning_type == "vw" else out
+            return masks
+        return pattern_fn
     if pruning_type not in ("tw1", "tw2", "tw1m", "tw2m"):
-        raise KeyError(f"{pruning_type!r} is not a tile-wise algorithm (tw1, tw2, tw1m, tw2m)")
+        raise KeyError(f"{pruning_type!r} is not one of tw1, tw2, tw1m, tw2m, ew, vw")
 
     def fn(accumulated_scores, sparsity, granularity=128, g1percent=None):
         res = build_mask(pruning_type, accumulated_scores, sparsity, granularity, g1percent)

@@ -1,6 +1,6 @@
 """Sweep of the benchmark configurations: masked GEMM vs cuBLAS dense on one B200.
 
-    python -m tilesparsity_b200.sweep [--configs bert,vgg,lstm,square] [--iters 200]
+    python -m tilesparsity_b200.sweep [--configs bert,vgg,lstm,square,balance,masks] [--iters 200]
 
 For every configuration the masks are built on the GPU from seeded synthetic weights (the reference's
 algorithms, tilesparsity_b200.masks), the layer is packed, and the tensor-core masked GEMM is timed
@@ -77,6 +77,26 @@ def tw_layer(sparsity, dtype, algo="tw1"):
     return fn
 
 
+def col_then_row_layer(col_sparsity, row_sparsity, dtype):
+    """Column pruning and tile-wise row pruning with independent sparsities (the reference's tw2 ties
+    both to one remapped value, Pruning/VGG/prune_algo.py:61): columns by L2 norm, survivors regrouped
+    into tiles of 128, rows per tile by a global percentile of the tile-row norms."""
+    def fn(W):
+        K, N = W.shape
+        cn = W.norm(dim=0)
+        keep_cols = cn > torch.quantile(cn, col_sparsity / 100.0)
+        cols = torch.nonzero(keep_cols).flatten()
+        groups = list(torch.split(cols, 128))
+        norms = torch.stack([W[:, g].norm(dim=1) / len(g) for g in groups])          # [tiles, K]
+        thr = torch.quantile(norms.flatten(), row_sparsity / 100.0)
+        lists = [torch.nonzero(norms[t] > thr).flatten().cpu().numpy().astype(np.int32) for t in range(len(groups))]
+        ts = tiles_from_lists(K, N, 128, lists, col_mask=keep_cols.cpu().numpy())
+        layer = TWLayer(ts, dtype, W.device)
+        layer.pack(W)
+        return layer, ts.kept_flops_per_row(), {"tiles": ts.n_tiles}
+    return fn
+
+
 def run_mask_case(algo, K, N, sparsity, g1=None, reps=5):
     """Wall-clock of the host-synchronous mask build (scores resident on the GPU) and its HBM-level
     bytes: the scores read once per norm pass plus the dense 0/1 mask written."""
@@ -117,12 +137,21 @@ def main(argv=None):
             for nm, (K, N) in synth.BERT_BASE_LAYER.items():
                 rows.append(run_case(f"bert_{nm}_tw{int(sp)}", 4096, K, N, torch.float16, tw_layer(sp, torch.float16), a.iters))
     if "vgg" in want:
-        # conv5 as an implicit GEMM: tile-wise 75 % on K after 10 % column pruning.  The reference's
-        # tw2 ties both sparsities to one remapped value; the closest reference setting to (10 % columns,
-        # 75 % rows) is bert_type8-style independent stages, taken here as tw2 at the sparsity whose
-        # remap gives ~10 % per stage plus tw1-style row pruning is not expressible, so tw2 at 75 % is used.
+        # conv5 as a GEMM over the im2col matrix: the reference's tw2 at 75 % (both stages at the
+        # remapped 50 %), and 10 % column pruning followed by 75 % tile-wise row pruning.
         rows.append(run_case("vgg16_conv5_tw2_75", 12544, 4608, 512, torch.bfloat16, tw_layer(75.0, torch.bfloat16, "tw2"),
                              a.iters, "tw2 at 75 %: 50 % of columns x 50 % of rows per tile"))
+        rows.append(run_case("vgg16_conv5_c10_k75", 12544, 4608, 512, torch.bfloat16,
+                             col_then_row_layer(10.0, 75.0, torch.bfloat16), a.iters,
+                             "10 % of columns pruned, then 75 % of the rows of every tile"))
+    if "balance" in want:
+        # per-tile percentile (BERT type 2, equal kept-K per tile) next to the global percentile of tw1
+        for nm in ("ffn1", "ffn2"):
+            K, N = synth.BERT_BASE_LAYER[nm]
+            rows.append(run_case(f"bert_{nm}_type2_75", 4096, K, N, torch.float16,
+                                 tw_layer(75.0, torch.float16, "bert_type2"), a.iters, "equal kept-K per tile"))
+            rows.append(run_case(f"bert_{nm}_tw1_75", 4096, K, N, torch.float16, tw_layer(75.0, torch.float16), a.iters,
+                                 "global percentile: kept-K varies per tile"))
     if "lstm" in want:
         def tew(W):
             res = build_mask("tw1m", [W.abs()], 75.0, 128, 1.5, want_residual=True)
