@@ -264,7 +264,39 @@ struct Scratch {
   unsigned int* hist = nullptr;
   unsigned long long* count = nullptr;
   unsigned int* min_gt = nullptr;
+  ts::SelectState* st = nullptr;   // state of the device-driven select
+  double* thr = nullptr;           // 4 thresholds on the device: column stage, row stage, residual, spare
 };
+
+int alloc_scratch(Arena& arena, Scratch* sc) {
+  TSM_OK(arena.alloc(&sc->hist, 256));
+  TSM_OK(arena.alloc(&sc->count, 1));
+  TSM_OK(arena.alloc(&sc->min_gt, 1));
+  TSM_OK(arena.alloc(&sc->st, 1));
+  TSM_OK(arena.alloc(&sc->thr, 4));
+  return TS_OK;
+}
+
+// np.percentile(vals, q) into sc.thr[slot], enqueued on s without reading anything back.
+int percentile_to_device(const float* vals, long long n, double q, bool wide, bool f64_values, const Scratch& sc,
+                         int slot, cudaStream_t s) {
+  if (n <= 0) return ts_internal_fail(TS_ERR_INVALID, "percentile of an empty set");
+  const Ranks r = percentile_ranks(n, q, wide);
+  const int arith = f64_values ? 2 : (wide ? 1 : 0);
+  TSM_CUDA(ts::percentile_dev_launch(vals, n, r.pi, r.ni, r.gamma_f, r.gamma_d, arith, sc.st, sc.hist,
+                                     sc.thr + slot, nullptr, s));
+  return TS_OK;
+}
+
+// Reads thresholds and the select's error flag back (one blocking copy each).
+int read_thresholds(const Scratch& sc, int slot, double* out, cudaStream_t s) {
+  ts::SelectState st;
+  TSM_CUDA(cudaMemcpyAsync(out, sc.thr + slot, sizeof(double), cudaMemcpyDeviceToHost, s));
+  TSM_CUDA(cudaMemcpyAsync(&st, sc.st, sizeof(st), cudaMemcpyDeviceToHost, s));
+  TSM_CUDA(cudaStreamSynchronize(s));
+  if (st.error) return ts_internal_fail(TS_ERR_CUDA, "radix select lost its rank (non-finite input?)");
+  return TS_OK;
+}
 
 // Row stage shared by every mode: norms of all tile-rows of all layers, a keep flag for each, the
 // per-tile kept-row lists, and (optionally) the dense masks.
@@ -307,12 +339,9 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
     }
   }
   if (sel == 0) {
-    const Ranks r = percentile_ranks(total, q, wide);
-    float a = 0, b = 0;
-    TSM_OK(order_statistics(norms, total, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s));
-    const double thr = percentile_lerp(a, b, r, wide);
-    if (thr_out) *thr_out = thr;
-    TSM_CUDA(ts::threshold_launch(norms, total, thr, keep, s));
+    TSM_OK(percentile_to_device(norms, total, q, wide, false, sc, 1, s));
+    TSM_CUDA(ts::threshold_dev_launch(norms, total, sc.thr + 1, keep, s));
+    if (thr_out) TSM_OK(read_thresholds(sc, 1, thr_out, s));
   } else {
     for (int l = 0; l < nl; ++l) {
       const int nt = static_cast<int>(bounds[l].size()) - 1;
@@ -449,9 +478,7 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
     }
   }
   Scratch sc;
-  TSM_OK(arena.alloc(&sc.hist, 256));
-  TSM_OK(arena.alloc(&sc.count, 1));
-  TSM_OK(arena.alloc(&sc.min_gt, 1));
+  TSM_OK(alloc_scratch(arena, &sc));
   ts_mask_result* res = new ts_mask_result();
 
   const bool two_d = mode == TS_MASK_TW2 || mode == TS_MASK_TW2M || mode == TS_MASK_BERT_TW_KN;
@@ -487,14 +514,11 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
         rc = ts_internal_fail(TS_ERR_CUDA, "column norm kernel failed: %s", cudaGetErrorString(e));
         break;
       }
-      const Ranks r = percentile_ranks(totalN, q, wide);
-      float a = 0, b = 0;
-      if ((rc = order_statistics(cn, totalN, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s)) != TS_OK) break;
-      res->thr[0] = percentile_lerp(a, b, r, wide);
-      e = ts::threshold_launch(cn, totalN, res->thr[0], ck, s);
+      if ((rc = percentile_to_device(cn, totalN, q, wide, false, sc, 0, s)) != TS_OK) break;
+      e = ts::threshold_dev_launch(cn, totalN, sc.thr + 0, ck, s);
       std::vector<uint8_t> all(totalN);
       if (e == cudaSuccess) e = cudaMemcpyAsync(all.data(), ck, totalN, cudaMemcpyDeviceToHost, s);
-      if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+      if (e == cudaSuccess && (rc = read_thresholds(sc, 0, &res->thr[0], s)) != TS_OK) break;
       if (e != cudaSuccess) {
         rc = ts_internal_fail(TS_ERR_CUDA, "column threshold failed: %s", cudaGetErrorString(e));
         break;
@@ -533,16 +557,13 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
       }
       const double q2 = 100.0 - g1percent;
       const bool wide2 = sparsity_is_f64 != 0;
-      const Ranks r = percentile_ranks(total, q2, wide2);
-      float a = 0, b = 0;
-      if ((rc = order_statistics(vals, total, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s)) != TS_OK) break;
-      res->thr[2] = percentile_lerp(a, b, r, wide2);
+      if ((rc = percentile_to_device(vals, total, q2, wide2, false, sc, 2, s)) != TS_OK) break;
       o = 0;
       for (int l = 0; l < n_layers && e == cudaSuccess; ++l) {
-        e = ts::tew_apply_launch(vals + o, res->thr[2], L[l].K, L[l].N, L[l].mask, L[l].ld_mask, L[l].residual, s);
+        e = ts::tew_apply_launch(vals + o, sc.thr + 2, L[l].K, L[l].N, L[l].mask, L[l].ld_mask, L[l].residual, s);
         o += static_cast<long long>(L[l].K) * L[l].N;
       }
-      if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+      if (e == cudaSuccess && (rc = read_thresholds(sc, 2, &res->thr[2], s)) != TS_OK) break;
       if (e != cudaSuccess) {
         rc = ts_internal_fail(TS_ERR_CUDA, "residual apply kernel failed: %s", cudaGetErrorString(e));
         break;
@@ -718,9 +739,7 @@ int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_d
   // percentile, the difference of the two order statistics included, is a double operation.
   Arena arena;
   Scratch sc;
-  TSM_OK(arena.alloc(&sc.hist, 256));
-  TSM_OK(arena.alloc(&sc.count, 1));
-  TSM_OK(arena.alloc(&sc.min_gt, 1));
+  TSM_OK(alloc_scratch(arena, &sc));
   float* vals = nullptr;
   TSM_OK(arena.alloc(&vals, static_cast<size_t>(total)));
   long long off = 0;
@@ -729,31 +748,24 @@ int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_d
                                    vals + off, s));
     off += static_cast<long long>(Ks[l]) * Ns[l];
   }
-  const Ranks r = percentile_ranks(total, sparsity, /*wide=*/true);
-  float a = 0, b = 0;
-  TSM_OK(order_statistics(vals, total, r.pi, r.ni, &a, &b, sc.hist, sc.count, sc.min_gt, s));
-  volatile double diff = static_cast<double>(b) - static_cast<double>(a);
-  volatile double thr = static_cast<double>(a) + diff * r.gamma_d;
-  if (r.gamma_d >= 0.5) {
-    volatile double omt = 1.0 - r.gamma_d;
-    thr = static_cast<double>(b) - diff * omt;
-  }
-  if (threshold_out) *threshold_out = thr;
+  TSM_OK(percentile_to_device(vals, total, sparsity, /*wide=*/true, /*f64_values=*/true, sc, 3, s));
   off = 0;
   for (int l = 0; l < n_layers; ++l) {
     const long long n_el = static_cast<long long>(Ks[l]) * Ns[l];
     const long long ldm = ld_masks ? ld_masks[l] : Ns[l];
     if (ldm == Ns[l]) {
-      TSM_CUDA(ts::threshold_launch(vals + off, n_el, thr, masks_dev[l], s));
+      TSM_CUDA(ts::threshold_dev_launch(vals + off, n_el, sc.thr + 3, masks_dev[l], s));
     } else {
       for (int k = 0; k < Ks[l]; ++k) {
-        TSM_CUDA(ts::threshold_launch(vals + off + static_cast<long long>(k) * Ns[l], Ns[l], thr,
-                                      masks_dev[l] + static_cast<long long>(k) * ldm, s));
+        TSM_CUDA(ts::threshold_dev_launch(vals + off + static_cast<long long>(k) * Ns[l], Ns[l], sc.thr + 3,
+                                          masks_dev[l] + static_cast<long long>(k) * ldm, s));
       }
     }
     off += n_el;
   }
-  TSM_CUDA(cudaStreamSynchronize(s));
+  double thr = 0.0;
+  TSM_OK(read_thresholds(sc, 3, &thr, s));
+  if (threshold_out) *threshold_out = thr;
   return TS_OK;
 }
 

@@ -256,6 +256,123 @@ select_neighbor_kernel(const float* __restrict__ vals, long long n, uint32_t key
 }
 
 // ---------------------------------------------------------------------------------------------
+// The same select with its digit choice on the device: nothing is read back between the passes
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+select_begin_kernel(SelectState* __restrict__ st, unsigned int* __restrict__ hist, unsigned long long rank) {
+  hist[threadIdx.x] = 0;
+  if (threadIdx.x == 0) {
+    st->prefix = 0;
+    st->error = 0;
+    st->rank = rank;
+    st->count_le = 0;
+    st->min_gt = 0xffffffffu;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+select_hist_dev_kernel(const float* __restrict__ vals, long long n, const SelectState* __restrict__ st,
+                       int shift, unsigned int* __restrict__ hist) {
+  __shared__ unsigned int h[256];
+  h[threadIdx.x] = 0;
+  __syncthreads();
+  const uint32_t prefix = st->prefix;
+  const uint32_t hi_mask = shift >= 24 ? 0u : (0xffffffffu << (shift + 8));
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t key = float_key(__ldg(vals + i));
+    if ((key & hi_mask) == (prefix & hi_mask)) atomicAdd(&h[(key >> shift) & 0xffu], 1u);
+  }
+  __syncthreads();
+  if (h[threadIdx.x]) atomicAdd(&hist[threadIdx.x], h[threadIdx.x]);
+}
+
+// One block: the digit whose bin holds the wanted rank joins the prefix; the histogram is cleared
+// for the next pass.
+__global__ void __launch_bounds__(256)
+select_pick_kernel(SelectState* __restrict__ st, unsigned int* __restrict__ hist, int shift) {
+  __shared__ unsigned long long cum[256];
+  const int t = threadIdx.x;
+  const unsigned long long mine = hist[t];
+  const unsigned long long rank = st->rank;
+  cum[t] = mine;
+  __syncthreads();
+  for (int o = 1; o < 256; o <<= 1) {
+    const unsigned long long add = t >= o ? cum[t - o] : 0;
+    __syncthreads();
+    cum[t] += add;
+    __syncthreads();
+  }
+  const unsigned long long incl = cum[t], excl = incl - mine;
+  if (excl <= rank && rank < incl) {
+    st->prefix |= static_cast<uint32_t>(t) << shift;
+    st->rank = rank - excl;
+  }
+  if (t == 255 && rank >= incl) st->error = 1;   // the rank lies beyond the keys that matched (non-finite input)
+  hist[t] = 0;
+}
+
+__global__ void __launch_bounds__(256)
+select_neighbor_dev_kernel(const float* __restrict__ vals, long long n, SelectState* __restrict__ st) {
+  const uint32_t key = st->prefix;
+  unsigned long long c = 0;
+  unsigned int m = 0xffffffffu;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t k = float_key(__ldg(vals + i));
+    if (k <= key) ++c;
+    else m = min(m, k);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+    m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (c) atomicAdd(&st->count_le, c);
+    if (m != 0xffffffffu) atomicMin(&st->min_gt, m);
+  }
+}
+
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// The two order statistics and NumPy's _lerp between them (a + (b-a)*t, or b - (b-a)*(1-t) when
+// t >= 0.5), with the operand types NumPy uses: arith 0 = all float32; 1 = t in double but b-a in
+// float32 (float32 array, float64 q); 2 = all double (float64 array).
+__global__ void select_finish_kernel(SelectState* __restrict__ st, long long pi, long long ni, float gamma_f,
+                                     double gamma_d, int arith, double* __restrict__ thr_out,
+                                     float* __restrict__ ab_out) {
+  const float a = key_to_float(st->prefix);
+  float b = a;
+  if (ni != pi && static_cast<long long>(st->count_le) < ni + 1) b = key_to_float(st->min_gt);
+  double res;
+  if (arith == 0) {
+    const float diff = __fsub_rn(b, a);
+    float r = __fadd_rn(a, __fmul_rn(diff, gamma_f));
+    if (gamma_f >= 0.5f) r = __fsub_rn(b, __fmul_rn(diff, __fsub_rn(1.0f, gamma_f)));
+    res = static_cast<double>(r);
+  } else {
+    const double diff = arith == 1 ? static_cast<double>(__fsub_rn(b, a))
+                                   : __dsub_rn(static_cast<double>(b), static_cast<double>(a));
+    res = __dadd_rn(static_cast<double>(a), __dmul_rn(diff, gamma_d));
+    if (gamma_d >= 0.5) res = __dsub_rn(static_cast<double>(b), __dmul_rn(diff, __dsub_rn(1.0, gamma_d)));
+  }
+  *thr_out = res;
+  if (ab_out) {
+    ab_out[0] = a;
+    ab_out[1] = b;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+threshold_dev_kernel(const float* __restrict__ vals, long long n, const double* __restrict__ thr,
+                     uint8_t* __restrict__ keep) {
+  const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (i < n) keep[i] = static_cast<double>(vals[i]) > *thr ? 1 : 0;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Thresholding and list building
 // ---------------------------------------------------------------------------------------------
 // keep[i] = vals[i] > thr  (compared in double: exact for both float32 and float64 thresholds)
@@ -437,11 +554,12 @@ tew_values_kernel(const float* __restrict__ score, long long ld, const uint8_t* 
 
 // mask[k][n] |= v > thr; residual[k][n] = (v > thr) & !mask_before   (prune_algo.py:171-175)
 __global__ void __launch_bounds__(256)
-tew_apply_kernel(const float* __restrict__ vals, double thr, int K, int N, uint8_t* __restrict__ mask,
-                 long long ld_mask, uint8_t* __restrict__ residual) {
+tew_apply_kernel(const float* __restrict__ vals, const double* __restrict__ thr_dev, int K, int N,
+                 uint8_t* __restrict__ mask, long long ld_mask, uint8_t* __restrict__ residual) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   const int k = blockIdx.y;
   if (n >= N) return;
+  const double thr = *thr_dev;
   const long long mi = static_cast<long long>(k) * ld_mask + n;
   const bool extra = static_cast<double>(vals[static_cast<long long>(k) * N + n]) > thr;
   const uint8_t before = mask[mi];
@@ -548,6 +666,26 @@ cudaError_t select_neighbor_launch(const float* vals, long long n, uint32_t key,
   return cudaGetLastError();
 }
 
+cudaError_t percentile_dev_launch(const float* vals, long long n, long long pi, long long ni, float gamma_f,
+                                  double gamma_d, int arith, SelectState* st, unsigned int* hist,
+                                  double* thr_out, float* ab_out, cudaStream_t s) {
+  select_begin_kernel<<<1, 256, 0, s>>>(st, hist, static_cast<unsigned long long>(pi));
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    select_hist_dev_kernel<<<stream_grid(n), 256, 0, s>>>(vals, n, st, shift, hist);
+    select_pick_kernel<<<1, 256, 0, s>>>(st, hist, shift);
+  }
+  if (ni != pi) select_neighbor_dev_kernel<<<stream_grid(n), 256, 0, s>>>(vals, n, st);
+  select_finish_kernel<<<1, 1, 0, s>>>(st, pi, ni, gamma_f, gamma_d, arith, thr_out, ab_out);
+  return cudaGetLastError();
+}
+
+cudaError_t threshold_dev_launch(const float* vals, long long n, const double* thr, uint8_t* keep,
+                                 cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  threshold_dev_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(vals, n, thr, keep);
+  return cudaGetLastError();
+}
+
 cudaError_t threshold_launch(const float* vals, long long n, double thr, uint8_t* keep,
                              cudaStream_t s) {
   if (n <= 0) return cudaSuccess;
@@ -609,7 +747,7 @@ cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* m
   return cudaGetLastError();
 }
 
-cudaError_t tew_apply_launch(const float* vals, double thr, int K, int N, uint8_t* mask,
+cudaError_t tew_apply_launch(const float* vals, const double* thr, int K, int N, uint8_t* mask,
                              long long ld_mask, uint8_t* residual, cudaStream_t s) {
   if (K <= 0 || N <= 0) return cudaSuccess;
   dim3 grid((N + 255) / 256, K);

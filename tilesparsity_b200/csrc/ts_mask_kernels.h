@@ -25,6 +25,28 @@ cudaError_t select_hist_launch(const float* vals, long long n, uint32_t prefix, 
 cudaError_t select_neighbor_launch(const float* vals, long long n, uint32_t key,
                                    unsigned long long* count_le, unsigned int* min_gt,
                                    cudaStream_t s);
+// State of one radix select kept on the device between its passes.
+struct SelectState {
+  uint32_t prefix;              // key bits fixed so far
+  uint32_t error;               // 1: the rank was not among the keys (non-finite input)
+  unsigned long long rank;      // rank still to be located inside the current prefix
+  unsigned long long count_le;  // #{key <= selected key}
+  uint32_t min_gt;              // smallest key above the selected one
+  uint32_t pad_;
+};
+
+// np.percentile(vals, q) enqueued without any read-back: ranks pi <= ni <= pi+1 and the interpolation
+// weight come from the host (they depend on n and q only); the threshold lands in *thr_out (device),
+// the two order statistics in ab_out[0..1] (device, optional).  arith: 0 float32 everywhere, 1 double
+// with a float32 difference, 2 double everywhere.  hist: 256 counters.
+cudaError_t percentile_dev_launch(const float* vals, long long n, long long pi, long long ni, float gamma_f,
+                                  double gamma_d, int arith, SelectState* st, unsigned int* hist,
+                                  double* thr_out, float* ab_out, cudaStream_t s);
+
+// keep[i] = vals[i] > *thr, the threshold read from device memory.
+cudaError_t threshold_dev_launch(const float* vals, long long n, const double* thr, uint8_t* keep,
+                                 cudaStream_t s);
+
 cudaError_t threshold_launch(const float* vals, long long n, double thr, uint8_t* keep,
                              cudaStream_t s);
 cudaError_t segment_count_launch(const uint8_t* keep, const long long* seg_ptr, int n_seg, int* counts,
@@ -42,7 +64,7 @@ cudaError_t vw_mask_launch(const float* score, long long ld, int K, int N, int t
 
 cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* mask, long long ld_mask,
                               int K, int N, float* vals, cudaStream_t s);
-cudaError_t tew_apply_launch(const float* vals, double thr, int K, int N, uint8_t* mask,
+cudaError_t tew_apply_launch(const float* vals, const double* thr, int K, int N, uint8_t* mask,
                              long long ld_mask, uint8_t* residual, cudaStream_t s);
 cudaError_t tile_rank_launch(const float* vals, int K, int n_tiles, int mode, int k_keep, int pi,
                              int ni, uint8_t* keep, float* stats, cudaStream_t s);
