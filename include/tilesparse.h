@@ -141,6 +141,18 @@ int ts_masked_gemm_simt(ts_layer_t* layer, int M, const void* At_dev, int64_t ld
 int ts_masked_gemm_host(ts_layer_t* layer, int M, const void* At_host, void* Ct_host, float alpha,
                         float beta, void* stream);
 
+/* The same in two steps, for callers that keep several of these in flight.  _async queues the work:
+ * the batch moves in up to four column blocks through copy-in, GEMM and copy-out on streams of the
+ * layer's own (both directions of the link and the kernel overlap), ordered after what `stream` holds
+ * at the call.  _wait makes `stream` wait (on the device, not the host) for the arrival of the last
+ * block of the layer's latest call; Ct_host is valid once the caller has then synchronised `stream`.
+ * Calls on different layers overlap with each other; calls on one layer run one after the other.
+ * No counterpart in the reference (its driver copies, computes and copies back in sequence,
+ * basic_nn.cu:986-1034). */
+int ts_masked_gemm_host_async(ts_layer_t* layer, int M, const void* At_host, void* Ct_host, float alpha,
+                              float beta, void* stream);
+int ts_masked_gemm_host_wait(ts_layer_t* layer, void* stream);
+
 /* Reads and clears the layer's device status word (synchronises `stream`).  Returns TS_OK or the
  * error a kernel recorded (TS_ERR_TIMEOUT when a bounded wait ran out). */
 int ts_layer_check(ts_layer_t* layer, void* stream);

@@ -134,6 +134,37 @@ def test_host_buffer_entry_point_and_row_major_op():
     layer.close()
 
 
+def test_host_buffer_pipeline_blocks_beta_and_async():
+    """Four column blocks (M = 2048 + a ragged tail), beta != 0 through the host path, zeros in the
+    columns no tile keeps after a beta pass, and the asynchronous variant on two layers at once."""
+    M = 2048 + 72
+    layer, At, A16, W16 = _case(384, 512, M, 96, torch.float16, 33)
+    ref = og.masked_matmul_compacted(A16, W16, layer.tiles)
+    hA = At.cpu().pin_memory()
+    hC = torch.empty((512, M), dtype=torch.float16).pin_memory()
+    layer.masked_gemm_host(hA, hC)
+    assert og.max_rel_error(hC.float().numpy(), ref) <= TOL
+    first = hC.clone()
+    layer.masked_gemm_host(hA, hC, alpha=0.5, beta=1.0)            # C <- 0.5 A W + C
+    assert og.max_rel_error(hC.float().numpy(), 1.5 * ref) <= TOL
+    layer.masked_gemm_host(hA, hC)                                   # beta = 0 again
+    assert torch.equal(hC, first)
+    layer2, At2, A2, W2 = _case(256, 384, M, 64, torch.float16, 34)
+    ref2 = og.masked_matmul_compacted(A2, W2, layer2.tiles)
+    hA2 = At2.cpu().pin_memory()
+    hC2 = torch.empty((384, M), dtype=torch.float16).pin_memory()
+    hC.zero_()
+    layer.masked_gemm_host(hA, hC, wait=False)
+    layer2.masked_gemm_host(hA2, hC2, wait=False)
+    layer.host_wait()
+    layer2.host_wait()
+    torch.cuda.current_stream().synchronize()
+    assert torch.equal(hC, first)
+    assert og.max_rel_error(hC2.float().numpy(), ref2) <= TOL
+    layer.close()
+    layer2.close()
+
+
 def test_bad_arguments_are_rejected():
     from tilesparsity_b200 import TileSparseError
     layer, At, _, _ = _case(64, 128, 64, 16, torch.float16, 41)

@@ -66,6 +66,8 @@ SIGNATURES = {
     "ts_masked_gemm_ex": (C.c_int, [_vp, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.POINTER(Epilogue), _vp]),
     "ts_masked_gemm_simt": (C.c_int, [_vp, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.c_float, C.c_float, _vp]),
     "ts_masked_gemm_host": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_float, C.c_float, _vp]),
+    "ts_masked_gemm_host_async": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_float, C.c_float, _vp]),
+    "ts_masked_gemm_host_wait": (C.c_int, [_vp, _vp]),
     "ts_layer_check": (C.c_int, [_vp, _vp]),
     "ts_layer_schedule_stats": (C.c_int, [_vp, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)]),
     "ts_stream_gemm_nn": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_float, _vp, _vp, C.c_float, _vp, C.c_int,

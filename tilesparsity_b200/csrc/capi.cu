@@ -290,6 +290,11 @@ struct ts_layer {
   size_t at_bytes = 0;
   void* d_ct = nullptr;
   size_t ct_bytes = 0;
+  // Host-buffer path: copy-in, compute and copy-out streams and the events that chain them.
+  cudaStream_t s_in = nullptr, s_mm = nullptr, s_out = nullptr;
+  std::vector<cudaEvent_t> events;
+  bool ct_dirty = true;   // the staging output holds something other than zeros where no tile writes
+  bool host_pending = false;   // events[1] marks the end of the latest host-buffer call
 };
 
 namespace {
@@ -421,6 +426,10 @@ int ts_layer_destroy(ts_layer_t* l) {
   cudaFree(l->d_status);
   cudaFree(l->d_at);
   cudaFree(l->d_ct);
+  for (cudaEvent_t e : l->events) cudaEventDestroy(e);
+  if (l->s_in) cudaStreamDestroy(l->s_in);
+  if (l->s_mm) cudaStreamDestroy(l->s_mm);
+  if (l->s_out) cudaStreamDestroy(l->s_out);
   delete l;
   return TS_OK;
 }
@@ -611,15 +620,15 @@ int ts_masked_gemm_simt(ts_layer_t* l, int M, const void* At, int64_t lda, void*
   return TS_OK;
 }
 
-int ts_masked_gemm_host(ts_layer_t* l, int M, const void* At_host, void* Ct_host, float alpha,
-                        float beta, void* stream) {
+int ts_masked_gemm_host_async(ts_layer_t* l, int M, const void* At_host, void* Ct_host, float alpha,
+                              float beta, void* stream) {
   if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
   if (M <= 0 || (M % 8) != 0) return fail(TS_ERR_INVALID, "M=%d must be a positive multiple of 8", M);
   if (!At_host || !Ct_host) return fail(TS_ERR_INVALID, "host buffers are NULL");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t a_bytes = static_cast<size_t>(l->K) * M * 2, c_bytes = static_cast<size_t>(l->N) * M * 2;
   if (a_bytes > l->at_bytes) {
-    TS_CUDA(cudaStreamSynchronize(s));
+    TS_CUDA(cudaDeviceSynchronize());
     cudaFree(l->d_at);
     l->d_at = nullptr;
     l->at_bytes = 0;
@@ -627,21 +636,91 @@ int ts_masked_gemm_host(ts_layer_t* l, int M, const void* At_host, void* Ct_host
     l->at_bytes = a_bytes;
   }
   if (c_bytes > l->ct_bytes) {
-    TS_CUDA(cudaStreamSynchronize(s));
+    TS_CUDA(cudaDeviceSynchronize());
     cudaFree(l->d_ct);
     l->d_ct = nullptr;
     l->ct_bytes = 0;
     TS_CUDA(cudaMalloc(&l->d_ct, c_bytes));
     l->ct_bytes = c_bytes;
-    // Columns no tile keeps are never written by the kernel: they stay zero in the staging buffer.
-    TS_CUDA(cudaMemsetAsync(l->d_ct, 0, c_bytes, s));
+    l->ct_dirty = true;
   }
-  TS_CUDA(cudaMemcpyAsync(l->d_at, At_host, a_bytes, cudaMemcpyHostToDevice, s));
-  if (beta != 0.0f) TS_CUDA(cudaMemcpyAsync(l->d_ct, Ct_host, c_bytes, cudaMemcpyHostToDevice, s));
-  int rc = ts_masked_gemm(l, M, l->d_at, M, l->d_ct, M, alpha, beta, stream);
+  if (!l->s_in) {
+    TS_CUDA(cudaStreamCreateWithFlags(&l->s_in, cudaStreamNonBlocking));
+    TS_CUDA(cudaStreamCreateWithFlags(&l->s_mm, cudaStreamNonBlocking));
+    TS_CUDA(cudaStreamCreateWithFlags(&l->s_out, cudaStreamNonBlocking));
+  }
+  // The batch is cut into up to four column blocks that move through copy-in, GEMM and copy-out
+  // on three streams, so the two directions of the link and the kernel overlap.
+  static const int want_chunks = [] {
+    const char* e = getenv("TS_HOST_CHUNKS");
+    const int v = e ? atoi(e) : 0;
+    return (v >= 1 && v <= 16) ? v : 4;
+  }();
+  const int n_chunks = M >= 256 * want_chunks ? want_chunks : 1;
+  const int mc = ((M / n_chunks) + 255) / 256 * 256;
+  const size_t need_events = 2 + 2 * static_cast<size_t>(n_chunks);
+  while (l->events.size() < need_events) {
+    cudaEvent_t e;
+    TS_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    l->events.push_back(e);
+  }
+  cudaEvent_t e_begin = l->events[0], e_end = l->events[1];
+  // a call on this layer that is still in flight uses the same staging buffers: follow it
+  if (l->host_pending) TS_CUDA(cudaStreamWaitEvent(l->s_in, e_end, 0));
+  // everything this call does comes after what the caller has queued on its stream ...
+  TS_CUDA(cudaEventRecord(e_begin, s));
+  TS_CUDA(cudaStreamWaitEvent(l->s_in, e_begin, 0));
+  TS_CUDA(cudaStreamWaitEvent(l->s_mm, e_begin, 0));
+  TS_CUDA(cudaStreamWaitEvent(l->s_out, e_begin, 0));
+  // Columns no tile keeps are never written by the kernel: with beta == 0 they must come back as zeros.
+  if (beta == 0.0f && l->ct_dirty) {
+    TS_CUDA(cudaMemsetAsync(l->d_ct, 0, c_bytes, l->s_in));
+  }
+  const size_t pitch = static_cast<size_t>(M) * 2;
+  int c = 0;
+  for (int m0 = 0; m0 < M; m0 += mc, ++c) {
+    const int ml = std::min(mc, M - m0);
+    cudaEvent_t e_in = l->events[2 + 2 * c], e_mm = l->events[3 + 2 * c];
+    uint8_t* a_dev = static_cast<uint8_t*>(l->d_at) + static_cast<size_t>(m0) * 2;
+    uint8_t* c_dev = static_cast<uint8_t*>(l->d_ct) + static_cast<size_t>(m0) * 2;
+    const uint8_t* a_host = static_cast<const uint8_t*>(At_host) + static_cast<size_t>(m0) * 2;
+    uint8_t* c_host = static_cast<uint8_t*>(Ct_host) + static_cast<size_t>(m0) * 2;
+    TS_CUDA(cudaMemcpy2DAsync(a_dev, pitch, a_host, pitch, static_cast<size_t>(ml) * 2, l->K,
+                              cudaMemcpyHostToDevice, l->s_in));
+    if (beta != 0.0f) {
+      TS_CUDA(cudaMemcpy2DAsync(c_dev, pitch, c_host, pitch, static_cast<size_t>(ml) * 2, l->N,
+                                cudaMemcpyHostToDevice, l->s_in));
+    }
+    TS_CUDA(cudaEventRecord(e_in, l->s_in));
+    TS_CUDA(cudaStreamWaitEvent(l->s_mm, e_in, 0));
+    int rc = ts_masked_gemm(l, ml, a_dev, M, c_dev, M, alpha, beta, l->s_mm);
+    if (rc != TS_OK) return rc;
+    TS_CUDA(cudaEventRecord(e_mm, l->s_mm));
+    TS_CUDA(cudaStreamWaitEvent(l->s_out, e_mm, 0));
+    TS_CUDA(cudaMemcpy2DAsync(c_host, pitch, c_dev, pitch, static_cast<size_t>(ml) * 2, l->N,
+                              cudaMemcpyDeviceToHost, l->s_out));
+  }
+  // ... and ts_masked_gemm_host_wait orders a stream after the arrival of the last block
+  TS_CUDA(cudaEventRecord(e_end, l->s_out));
+  l->host_pending = true;
+  l->ct_dirty = beta != 0.0f;   // a beta pass leaves the caller's values in the columns no tile keeps
+  return TS_OK;
+}
+
+int ts_masked_gemm_host_wait(ts_layer_t* l, void* stream) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (!l->host_pending) return TS_OK;
+  TS_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), l->events[1], 0));
+  return TS_OK;
+}
+
+int ts_masked_gemm_host(ts_layer_t* l, int M, const void* At_host, void* Ct_host, float alpha,
+                        float beta, void* stream) {
+  int rc = ts_masked_gemm_host_async(l, M, At_host, Ct_host, alpha, beta, stream);
   if (rc != TS_OK) return rc;
-  TS_CUDA(cudaMemcpyAsync(Ct_host, l->d_ct, c_bytes, cudaMemcpyDeviceToHost, s));
-  TS_CUDA(cudaStreamSynchronize(s));
+  rc = ts_masked_gemm_host_wait(l, stream);
+  if (rc != TS_OK) return rc;
+  TS_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
 

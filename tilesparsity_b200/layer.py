@@ -175,8 +175,11 @@ class TWLayer:
         return out
 
     def masked_gemm_host(self, At_host: torch.Tensor, Ct_host: torch.Tensor, alpha: float = 1.0,
-                         beta: float = 0.0) -> torch.Tensor:
-        """Host-buffer variant: H2D copy, GEMM, D2H copy, synchronise (one C-ABI call)."""
+                         beta: float = 0.0, wait: bool = True) -> torch.Tensor:
+        """Host-buffer variant: H2D copy, GEMM, D2H copy in overlapping column blocks (one C-ABI call).
+        With wait=False the call returns once everything is queued; `host_wait()` then orders the
+        current stream after the arrival of the output, and Ct_host is valid once that stream has
+        been synchronised."""
         if At_host.is_cuda or Ct_host.is_cuda:
             raise ValueError("masked_gemm_host takes host tensors")
         if At_host.dtype != self.dtype or Ct_host.dtype != self.dtype:
@@ -187,9 +190,15 @@ class TWLayer:
         if tuple(At_host.shape) != (self.K, M) or tuple(Ct_host.shape) != (self.N, M):
             raise ValueError("shape mismatch")
         with torch.cuda.device(self.device):
-            check(lib.ts_masked_gemm_host(self._h, M, C.c_void_p(At_host.data_ptr()), C.c_void_p(Ct_host.data_ptr()),
-                                          alpha, beta, _stream_ptr(self.device)))
+            fn = lib.ts_masked_gemm_host if wait else lib.ts_masked_gemm_host_async
+            check(fn(self._h, M, C.c_void_p(At_host.data_ptr()), C.c_void_p(Ct_host.data_ptr()), alpha, beta,
+                     _stream_ptr(self.device)))
         return Ct_host
+
+    def host_wait(self) -> None:
+        """Makes the current stream wait for this layer's latest masked_gemm_host(wait=False)."""
+        with torch.cuda.device(self.device):
+            check(lib.ts_masked_gemm_host_wait(self._h, _stream_ptr(self.device)))
 
     def check(self) -> None:
         """Raises if a kernel of this layer recorded an error (synchronises the current stream)."""
