@@ -230,8 +230,8 @@ void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, i
   *grid = g;
 
   // The same lists at K-block granularity for the gather warps.  The stream of every CTA ends with
-  // end markers; 24 of them cover the deepest look-ahead (every gather warp reads one block past its
-  // own end marker) with room to spare.
+  // end markers; 24 of them cover the deepest look-ahead (a gather warp requests the record of the
+  // block up to 16 positions past the one it is copying) with room to spare.
   size_t max_blocks = 0;
   for (const auto& l : lists) {
     size_t nb = 0;
