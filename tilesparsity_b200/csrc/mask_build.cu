@@ -233,6 +233,31 @@ select_hist_kernel(const float* __restrict__ vals, long long n, uint32_t prefix,
   if (h[threadIdx.x]) atomicAdd(&hist[threadIdx.x], h[threadIdx.x]);
 }
 
+// Block-wide sum of c and minimum of m (256 threads), then one atomic of each per block.
+__device__ __forceinline__ void block_count_min(unsigned long long c, unsigned int m,
+                                                unsigned long long* count_le, unsigned int* min_gt) {
+  __shared__ unsigned long long sc[8];
+  __shared__ unsigned int sm[8];
+  for (int o = 16; o > 0; o >>= 1) {
+    c += __shfl_xor_sync(0xffffffffu, c, o);
+    m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
+  }
+  const int w = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) {
+    sc[w] = c;
+    sm[w] = m;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) {
+      c += sc[i];
+      m = min(m, sm[i]);
+    }
+    if (c) atomicAdd(count_le, c);
+    if (m != 0xffffffffu) atomicMin(min_gt, m);
+  }
+}
+
 // res[0..1] (64-bit) += #{key_i <= key};  res[2] = min(res[2], min{key_i : key_i > key})
 __global__ void __launch_bounds__(256)
 select_neighbor_kernel(const float* __restrict__ vals, long long n, uint32_t key,
@@ -245,14 +270,7 @@ select_neighbor_kernel(const float* __restrict__ vals, long long n, uint32_t key
     if (k <= key) ++c;
     else m = min(m, k);
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    c += __shfl_xor_sync(0xffffffffu, c, o);
-    m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
-  }
-  if ((threadIdx.x & 31) == 0) {
-    if (c) atomicAdd(count_le, c);
-    if (m != 0xffffffffu) atomicMin(min_gt, m);
-  }
+  block_count_min(c, m, count_le, min_gt);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -323,14 +341,7 @@ select_neighbor_dev_kernel(const float* __restrict__ vals, long long n, SelectSt
     if (k <= key) ++c;
     else m = min(m, k);
   }
-  for (int o = 16; o > 0; o >>= 1) {
-    c += __shfl_xor_sync(0xffffffffu, c, o);
-    m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
-  }
-  if ((threadIdx.x & 31) == 0) {
-    if (c) atomicAdd(&st->count_le, c);
-    if (m != 0xffffffffu) atomicMin(&st->min_gt, m);
-  }
+  block_count_min(c, m, &st->count_le, &st->min_gt);
 }
 
 __device__ __forceinline__ float key_to_float(uint32_t k) {
