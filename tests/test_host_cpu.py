@@ -45,6 +45,19 @@ def test_argument_validation_needs_no_gpu():
     assert _lib.lib.ts_masked_gemm(None, 8, None, 8, None, 8, 1.0, 0.0, None) == _lib.TS_ERR_INVALID
     assert _lib.lib.ts_build_tw_mask(99, 1, None, None, None, None, 128, 50.0, 0, 0.0, None, None, None,
                                      C.byref(h), None) == _lib.TS_ERR_INVALID
+    assert _lib.lib.ts_build_pattern_mask(7, 1, None, None, None, None, 50.0, None, None, None, None) == _lib.TS_ERR_INVALID
+    assert "pattern" in _lib.last_error()
+    assert _lib.lib.ts_build_pattern_mask(0, 0, None, None, None, None, 50.0, None, None, None, None) == _lib.TS_ERR_INVALID
+    assert _lib.lib.ts_masked_gemm_host_async(None, 8, None, None, 1.0, 0.0, None) == _lib.TS_ERR_INVALID
+    assert _lib.lib.ts_masked_gemm_host_wait(None, None) == _lib.TS_ERR_INVALID
+
+
+def test_pruning_fun_dispatch_matches_the_reference_names():
+    from tilesparsity_b200 import masks
+    for name in ("tw1", "tw2", "tw1m", "tw2m", "ew", "vw"):
+        assert callable(masks.pruning_fun(name))
+    with pytest.raises(KeyError):
+        masks.pruning_fun("bw")          # block-wise: host-BLAS-dependent norms, not offered
 
 
 def test_shard_plan_is_lpt_and_balanced():
