@@ -316,6 +316,7 @@ void free_tiles(ts_layer* l) {
     cudaFree(kv.second.d_meta);
   }
   l->schedules.clear();
+  l->peer_key.clear();
   l->packed = false;
 }
 
