@@ -165,6 +165,26 @@ def test_host_buffer_pipeline_blocks_beta_and_async():
     layer2.close()
 
 
+def test_grouped_layers_equal_separate_launches():
+    """Independent layers as one block-structured layer over stacked activations and outputs."""
+    from tilesparsity_b200 import TWLayer
+    M = 512
+    a, At_a, _, _ = _case(256, 384, M, 64, torch.float16, 51)
+    b, At_b, _, _ = _case(640, 128, M, lambda g, nt: [200] * nt, torch.float16, 52)
+    g1, g2 = synth.rng(51), synth.rng(52)
+    # the dense weights the two cases were packed from
+    g1.standard_normal((M, 256), dtype=np.float32)
+    Wa = torch.from_numpy((g1.standard_normal((256, 384), dtype=np.float32) * np.float32(0.05))).cuda()
+    g2.standard_normal((M, 640), dtype=np.float32)
+    Wb = torch.from_numpy((g2.standard_normal((640, 128), dtype=np.float32) * np.float32(0.05))).cuda()
+    layer, k_off, n_off = TWLayer.grouped([Wa, Wb], [a.tiles, b.tiles], torch.float16)
+    out = layer.masked_gemm(torch.cat([At_a, At_b], dim=0).contiguous())
+    assert torch.equal(out[:384], a.masked_gemm(At_a))
+    assert torch.equal(out[384:], b.masked_gemm(At_b))
+    for x in (layer, a, b):
+        x.close()
+
+
 def test_bad_arguments_are_rejected():
     from tilesparsity_b200 import TileSparseError
     layer, At, _, _ = _case(64, 128, 64, 16, torch.float16, 41)

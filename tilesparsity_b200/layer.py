@@ -72,6 +72,37 @@ class TWLayer:
         layer.pack(W)
         return layer
 
+    @classmethod
+    def grouped(cls, Ws, tile_sets, dtype=torch.float16):
+        """Several independent tile-wise sparse layers as ONE layer, so that one launch computes all of
+        them: the weights become a block-structured [sum K, sum N] matrix whose tile t of layer l keeps
+        the rows (K offset of l) + kept rows, the activations are stacked [sum K][M] (layer l at row
+        offset k_off[l]) and the outputs [sum N][M] (layer l at row offset n_off[l]).  Nothing in the
+        kernel is special-cased: units of all layers share one schedule, and the start and end of the
+        individual GEMMs overlap.  The layers must not depend on each other's outputs.
+        Returns (layer, k_off, n_off); the dense block matrix exists only while the weights are packed."""
+        if not Ws or len(Ws) != len(tile_sets):
+            raise ValueError("one weight matrix per tile set")
+        G = tile_sets[0].G
+        dev = Ws[0].device
+        k_off = np.concatenate([[0], np.cumsum([ts.K for ts in tile_sets])]).astype(np.int64)
+        n_off = np.concatenate([[0], np.cumsum([ts.N for ts in tile_sets])]).astype(np.int64)
+        lists, col_masks = [], []
+        for l, ts in enumerate(tile_sets):
+            if ts.G != G or (ts.N % G) != 0 and l + 1 < len(tile_sets):
+                raise ValueError("layers must share G, and every layer but the last needs N divisible by G")
+            lists += [(ts.tile_rows(t) + k_off[l]).astype(np.int32) for t in range(ts.n_tiles)]
+            col_masks.append(ts.col_mask())
+        col_mask = np.concatenate(col_masks)
+        if not col_mask.all():
+            raise ValueError("grouped layers with pruned columns are not supported")
+        W_all = torch.zeros((int(k_off[-1]), int(n_off[-1])), dtype=Ws[0].dtype, device=dev)
+        for l, W in enumerate(Ws):
+            W_all[k_off[l]:k_off[l + 1], n_off[l]:n_off[l + 1]] = W
+        layer = cls(tiles_from_lists(int(k_off[-1]), int(n_off[-1]), G, lists), dtype, dev)
+        layer.pack(W_all)
+        return layer, k_off, n_off
+
     def pack(self, W: torch.Tensor) -> None:
         if W.device != self.device or W.dim() != 2 or tuple(W.shape) != (self.K, self.N):
             raise ValueError(f"W must be a [{self.K}, {self.N}] tensor on {self.device}")
