@@ -52,9 +52,10 @@ constexpr uint32_t kALbo = kKB * 128;    // bytes between its 64-column batch gr
 constexpr uint32_t kWSbo = 1024;         // bytes between 8-row groups of the weight operand
 constexpr int kMaxStages = 6;
 constexpr int kGW = 4;                   // gather warps
-// Gather warps that share one K block (1, 2 or 4).  Measured on B200: 4 is best or within 3 % of the
-// best on every workload tried (1 loses up to 30 % where the activations stream from DRAM, because
-// the blocks of different warps then land out of order and the MMA warp consumes them in order).
+// Gather warps that share one K block.  Measured on B200 with 1, 2 and 4: 4 is best or within 3 % of
+// the best on every workload tried (1 loses up to 30 % where the activations stream from DRAM,
+// because the blocks of different warps then land out of order and the MMA warp consumes them in
+// order).  With fewer than 4 the per-warp record slices grow and the ring below must shrink to fit.
 #ifndef TS_WARPS_PER_BLOCK
 #define TS_WARPS_PER_BLOCK 4
 #endif
@@ -128,6 +129,7 @@ struct Cfg {
   static constexpr int kUsedBytes = kStages * kStageBytes + kEpiBytes + static_cast<int>(sizeof(Barriers));
   static constexpr int kSmemBytes = (kUsedBytes + 1023 + 1023) / 1024 * 1024 > 232448 ? 232448
                                                                                       : (kUsedBytes + 1023 + 1023) / 1024 * 1024;
+  static_assert(kUsedBytes <= kSmemBytes, "stages, staging and barriers exceed the shared memory of one CTA");
   static constexpr int kLanesPerRow = MT / 8;       // 16-byte chunks in one gathered row
   static constexpr int kRowsPerInstr = 32 / kLanesPerRow;
 };
