@@ -416,24 +416,25 @@ segment_compact_kernel(const uint8_t* __restrict__ keep, const long long* __rest
                        const int* __restrict__ out_ptr, int* __restrict__ list) {
   const long long a = seg_ptr[blockIdx.x], b = seg_ptr[blockIdx.x + 1];
   int* out = list + out_ptr[blockIdx.x];
-  __shared__ int scan[256];
-  __shared__ int base;
-  if (threadIdx.x == 0) base = 0;
-  __syncthreads();
+  // 256 flags per step: ranks inside a warp by ballot, across the eight warps by a small table
+  __shared__ int warp_cnt[8];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  int base = 0;   // kept flags before this step (the same value in every thread)
   for (long long i0 = a; i0 < b; i0 += blockDim.x) {
     const long long i = i0 + threadIdx.x;
     const int f = (i < b) ? keep[i] : 0;
-    scan[threadIdx.x] = f;
+    const unsigned int bal = __ballot_sync(0xffffffffu, f != 0);
+    if (lane == 0) warp_cnt[w] = __popc(bal);
     __syncthreads();
-    for (int o = 1; o < 256; o <<= 1) {
-      const int v = threadIdx.x >= o ? scan[threadIdx.x - o] : 0;
-      __syncthreads();
-      scan[threadIdx.x] += v;
-      __syncthreads();
+    int before = 0, total = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = warp_cnt[j];
+      if (j < w) before += c;
+      total += c;
     }
-    if (f) out[base + scan[threadIdx.x] - 1] = static_cast<int>(i - a);
-    __syncthreads();
-    if (threadIdx.x == 255) base += scan[255];
+    if (f) out[base + before + __popc(bal & ((1u << lane) - 1u))] = static_cast<int>(i - a);
+    base += total;
     __syncthreads();
   }
 }
