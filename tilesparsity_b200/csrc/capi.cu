@@ -316,7 +316,6 @@ void free_tiles(ts_layer* l) {
     cudaFree(kv.second.d_meta);
   }
   l->schedules.clear();
-  l->peer_key.clear();
   l->packed = false;
 }
 
