@@ -295,9 +295,6 @@ struct ts_layer {
   std::vector<cudaEvent_t> events;
   bool ct_dirty = true;   // the staging output holds something other than zeros where no tile writes
   bool host_pending = false;   // events[1] marks the end of the latest host-buffer call
-  // Tensor maps over the peer buffers of a sharded layer, in device memory, and what they were made for.
-  CUtensorMap* d_peer_maps = nullptr;
-  std::vector<long long> peer_key;
 };
 
 namespace {
@@ -429,7 +426,6 @@ int ts_layer_destroy(ts_layer_t* l) {
   cudaFree(l->d_status);
   cudaFree(l->d_at);
   cudaFree(l->d_ct);
-  cudaFree(l->d_peer_maps);
   for (cudaEvent_t e : l->events) cudaEventDestroy(e);
   if (l->s_in) cudaStreamDestroy(l->s_in);
   if (l->s_mm) cudaStreamDestroy(l->s_mm);
@@ -595,28 +591,9 @@ int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* C
   if (s->n_units == 0) return TS_OK;
   CUtensorMap tmap_c;
   const bool tst = use_tma_store();
-  ep.peer_maps = nullptr;
   if (tst) {
     rc = make_out_tmap(&tmap_c, l->dtype, Ct, l->N, M, ldc);
     if (rc != TS_OK) return rc;
-    if (ep.n_peers > 0) {
-      // one tensor map per peer buffer, kept in device memory and rebuilt only when the buffers,
-      // the batch size or the pitch change
-      std::vector<long long> key{M, static_cast<long long>(ldc)};
-      for (int p = 0; p < ep.n_peers; ++p) key.push_back(reinterpret_cast<long long>(ep.peers[p]));
-      if (key != l->peer_key) {
-        CUtensorMap maps[7];
-        for (int p = 0; p < ep.n_peers; ++p) {
-          rc = make_out_tmap(&maps[p], l->dtype, ep.peers[p], l->N, M, ldc);
-          if (rc != TS_OK) return rc;
-        }
-        if (!l->d_peer_maps) TS_CUDA(cudaMalloc(&l->d_peer_maps, 7 * sizeof(CUtensorMap)));
-        TS_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));   // a launch may still read the old maps
-        TS_CUDA(cudaMemcpy(l->d_peer_maps, maps, ep.n_peers * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
-        l->peer_key = key;
-      }
-      ep.peer_maps = l->d_peer_maps;
-    }
   }
   TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, l->tmap, tst ? &tmap_c : nullptr, s->d_units, s->rounds,
                                  s->grid, s->d_meta, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,

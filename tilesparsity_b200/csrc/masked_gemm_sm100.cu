@@ -450,9 +450,8 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int m0 = w.m_begin;
       const int m_cnt = min(w.m_len, M - m0);
       const bool active = j < w.n_count;
-      // TMA store: consecutive Ct rows, nothing to read back; peer copies need their tensor maps
-      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f &&
-                             (ep.n_peers == 0 || ep.peer_maps != nullptr);
+      // TMA store: consecutive Ct rows, nothing to read back, no peer copies
+      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f && ep.n_peers == 0;
       const bool plain = beta == 0.0f && ep.bias == nullptr && ep.act == kActNone;
       const long long c_row = active ? c_row_of(w, j) : 0;
       const int c_row_or_none = active ? static_cast<int>(c_row) : -1;
@@ -543,10 +542,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
           named_barrier_sync(half_bar, 128);     // the whole group is staged
           if (leader) {
             tma_store_2d(&tmap_c, smem_u32(stage_grp), m0 + grp_col, tile_row0);
-            // tile-sharded layers: the same group goes to the other GPUs' copies of Ct over NVLink
-            for (int p = 0; p < ep.n_peers; ++p) {
-              tma_store_2d(ep.peer_maps + p, smem_u32(stage_grp), m0 + grp_col, tile_row0);
-            }
             bulk_commit();
           }
         } else {

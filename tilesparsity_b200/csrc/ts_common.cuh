@@ -68,8 +68,7 @@ static_assert(sizeof(WorkItem) == 48, "WorkItem is read as three 16-byte words")
 // What the GEMM epilogue does with an accumulator value x of tile column n before it is stored:
 //     y = act(alpha * x + beta * Ct_old + bias[n])
 // and where the result goes besides Ct: up to 7 peer buffers with the same layout (other GPUs'
-// copies of Ct, written over NVLink with TMA stores where the local Ct is, with plain stores
-// otherwise: the all-gather of a tile-sharded layer).
+// copies of Ct, written with plain stores over NVLink: the all-gather of a tile-sharded layer).
 enum : int { kActNone = 0, kActRelu = 1, kActGelu = 2 };
 struct EpilogueArgs {
   float alpha;
@@ -78,9 +77,6 @@ struct EpilogueArgs {
   int act;
   int n_peers;
   uint16_t* peers[7];
-  // Tensor maps over the peer buffers (same shape as the one over Ct), in device memory; nullptr:
-  // the peers are written with plain stores only.
-  const CUtensorMap* peer_maps;
 };
 
 // One 64-row K block of a work unit.  A CTA's blocks are stored in processing order; the host
