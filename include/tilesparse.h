@@ -158,9 +158,29 @@ int ts_masked_gemm_host_wait(ts_layer_t* layer, void* stream);
 int ts_layer_check(ts_layer_t* layer, void* stream);
 
 /* Per-CTA load of the schedule ts_masked_gemm uses for batch size M: writes the summed cost of
- * every CTA's work units (in 64-row K blocks, epilogue included) to cta_cost[0..*n_ctas).  Pass
- * cta_cost == NULL to query *n_ctas. */
+ * every CTA's work units to cta_cost[0..*n_ctas).  The cost of a unit is the scheduler's model of it
+ * in units of 8 KiB moved between L2 and the SM (packed weights and gathered activations per K block,
+ * the output, and a constant per unit).  Pass cta_cost == NULL to query *n_ctas.  This is the
+ * CTA-level load balance of the single launch that replaces the reference's stream per tile
+ * (basic_nn.cu:396-427). */
 int ts_layer_schedule_stats(ts_layer_t* layer, int M, int* n_ctas, float* cta_cost, int* n_units);
+
+/* Pins the kernel variant of the layer: work units of at most 128 or 256 batch rows; 0 returns the
+ * choice to the scheduler.  Drops the cached schedules (synchronises the device).  A tuning and
+ * testing aid; the reference fixes its CTA tile at compile time (basic_nn.cu:250-259). */
+int ts_layer_set_unit_rows(ts_layer_t* layer, int unit_rows);
+
+/* The work distribution ts_masked_gemm would use for tiles with k_counts[t] kept rows and n_counts[t]
+ * kept columns, activations of K rows and batch size M, on n_ctas SMs -- without a device (pure host
+ * function).  Work units are (tile, run of batch rows); units_out receives one quadruple
+ * {cta, tile, m_begin, m_len} per unit, CTA by CTA in processing order (max_units quadruples of room;
+ * pass NULL to query *n_units_out first); cta_cost_out[n_ctas] receives the modelled load per CTA.
+ * While the activations fit in L2 the schedule is a balanced contiguous partition of the 64-row
+ * batch granules; beyond that a list schedule over L2-sized groups of tiles.  Replaces the reference's
+ * "tile t runs on stream t" (basic_nn.cu:402-427). */
+int ts_plan_schedule(int n_tiles, const int32_t* k_counts, const int32_t* n_counts, int64_t K, int M, int n_ctas,
+                     int unit_rows, int* unit_rows_out, int* n_ctas_out, int* n_units_out, int32_t* units_out,
+                     int max_units, float* cta_cost_out);
 
 /* Element-wise residual of a TEW mask as a sparse term, applied after ts_masked_gemm:
  *     Ct[n][m] = (col_written[n] ? Ct[n][m] : 0) + alpha * sum_p val[p] * At[row_idx[p]][m]
@@ -203,6 +223,9 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
 #define TS_MASK_BERT_TW_KN 6    /* type 8, tw2 without the sparsity remap,     MyHook.py:260-313 */
 #define TS_MASK_TOPK_L1 7       /* per-tile top-k by L1 row magnitude, ties to the lower row index;
                                    k = round(K*(1-sparsity/100)); no reference counterpart      */
+#define TS_MASK_TW_COLS_ROWS 8  /* the two stages of tiled_wise_2d with percentiles of their own:
+                                   columns at `g1percent`, then tile rows at `sparsity` (the
+                                   reference ties both to one remapped value, prune_algo.py:61)  */
 
 typedef struct ts_mask_result ts_mask_result_t;
 
@@ -213,13 +236,15 @@ typedef struct ts_mask_result ts_mask_result_t;
  *   sparsity       percent in [0, 100]; sparsity_is_f64 != 0 selects the double-precision percentile
  *                  arithmetic NumPy uses when the caller passes a numpy.float64 instead of a Python
  *                  number (the tw2 variants always switch to it after their remap, prune_algo.py:61)
- *   g1percent      element-wise residual percentage of the TEW variants, ignored otherwise
+ *   g1percent      element-wise residual percentage of the TEW variants; the column-stage percentile
+ *                  of TS_MASK_TW_COLS_ROWS; ignored otherwise
  *   masks_dev[l]   optional uint8 [Ks[l]][ld_masks[l]] outputs receiving the 0/1 mask (TW part plus,
  *                  for TEW, the residual elements); the array or any entry may be NULL
  *   residual_dev[l] optional uint8 [Ks[l]][Ns[l]] outputs receiving the residual elements only
  *   *out           tile structure of every layer (the TW part): read it with ts_mask_result_*
  * Allocates device scratch (norms, keys, histograms), synchronises `stream` several times and
- * returns when the masks are complete. */
+ * returns when the masks are complete.  Limits (TS_ERR_UNSUPPORTED beyond them): 65535 column tiles
+ * and 1048560 rows per layer. */
 int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
                      const int64_t* lds, int G, double sparsity, int sparsity_is_f64, double g1percent,
                      uint8_t* const* masks_dev, const int64_t* ld_masks, uint8_t* const* residual_dev,
@@ -263,7 +288,8 @@ int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, 
  *   scores_dev[l]  float32 [Ks[l]][lds[l]] (lds NULL: dense rows)
  *   masks_dev[l]   uint8 [Ks[l]][ld_masks[l]] (ld_masks NULL: dense rows), receives 0/1
  *   threshold_out  optional: the element-wise threshold (NaN for vector-wise)
- * Allocates device scratch for "ew", synchronises `stream`, returns when the masks are complete. */
+ * Allocates device scratch for "ew", synchronises `stream`, returns when the masks are complete.
+ * Limit: 1048560 rows per layer (TS_ERR_UNSUPPORTED beyond). */
 int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
                           const int64_t* lds, double sparsity, uint8_t* const* masks_dev, const int64_t* ld_masks,
                           double* threshold_out, void* stream);

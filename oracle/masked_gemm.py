@@ -16,6 +16,10 @@ in-binary comparison of the kernel with compaction + cuBLAS on unseeded random d
 basic_nn.cu:1081-1090), and its CUDA kernel cannot be run here (no GPU in the build container; the
 Volta-only MMA bodies compile to nothing for sm_100).  The two restatements below are checked
 against each other and against float64; beyond that the GEMM parity is unpinned by reference data.
+
+Acceptance rules the GPU tests apply: `max_rel_error` (matrix level), `elementwise_violations`
+(per element, relative with a floor) and the driver's own `checkout_errors` on data that does not
+cancel (positive operands), where its absolute and ratio tests are both meaningful.
 """
 from __future__ import annotations
 
@@ -75,3 +79,33 @@ def max_rel_error(test, ref):
     ref = np.asarray(ref, dtype=np.float64)
     denom = np.abs(ref).max()
     return float(np.abs(test - ref).max() / denom) if denom > 0 else float(np.abs(test).max())
+
+
+def masked_matmul_rows(At, W, tiles, rows, dtype=np.float64):
+    """Selected rows of Ct[N, M] by compaction (same definition as masked_matmul_compacted), for
+    shapes whose full product is too slow for a test: row n of Ct is the kept rows of At weighted by
+    column n of W restricted to the kept rows of the tile that owns n; zero when no tile keeps n."""
+    At = np.asarray(At)
+    W = np.asarray(W)
+    out = np.zeros((len(rows), At.shape[1]), dtype=dtype)
+    owner = np.full(tiles.N, -1, dtype=np.int64)
+    for t in range(tiles.n_tiles):
+        owner[tiles.tile_cols(t)] = t
+    for i, n in enumerate(rows):
+        t = owner[n]
+        if t < 0:
+            continue
+        r = tiles.tile_rows(t)
+        if len(r):
+            out[i] = W[r, n].astype(dtype) @ At[r, :].astype(dtype)
+    return out
+
+
+def elementwise_violations(test, ref, rtol=1e-2, floor=1e-3):
+    """Number of elements with |test - ref| > rtol * |ref| + floor * rms(ref): a per-element relative
+    bound (the `max relative error <= 1e-2` of 16-bit outputs with fp32 accumulation) with an absolute
+    floor tied to the typical magnitude, for elements that cancel to almost nothing."""
+    test = np.asarray(test, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    rms = float(np.sqrt(np.mean(ref * ref))) if ref.size else 0.0
+    return int((np.abs(test - ref) > rtol * np.abs(ref) + floor * rms).sum())

@@ -9,10 +9,10 @@ kernels implement.  Parity is pinned to NumPy 2.3 (the version in the build imag
 
 Pinning: tests/golden/*.npz hold masks produced by the reference's own prune_algo.py
 (Pruning/VGG/prune_algo.py, imported unmodified by tests/golden/make_golden.py) on seeded inputs;
-tests check every function below against them.  The BERT variants (Pruning/BERT/utils/MyHook.py)
-cannot be imported (the module imports TensorFlow, which is absent): `bert_type7` / `bert_type8`
-are pinned through their equality with tw1 / un-remapped tw2 on divisible shapes, `bert_type2` and
-`topk_l1` are restatements only (parity unpinned by reference output).
+tests check every function below against them.  The BERT variants (Pruning/BERT/utils/MyHook.py,
+pruning types 2, 7 and 8) are pinned the same way: make_golden.py imports that file unmodified beside
+a stub `tensorflow` module and stores the masks its `granularity_pruning` and `pruning` produce.
+`topk_l1` is a restatement only: no reference code performs that selection (parity unpinned).
 """
 from __future__ import annotations
 
@@ -78,14 +78,17 @@ def tw1(scores, sparsity, granularity=128):
             for layer, b, s in zip(norms, bounds, scores)]
 
 
-def tw2(scores, sparsity, granularity=128, remap=True, return_parts=False):
+def tw2(scores, sparsity, granularity=128, remap=True, return_parts=False, col_sparsity=None):
     """tiled_wise_2d (prune_algo.py:55-111): column pruning by a global percentile of column norms
     (divided by K), regrouping of the surviving columns into tiles of `granularity`, then row
-    pruning per tile by a second global percentile at the same (remapped) sparsity."""
-    if remap:
+    pruning per tile by a second global percentile at the same (remapped) sparsity.
+    col_sparsity (not in the reference, which ties both stages to one value at :61) gives the column
+    stage a percentile of its own; the row stage then uses `sparsity` as passed."""
+    if remap and col_sparsity is None:
         sparsity = 100 - np.sqrt(10000 - sparsity * 100)                      # :61
     col_norms = [np.linalg.norm(s, axis=0) / s.shape[0] for s in scores]       # :64
-    threshold = np.percentile([v for n in col_norms for v in n], sparsity)     # :65-66
+    threshold = np.percentile([v for n in col_norms for v in n],
+                              sparsity if col_sparsity is None else col_sparsity)     # :65-66
     col_masks = [n > threshold for n in col_norms]                             # :67
     pruned = [np.tile(m, (s.shape[0], 1)).reshape(s.shape) * s for m, s in zip(col_masks, scores)]  # :68-69
     bounds = [regroup_bounds(m, granularity) for m in col_masks]               # :72-89
@@ -136,6 +139,12 @@ def bert_type7(scores, sparsity, granularity=128):
 def bert_type8(scores, sparsity, granularity=128):
     """BERT pruning type 8 (MyHook.py:260-313): tw2 without the sparsity remap."""
     return tw2(scores, sparsity, granularity, remap=False)
+
+
+def tw_cols_rows(scores, col_sparsity, row_sparsity, granularity=128):
+    """The machinery of tiled_wise_2d with independent column and row percentiles ("10 % of the
+    columns, then 75 % of the rows of every tile").  No reference function has this call shape."""
+    return tw2(scores, row_sparsity, granularity, remap=False, col_sparsity=col_sparsity)
 
 
 def bert_type2(score, sparsity, granularity=128):

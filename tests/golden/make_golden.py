@@ -1,15 +1,20 @@
 """Generates tests/golden/tw_masks.npz by running the REFERENCE's mask builder, unmodified.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where a checkout of the reference repository is available:
 
-    python tests/golden/make_golden.py [path-to-reference]
+    python tests/golden/make_golden.py <path-to-reference-checkout>
 
 It imports Pruning/VGG/prune_algo.py from the reference tree and calls
 pruning_fun(name)(scores, sparsity[, granularity][, g1percent]) (prune_algo.py:267-278) on seeded
-inputs; the resulting 0/1 masks are stored bit-packed.  Inputs are not stored: `case_inputs`
-regenerates them from the seed, and the tests call it too.  Seeded synthetic weights stand in for
-the trained networks the reference pruned (N(0, 0.02) like BERT's initialiser, He-normal for the
-conv kernel, U(-0.1, 0.1) like the NMT LSTM).
+inputs; the resulting 0/1 masks are stored bit-packed.  The BERT variants live in
+Pruning/BERT/utils/MyHook.py, whose only TensorFlow uses at import time are the module-level import
+and two `tf.train.SessionRunHook` base classes; a stub module with that one attribute lets the file be
+imported as it is, and `granularity_pruning` (:202-214, pruning type 2) and `pruning(...)` types 7 and
+8 (:216-313) are then called directly, with a stand-in session that captures the masks the function
+feeds to its assign ops.  Inputs are not stored: `case_inputs` regenerates them from the seed, and
+the tests call it too.  Seeded synthetic weights stand in for the trained networks the reference
+pruned (N(0, 0.02) like BERT's initialiser, He-normal for the conv kernel, U(-0.1, 0.1) like the NMT
+LSTM).
 """
 from __future__ import annotations
 
@@ -33,6 +38,9 @@ CASES = {
     "tw1m_small":       ("tw1m", [(96, 320)], 70.0, 128, 5.0, 31, "normal"),
     "tw1m_lstm":        ("tw1m", [(256, 512), (128, 512)], 75.0, 128, 1.5, 32, "uniform"),
     "tw2m_small":       ("tw2m", [(96, 384)], 70.0, 128, 1.0, 41, "normal"),
+    # benchmark-configuration sizes: VGG16 conv5 as a 4608 x 512 matrix, the NMT LSTM gate matrix
+    "tw2_vgg_conv5":    ("tw2", [(3, 3, 512, 512)], 75.0, 128, None, 3001, "he"),
+    "tw1m_nmt_lstm":    ("tw1m", [(2048, 4096)], 75.0, 128, 1.5, 4001, "uniform"),
     # baseline patterns (no granularity argument): element-wise and vector-wise
     "ew_small":         ("ew", [(96, 320)], 75.0, None, None, 51, "normal"),
     "ew_group":         ("ew", [(64, 256), (80, 200), (48, 130)], 62.5, None, None, 52, "normal"),
@@ -43,10 +51,27 @@ CASES = {
 }
 
 
+# BERT pruning types (Pruning/BERT/utils/MyHook.py): name -> (type, shapes, sparsity, granularity, seed, dist).
+# Type 2 prunes one matrix at a time; types 7 and 8 take the whole list under one threshold and need
+# 768 % granularity == 0 and N % granularity == 0.
+BERT_CASES = {
+    "bert2_small":      (2, [(96, 256)], 75.0, 128, 71, "normal"),
+    "bert2_ffn1":       (2, [(768, 3072)], 75.0, 128, 2003, "bert"),
+    "bert2_g64":        (2, [(128, 384)], 40.0, 64, 72, "uniform"),
+    "bert7_group":      (7, [(96, 256), (64, 384)], 60.0, 128, 73, "normal"),
+    "bert7_attn":       (7, [(768, 768)], 75.0, 128, 2002, "bert"),
+    "bert8_group":      (8, [(96, 384), (72, 256)], 50.0, 64, 74, "normal"),
+    "bert8_qkv":        (8, [(768, 2304)], 50.0, 128, 2001, "bert"),
+}
+
+
 def case_inputs(name: str):
     """The seeded score matrices of a case, as the reference's hooks hand them over: 2-D arrays of
     absolute values (img2col_forward, prune_algo.py:16-24, reshapes HWIO kernels and takes abs)."""
-    algo, shapes, sparsity, gran, g1, seed, dist = CASES[name]
+    if name in BERT_CASES:
+        _, shapes, sparsity, gran, seed, dist = BERT_CASES[name]
+    else:
+        algo, shapes, sparsity, gran, g1, seed, dist = CASES[name]
     g = np.random.Generator(np.random.PCG64(seed))
     out = []
     for shp in shapes:
@@ -66,8 +91,55 @@ def case_inputs(name: str):
     return out
 
 
+def import_bert_hook(ref: str):
+    """The reference's Pruning/BERT/utils/MyHook.py, imported unmodified next to a stub `tensorflow`
+    module that provides the one attribute the file touches while it is being imported."""
+    import importlib.util
+    import types
+    if "tensorflow" not in sys.modules:
+        tf = types.ModuleType("tensorflow")
+        tf.train = types.SimpleNamespace(SessionRunHook=object)
+        sys.modules["tensorflow"] = tf
+    spec = importlib.util.spec_from_file_location(
+        "reference_bert_myhook", os.path.join(ref, "Pruning", "BERT", "utils", "MyHook.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+class _Placeholder:
+    """Stands in for a TF placeholder: hashable, with the shape the reference asserts on."""
+
+    def __init__(self, shape):
+        self.shape = tuple(shape)
+
+
+class _Session:
+    """Stands in for tf.Session: keeps the feed dict of the one `run(assign_ops, feed)` call."""
+
+    def __init__(self):
+        self.feed = None
+
+    def run(self, ops, feed):
+        self.feed = feed
+
+
+def run_bert_case(hook_mod, name: str):
+    ptype, shapes, sparsity, gran, seed, dist = BERT_CASES[name]
+    scores = case_inputs(name)
+    pruner = hook_mod.SparseColumnPruningRank()
+    if ptype == 2:
+        return [pruner.granularity_pruning(768, gran, sc, sparsity) for sc in scores]
+    ph = [_Placeholder(sc.shape) for sc in scores]
+    sess = _Session()
+    pruner.pruning("golden", scores, sparsity, ph, sess, None, ptype, gran)
+    return [sess.feed[p] for p in ph]
+
+
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path-to-reference-checkout>")
+    ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "Pruning", "VGG"))
     import prune_algo  # the reference's own module
     store = {}
@@ -78,6 +150,14 @@ def main():
             masks = fn(scores, sparsity)
         else:
             masks = fn(scores, sparsity, gran) if g1 is None else fn(scores, sparsity, gran, g1)
+        for i, m in enumerate(masks):
+            m = np.asarray(m).astype(bool)
+            store[f"{name}/{i}/shape"] = np.asarray(m.shape, dtype=np.int32)
+            store[f"{name}/{i}/bits"] = np.packbits(m.reshape(-1))
+        print(name, [float(np.asarray(m).mean()) for m in masks])
+    hook_mod = import_bert_hook(ref)
+    for name in BERT_CASES:
+        masks = run_bert_case(hook_mod, name)
         for i, m in enumerate(masks):
             m = np.asarray(m).astype(bool)
             store[f"{name}/{i}/shape"] = np.asarray(m.shape, dtype=np.int32)

@@ -47,3 +47,31 @@ def test_bert_pruned_model_pickle(tmp_path):
     assert np.array_equal(W, kernel * mi[:, None] * mo[None, :])
     ts = importers.tiles_from_bert_layer(L, K, N, 128)
     assert np.array_equal(ts.dense_mask(), (mi[:, None] * mo[None, :]) != 0)
+
+
+def test_bert_dumped_model_pickle(tmp_path):
+    """The layout dump_pruned_model.py writes (Pruning/BERT/utils/dump_pruned_model.py:118-140)."""
+    mask = load_golden("bert7_group")[0]                        # a type-7 mask of the reference, 96 x 256
+    g = np.random.Generator(np.random.PCG64(6))
+    kernel = g.standard_normal(mask.shape).astype(np.float32)
+    bias = g.standard_normal(mask.shape[1]).astype(np.float32)
+    scope = "bert/encoder/layer_0/intermediate/dense"
+    model = {"transformer_ckpt": {
+        "origin_ckpt": {scope + "/kernel:0": kernel, scope + "/bias:0": bias},
+        "masked_ckpt": {scope + "/kernel:0": kernel * mask},
+        "absolute_mask": {scope + "/mask-o:0": mask.astype(np.float32)}}}
+    p = tmp_path / "model.pkl"
+    with open(p, "wb") as f:
+        pickle.dump(model, f, pickle.HIGHEST_PROTOCOL)
+    layers = importers.load_bert_dumped_model(str(p))
+    assert len(layers) == 1
+    L = layers[0]
+    assert L["name"] == scope + "/kernel:0" and np.array_equal(L["mask"], mask)
+    assert np.array_equal(L["masked_kernel"], kernel * mask) and np.array_equal(L["bias"], bias)
+    ts, res = importers.tiles_from_dumped_layer(L, 128)
+    assert not res.any() and np.array_equal(ts.dense_mask(), mask)
+    with open(p, "wb") as f:
+        pickle.dump({"something": 1}, f)
+    import pytest
+    with pytest.raises(ValueError):
+        importers.load_bert_dumped_model(str(p))

@@ -1,7 +1,9 @@
 """Tensor-core masked GEMM (through the C ABI) vs the CPU oracle and vs its CUDA-core twin.
 
-Acceptance bound: max |C - C_ref| / max |C_ref| <= 1e-2 against the float32 oracle evaluated on the
-same 16-bit-rounded inputs (fp16/bf16 inputs, fp32 accumulation).
+Acceptance, against the float32/float64 oracle evaluated on the same 16-bit-rounded inputs (fp16/bf16
+inputs, fp32 accumulation): the matrix-level bound max |C - C_ref| / max |C_ref| <= 1e-2 AND the
+per-element bound |C - C_ref| <= 1e-2 |C_ref| + 1e-3 rms(C_ref) on every element; the reference
+driver's own rule (basic_nn.cu:785) is applied where its absolute test is meaningful (positive data).
 """
 import numpy as np
 import pytest
@@ -51,16 +53,22 @@ CASES = [
 ]
 
 
+def _accept(out, ref):
+    assert og.max_rel_error(out, ref) <= TOL
+    bad = og.elementwise_violations(out, ref, rtol=1e-2, floor=1e-3)
+    assert bad == 0, f"{bad} of {ref.size} elements outside |err| <= 1e-2 |ref| + 1e-3 rms(ref)"
+
+
 @pytest.mark.parametrize("K,N,M,keep,dtype,col_keep", CASES)
-@pytest.mark.parametrize("unit_rows", ["128", "256"])
-def test_matches_oracle(K, N, M, keep, dtype, col_keep, unit_rows, monkeypatch):
-    monkeypatch.setenv("TS_UNIT_ROWS", unit_rows)
+@pytest.mark.parametrize("unit_rows", [128, 256, 0])
+def test_matches_oracle(K, N, M, keep, dtype, col_keep, unit_rows):
     layer, At, A16, W16 = _case(K, N, M, keep, dtype, K + N + M, col_keep)
+    layer.set_unit_rows(unit_rows)              # both kernel variants, and the scheduler's own choice
     ref = og.masked_matmul_compacted(A16, W16, layer.tiles)
     Ct = layer.masked_gemm(At)
     layer.check()
     out = Ct.float().cpu().numpy()
-    assert og.max_rel_error(out, ref) <= TOL
+    _accept(out, ref)
     # columns no tile keeps are untouched (the output buffer starts as zeros)
     dead = ~layer.tiles.col_mask()
     assert not out[dead].any()
@@ -261,4 +269,173 @@ def test_peer_copies_receive_the_same_rows():
     extra = [torch.zeros((512, 520), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
     out = layer.masked_gemm(At, peers=[e.data_ptr() for e in extra])
     assert torch.equal(extra[0], out) and torch.equal(extra[1], out)
+    layer.close()
+
+
+# ------------------------------------------------------------------------------------------------
+# The benchmark configurations at their own sizes
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["qkv", "attn_out", "ffn1", "ffn2"])
+@pytest.mark.parametrize("sparsity", [50.0, 75.0, 90.0])
+def test_bert_layer_gemms_with_gpu_built_tw1_masks(name, sparsity):
+    """BERT-base GEMMs at M = 4096, fp16, with the tw1 masks the GPU mask builder derives from the
+    synthetic weights (non-uniform kept rows per tile): the workload bench.py times."""
+    from tilesparsity_b200 import TWLayer, build_mask
+    A, W = synth.bert_gemm(name, 4096)
+    Wd = torch.from_numpy(W).cuda()
+    res = build_mask("tw1", [Wd.abs()], sparsity, 128)
+    layer = TWLayer(res.tiles[0], torch.float16, Wd.device)
+    layer.pack(Wd)
+    At = torch.from_numpy(np.ascontiguousarray(A.T)).to(torch.float16).cuda()
+    out = layer.masked_gemm(At).float().cpu().numpy()
+    layer.check()
+    ref = og.masked_matmul_compacted(At.float().cpu().numpy(), Wd.half().float().cpu().numpy(), layer.tiles)
+    _accept(out, ref)
+    # the dense-masked form the reference's model code computes (modeling.py:1001-1003)
+    mask = res.masks[0].cpu().numpy()
+    dense = og.masked_matmul_dense(At.float().cpu().numpy().T, Wd.half().float().cpu().numpy(), mask).T
+    _accept(out, dense)
+    layer.close()
+
+
+@pytest.mark.parametrize("algo,sparsity,g1", [("tw2", 75.0, None), ("tw_cols_rows", 75.0, 10.0)])
+def test_vgg_conv5_shape_at_full_batch(algo, sparsity, g1):
+    """VGG16 conv5 as a GEMM: M = 64 x 14 x 14 = 12544, K = 4608, N = 512, bf16, activations after a
+    ReLU (about half zeros), He-normal weights; the reference's tw2 at 75 % and the "10 % of the
+    columns, then 75 % of the rows" mask, both built by the GPU mask builder."""
+    from tilesparsity_b200 import TWLayer, build_mask
+    g = synth.rng(3001)
+    M, K, N = 12544, 4608, 512
+    A = np.maximum(g.standard_normal((M, K), dtype=np.float32), 0)
+    W = g.standard_normal((K, N), dtype=np.float32) * np.float32(np.sqrt(2.0 / K))
+    Wd = torch.from_numpy(W).cuda()
+    res = build_mask(algo, [Wd.abs()], sparsity, 128, g1)
+    ts = res.tiles[0]
+    if algo == "tw_cols_rows":
+        want = om_tw_cols_rows(np.abs(W), g1, sparsity)
+        assert np.array_equal(res.masks[0].cpu().numpy(), want)
+        assert abs(ts.col_mask().mean() - 0.9) < 0.01
+    layer = TWLayer(ts, torch.bfloat16, Wd.device)
+    layer.pack(Wd)
+    At = torch.from_numpy(np.ascontiguousarray(A.T)).to(torch.bfloat16).cuda()
+    out = layer.masked_gemm(At).float().cpu().numpy()
+    layer.check()
+    ref = og.masked_matmul_compacted(At.float().cpu().numpy(), Wd.bfloat16().float().cpu().numpy(), ts)
+    _accept(out, ref)
+    assert not out[~ts.col_mask()].any()
+    layer.close()
+
+
+def om_tw_cols_rows(score, col_sparsity, row_sparsity):
+    from oracle import tw_masks as om
+    return np.asarray(om.tw_cols_rows([score], col_sparsity, row_sparsity, 128)[0], dtype=bool)
+
+
+def test_nmt_lstm_tew_at_config_size():
+    """NMT LSTM gate GEMM: K = 2048, N = 4096, M = 6400, fp16, W ~ U(-0.1, 0.1), TEW = tw1m at 75 % with
+    a 1.5 % element-wise residual kept as a sparse term; against A @ (W * mask_tew)."""
+    from tilesparsity_b200 import TEWLayer, build_mask
+    g = synth.rng(4001)
+    K, N, M = 2048, 4096, 6400
+    W = g.uniform(-0.1, 0.1, size=(K, N)).astype(np.float32)
+    A = g.standard_normal((M, K), dtype=np.float32)
+    Wd = torch.from_numpy(W).cuda()
+    res = build_mask("tw1m", [Wd.abs()], 75.0, 128, 1.5, want_residual=True)
+    layer = TEWLayer(Wd, res.tiles[0], res.residuals[0], torch.float16)
+    assert abs(layer.nnz / (K * N) - 0.015) < 0.002
+    At = torch.from_numpy(np.ascontiguousarray(A.T)).to(torch.float16).cuda()
+    out = layer.masked_gemm(At).float().cpu().numpy()
+    layer.tw.check()
+    mask = res.masks[0].cpu().numpy()
+    ref = og.masked_matmul_dense(At.float().cpu().numpy().T, Wd.half().float().cpu().numpy(), mask).T
+    _accept(out, ref)
+    layer.close()
+
+
+@pytest.mark.parametrize("n", [4096, 8192])
+def test_skewed_squares_against_the_oracle_on_sampled_rows(n):
+    """M = N = K = n, bf16, per-tile kept-row counts ~ Beta(2,5): 96 output rows (two per sampled tile
+    plus random ones) against the float64 oracle; the whole output against the CUDA-core twin."""
+    from tilesparsity_b200 import TWLayer
+    from tilesparsity_b200.tiles import tiles_from_lists
+    nt = n // 128
+    counts = synth.beta_skewed_counts(n, nt, 0.25, 5000 + int(np.log2(n)))
+    g = synth.rng(5000 + int(np.log2(n)))
+    lists = [np.sort(g.choice(n, size=int(c), replace=False)).astype(np.int32) for c in counts]
+    ts = tiles_from_lists(n, n, 128, lists)
+    gen = torch.Generator(device="cuda").manual_seed(n)
+    W = torch.randn((n, n), generator=gen, device="cuda", dtype=torch.float32)
+    At = torch.randn((n, n), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    layer = TWLayer(ts, torch.bfloat16, W.device)
+    layer.pack(W)
+    out = layer.masked_gemm(At)
+    layer.check()
+    heavy, light = int(np.argmax(counts)), int(np.argmin(counts))
+    rows = sorted(set([heavy * 128, heavy * 128 + 127, light * 128, light * 128 + 5] +
+                      [int(r) for r in g.choice(n, size=92, replace=False)]))
+    ref = og.masked_matmul_rows(At.float().cpu().numpy(), W.bfloat16().float().cpu().numpy(), ts, rows)
+    got = out[torch.tensor(rows, device="cuda")].float().cpu().numpy()
+    _accept(got, ref)
+    if n <= 4096:
+        twin = layer.masked_gemm(At, simt=True).float()
+        assert float((out.float() - twin).abs().max() / twin.abs().max()) <= TOL
+    layer.close()
+
+
+def test_reference_drivers_acceptance_rule_on_positive_data():
+    """The perf driver's `checkout` (basic_nn.cu:771-798: ratio either way > 1 + err, or |diff| > err,
+    err = 1e-2) with no relaxation, on operands that do not cancel."""
+    from tilesparsity_b200 import TWLayer
+    g = synth.rng(123)
+    K, N, M = 768, 1024, 1024
+    A = g.random((M, K), dtype=np.float32)
+    W = g.random((K, N), dtype=np.float32) * np.float32(0.05)
+    lists = synth.random_kept_lists(K, N // 128, 192, 124)
+    Wd = torch.from_numpy(W).cuda()
+    layer = TWLayer.from_lists(Wd, lists, None, 128, torch.float16)
+    At = torch.from_numpy(np.ascontiguousarray(A.T)).to(torch.float16).cuda()
+    out = layer.masked_gemm(At).float().cpu().numpy()
+    ref = og.masked_matmul_compacted(At.float().cpu().numpy(), Wd.half().float().cpu().numpy(), layer.tiles)
+    assert og.checkout_errors(out, ref, 1e-2) == 0
+    layer.close()
+
+
+def test_host_buffer_path_returns_zeros_in_pruned_columns_after_m_or_tiles_change():
+    """The staging output of the host-buffer entry point is zeroed lazily: a different batch size (the
+    row pitch changes) or a different tile set must not let earlier results show through in the
+    columns no tile keeps."""
+    from tilesparsity_b200 import TWLayer
+    from tilesparsity_b200.tiles import tiles_from_lists
+    g = synth.rng(77)
+    K, N = 256, 512
+    W = (g.standard_normal((K, N), dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    Wd = torch.from_numpy(W).cuda()
+    col1 = g.random(N) < 0.7
+    col2 = g.random(N) < 0.5
+
+    def lists_for(col):
+        nt = len(tile_bounds_from_col_mask(col, 128)) - 1
+        return synth.random_kept_lists(K, nt, 64, int(col.sum()))
+
+    layer = TWLayer.from_lists(Wd, lists_for(col1), col1, 128, torch.float16)
+    for M in (512, 256, 384):
+        hA = torch.from_numpy(g.standard_normal((K, M), dtype=np.float32)).to(torch.float16).pin_memory()
+        hC = torch.full((N, M), 9.0, dtype=torch.float16).pin_memory()
+        layer.masked_gemm_host(hA, hC)
+        ref = og.masked_matmul_compacted(hA.float().numpy(), Wd.half().float().cpu().numpy(), layer.tiles)
+        _accept(hC.float().numpy(), ref)
+        assert not hC.numpy()[~col1].any(), f"stale values in pruned columns at M = {M}"
+    layer.close()
+    # the same handle re-used with another tile set
+    layer = TWLayer.from_lists(Wd, lists_for(col1), col1, 128, torch.float16)
+    hA = torch.from_numpy(g.standard_normal((K, 256), dtype=np.float32)).to(torch.float16).pin_memory()
+    hC = torch.empty((N, 256), dtype=torch.float16).pin_memory()
+    layer.masked_gemm_host(hA, hC)
+    ts2 = tiles_from_lists(K, N, 128, lists_for(col2), col2)
+    layer.retile(ts2)
+    layer.pack(Wd)
+    layer.masked_gemm_host(hA, hC)
+    ref = og.masked_matmul_compacted(hA.float().numpy(), Wd.half().float().cpu().numpy(), ts2)
+    _accept(hC.float().numpy(), ref)
+    assert not hC.numpy()[~col2].any()
     layer.close()

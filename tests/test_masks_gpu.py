@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 import torch
 
-from make_golden import CASES, case_inputs, load_golden
+from make_golden import BERT_CASES, CASES, case_inputs, load_golden
 from oracle import tw_masks as om
 
 pytestmark = pytest.mark.gpu
@@ -103,6 +103,24 @@ def test_matches_oracle(algo, sparsity, gran, g1, shapes, seed):
     res = _gpu_masks(algo, scores, sparsity, gran, g1)
     for m, r in zip(res.masks, ref):
         assert np.array_equal(m.cpu().numpy(), np.asarray(r, dtype=bool))
+
+
+@pytest.mark.parametrize("name", sorted(BERT_CASES))
+def test_bert_types_match_reference_golden(name):
+    """Pruning types 2, 7 and 8 against the masks of the reference's own MyHook.py: bit for bit."""
+    ptype, shapes, sparsity, gran, seed, dist = BERT_CASES[name]
+    scores = case_inputs(name)
+    gold = load_golden(name)
+    mode = {2: "bert_type2", 7: "bert_type7", 8: "bert_type8"}[ptype]
+    if ptype == 2:
+        got = [_gpu_masks(mode, [sc], sparsity, gran, None).masks[0] for sc in scores]
+    else:
+        got = _gpu_masks(mode, scores, sparsity, gran, None).masks
+    assert len(got) == len(gold)
+    for m, g in zip(got, gold):
+        m = m.cpu().numpy()
+        assert m.shape == g.shape
+        assert np.array_equal(m, g), f"{name}: {int((m != g).sum())} mask bits differ from the reference"
 
 
 def test_bert_variants_and_topk():

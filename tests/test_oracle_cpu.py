@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from make_golden import CASES, case_inputs, load_golden
+from make_golden import BERT_CASES, CASES, case_inputs, load_golden
 from oracle import masked_gemm as og
 from oracle import tw_masks as om
 from tilesparsity_b200 import synth
@@ -18,6 +18,21 @@ def test_oracle_reproduces_reference_masks(name):
         mine = fn(scores, sparsity)
     else:
         mine = fn(scores, sparsity, gran) if g1 is None else fn(scores, sparsity, gran, g1)
+    gold = load_golden(name)
+    assert len(mine) == len(gold)
+    for a, b in zip(mine, gold):
+        assert np.array_equal(np.asarray(a, dtype=bool), b)
+
+
+@pytest.mark.parametrize("name", sorted(BERT_CASES))
+def test_oracle_reproduces_reference_bert_masks(name):
+    """Masks of the reference's own Pruning/BERT/utils/MyHook.py (types 2, 7, 8), stored by make_golden."""
+    ptype, shapes, sparsity, gran, seed, dist = BERT_CASES[name]
+    scores = case_inputs(name)
+    if ptype == 2:
+        mine = [om.bert_type2(sc, sparsity, gran) for sc in scores]
+    else:
+        mine = (om.bert_type7 if ptype == 7 else om.bert_type8)(scores, sparsity, gran)
     gold = load_golden(name)
     assert len(mine) == len(gold)
     for a, b in zip(mine, gold):

@@ -28,14 +28,23 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
     g = np.random.Generator(np.random.PCG64(2024))
     first = np.abs(g.standard_normal((768, 3072), dtype=np.float32) * np.float32(0.02))
     second = np.abs(g.standard_normal((300, 1000), dtype=np.float32))          # other shape, ragged last tile
-    for scores, sparsity, G in [(first, 75.0, 128), (second, np.float64(40.0), 128), (first, 90.0, 64)]:
+    for call, (scores, sparsity, G) in enumerate([(first, 75.0, 128), (second, np.float64(40.0), 128),
+                                                  (first, 90.0, 64)]):
         want, want_thr = _expected_flags(scores, sparsity, G)
         dev = torch.from_numpy(scores).cuda()
         out = torch.full(want.shape, 255, dtype=torch.uint8, device="cuda")    # caller-owned output
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         got, thr = tm.tw1_row_keep_noalloc(dev, sparsity, G, out=out)
+        torch.cuda.synchronize()
+        free_after = torch.cuda.mem_get_info()[0]
         assert got.data_ptr() == out.data_ptr()
         assert np.array_equal(got.cpu().numpy(), want)
         assert thr == want_thr
+        # The property the entry point exists for: the device's free memory is the same after the call
+        # as before it.  (The very first call of a process may still load the kernels' code.)
+        if call > 0:
+            assert free_after == free_before, f"call {call} changed free device memory by {free_before - free_after} bytes"
 
 
 def test_inputs_beyond_the_built_in_scratch_are_rejected():

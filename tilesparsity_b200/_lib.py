@@ -10,15 +10,14 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# TILESPARSE_LIB points the loader at another build of the same library (e.g. a traced one).
-LIB_PATH = os.environ.get("TILESPARSE_LIB") or os.path.join(HERE, "libtilesparse.so")
+LIB_PATH = os.path.join(HERE, "libtilesparse.so")
 
 TS_OK = 0
 TS_ERR_INVALID, TS_ERR_CUDA, TS_ERR_TIMEOUT, TS_ERR_UNSUPPORTED, TS_ERR_NOMEM = 1, 2, 3, 4, 5
 TS_DTYPE_F16, TS_DTYPE_BF16, TS_DTYPE_F32 = 0, 1, 2
 TS_INDEX_ABSOLUTE, TS_INDEX_RELATIVE = 0, 1
 MASK_MODES = {"tw1": 0, "tw2": 1, "tw1m": 2, "tw2m": 3, "bert_type2": 4, "bert_type7": 5, "bert_type8": 6,
-              "topk_l1": 7}
+              "topk_l1": 7, "tw_cols_rows": 8}
 
 
 PATTERN_MODES = {"ew": 0, "vw": 1}
@@ -70,6 +69,9 @@ SIGNATURES = {
     "ts_masked_gemm_host_wait": (C.c_int, [_vp, _vp]),
     "ts_layer_check": (C.c_int, [_vp, _vp]),
     "ts_layer_schedule_stats": (C.c_int, [_vp, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)]),
+    "ts_layer_set_unit_rows": (C.c_int, [_vp, C.c_int]),
+    "ts_plan_schedule": (C.c_int, [C.c_int, _i32p, _i32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int),
+                                   C.POINTER(C.c_int), C.POINTER(C.c_int), _i32p, C.c_int, C.POINTER(C.c_float)]),
     "ts_stream_gemm_nn": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_float, _vp, _vp, C.c_float, _vp, C.c_int,
                                     C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(_vp), C.POINTER(_vp),
                                     C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, _vp]),

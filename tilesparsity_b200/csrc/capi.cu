@@ -5,7 +5,6 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -102,12 +101,6 @@ int make_out_tmap(CUtensorMap* map, int dtype, const void* Ct, long long n_rows,
   return TS_OK;
 }
 
-// TS_STORE=lsu turns the epilogue's TMA stores off (debugging aid).
-bool use_tma_store() {
-  const char* e = getenv("TS_STORE");
-  return !(e && strcmp(e, "lsu") == 0);
-}
-
 struct Schedule {
   ts::WorkItem* d_units = nullptr;
   ts::BlockDesc* d_blocks = nullptr;
@@ -120,34 +113,214 @@ struct Schedule {
   std::vector<float> cta_cost;
 };
 
-// Cost of one work unit in 64-row K blocks; the constant stands for the epilogue (TMEM read-out,
-// conversion and the output rows' bulk stores), which weighs about as much as two K blocks.
-inline float unit_cost(int k_count) { return static_cast<float>((k_count + 63) / 64) + 2.0f; }
-
-// Batch rows per work unit: 256-row units halve the weight traffic per output; 128-row units are
-// used when there are too few 256-row units to occupy even half of the SMs.  The
-// TS_UNIT_ROWS environment variable (128 or 256) overrides the choice.
-int choose_unit_rows(int n_live_tiles, int M, int n_ctas) {
-  if (const char* e = getenv("TS_UNIT_ROWS")) {
-    const int v = atoi(e);
-    if (v == 128 || v == 256) return v;
-  }
-  const long long units256 = static_cast<long long>(n_live_tiles) * ((M + 255) / 256);
-  return 2 * units256 >= n_ctas ? 256 : 128;
+// Cost of one work unit of `granules` 64-row batch granules over a tile with k_count kept rows, in
+// units of 8 KiB moved between L2 and the SM: per 64-row K block 16 KiB of packed weights and 8 KiB of
+// gathered activations per granule; per granule 16 KiB of output; and a constant for the hand-over
+// between consecutive units of a CTA (accumulator swap, pipeline refill).
+inline float unit_cost(int k_count, int granules) {
+  const int kb = (k_count + 63) / 64;
+  return static_cast<float>(kb * (2 + granules) + 2 * granules + 3);
 }
 
-// Work distribution for the persistent kernel.  Units are (tile, run of batch rows); tiles are taken
-// in descending kept-K order and cut into units of `unit_rows` batch rows (the last unit of a tile
-// may be narrower, a multiple of 64 rows).  Assignment is longest-processing-time list scheduling.
-// Cutting the last, partial wave of units into narrower ones so that every SM gets a piece was
-// measured and dropped: narrow units keep fewer bytes in flight per SM and re-read the packed
-// weights more often, which cost as much as the better balance gained (BERT layer +-1 %, VGG conv5
-// shape -20 %).
+struct Unit {
+  int tile, m_begin, m_len;
+  float cost;
+};
+
+// While the activations fit comfortably in L2 (K*M*2 bytes <= 64 MiB) the schedule is a balanced
+// contiguous partition; beyond that it is the blocked list schedule further down.
+inline bool small_activations(long long at_rows, int M) { return 2LL * at_rows * M <= (64LL << 20); }
+
+// Balanced contiguous partition.  The 64-row batch granules of all tiles, tile after tile in `order`,
+// form one line; every CTA receives one contiguous piece of it, cut into units of at most `cap`
+// granules that do not cross a tile boundary.  Three candidates: (a) the pieces whose largest cost is
+// minimal (binary search on the bound, greedy filling for a given bound); (b) pieces of equal weight
+// (kept K blocks + output per granule), which always spreads the line over all n_ctas SMs; (c) when
+// there are no more tiles than SMs, every tile split evenly among a number of CTAs of its own, the
+// CTAs handed out one by one to the tile with the costliest piece, so that no CTA changes tile and
+// re-fetches packed weights.  (c) is taken when its largest piece is no costlier than the others'
+// (within 3 %), else (b) under the same rule, else (a).  All of them fill the machine when there are
+// fewer 256-row units than SMs (a 768-column layer has 6 tiles x 16 such units for 148 SMs) and leave
+// no partial last wave.  A CTA's units are consecutive runs of one tile.
+void partition_contiguous(const std::vector<ts::TileDesc>& tiles, const std::vector<int>& order, int M, int cap,
+                          int n_ctas, std::vector<std::vector<Unit>>* lists) {
+  const int granules = (M + 63) / 64;
+  const long long line = static_cast<long long>(order.size()) * granules;
+  // pieces given by their exclusive end positions on the line -> unit lists and the largest cost
+  auto cut = [&](const std::vector<long long>& ends, std::vector<std::vector<Unit>>* out) -> double {
+    double worst = 0.0;
+    if (out) out->clear();
+    long long pos = 0;
+    for (long long end : ends) {
+      if (end <= pos) continue;
+      if (out) out->push_back({});
+      double load = 0.0;
+      while (pos < end) {
+        const int t = order[pos / granules];
+        const int g0 = static_cast<int>(pos % granules);
+        const int len = static_cast<int>(std::min<long long>({cap, granules - g0, end - pos}));
+        const Unit u{t, g0 * 64, len * 64, unit_cost(tiles[t].k_count, len)};
+        if (out) out->back().push_back(u);
+        load += u.cost;
+        pos += len;
+      }
+      worst = std::max(worst, load);
+    }
+    return worst;
+  };
+  // (a) greedy filling under a bound; returns false when it needs more than n_ctas pieces
+  auto fill = [&](double bound, std::vector<long long>* ends) -> bool {
+    if (ends) ends->clear();
+    int used = 1;
+    double load = 0.0;
+    int open_tile = -1, open_len = 0;
+    long long pos = 0;
+    for (int t : order) {
+      const int kc = tiles[t].k_count;
+      const double first = unit_cost(kc, 1), more = unit_cost(kc, 2) - unit_cost(kc, 1);
+      for (int g = 0; g < granules; ++g, ++pos) {
+        const bool extend = open_tile == t && open_len < cap;
+        double delta = extend ? more : first;
+        if (load > 0.0 && load + delta > bound) {
+          if (++used > n_ctas) return false;
+          if (ends) ends->push_back(pos);
+          load = 0.0;
+          delta = first;
+          open_len = 0;
+        } else if (!extend) {
+          open_len = 0;
+        }
+        open_tile = t;
+        ++open_len;
+        load += delta;
+      }
+    }
+    if (ends) ends->push_back(line);
+    return true;
+  };
+  double lo = 0.0, hi = 0.0, weight = 0.0;
+  for (int t : order) {
+    lo = std::max<double>(lo, unit_cost(tiles[t].k_count, 1));
+    hi += static_cast<double>(unit_cost(tiles[t].k_count, 1)) * granules;
+    weight += static_cast<double>((tiles[t].k_count + 63) / 64 + 2) * granules;
+  }
+  lo = std::max(lo, hi / std::max(1, n_ctas) * 0.25);
+  for (int it = 0; it < 40 && hi - lo > 0.25; ++it) {
+    const double mid = 0.5 * (lo + hi);
+    if (fill(mid, nullptr)) hi = mid;
+    else lo = mid;
+  }
+  std::vector<long long> ends_a, ends_b;
+  fill(hi, &ends_a);
+  // (b) equal weight: granule i belongs to the piece its weight midpoint falls into
+  {
+    const double share = weight / n_ctas;
+    double cum = 0.0;
+    int piece = 0;
+    long long pos = 0;
+    for (int t : order) {
+      const double wt = static_cast<double>((tiles[t].k_count + 63) / 64 + 2);
+      for (int g = 0; g < granules; ++g, ++pos) {
+        const int want = std::min<int>(n_ctas - 1, static_cast<int>((cum + 0.5 * wt) / share));
+        while (piece < want) {
+          ends_b.push_back(pos);
+          ++piece;
+        }
+        cum += wt;
+      }
+    }
+    ends_b.push_back(line);
+  }
+  // (c) per-tile split
+  std::vector<long long> ends_c;
+  const int nt = static_cast<int>(order.size());
+  if (nt <= n_ctas) {
+    auto piece_cost = [&](int t, int pieces) {   // cost of the largest of `pieces` even parts of tile t
+      const int len = (granules + pieces - 1) / pieces;
+      double c = 0.0;
+      for (int g = 0; g < len; g += cap) c += unit_cost(tiles[t].k_count, std::min(cap, len - g));
+      return c;
+    };
+    std::vector<int> parts(nt, 1);
+    typedef std::pair<double, int> Top;   // (cost of the tile's largest piece, position in order)
+    std::priority_queue<Top> heap;
+    for (int i = 0; i < nt; ++i) heap.push({piece_cost(order[i], 1), i});
+    int spare = n_ctas - nt;
+    while (spare > 0 && !heap.empty()) {
+      const int i = heap.top().second;
+      heap.pop();
+      if (parts[i] >= granules) continue;   // one granule per CTA already; the tile leaves the heap
+      ++parts[i];
+      --spare;
+      heap.push({piece_cost(order[i], parts[i]), i});
+    }
+    for (int i = 0; i < nt; ++i) {
+      for (int p = 1; p <= parts[i]; ++p) {
+        ends_c.push_back(static_cast<long long>(i) * granules + static_cast<long long>(granules) * p / parts[i]);
+      }
+    }
+  }
+  const double worst_a = cut(ends_a, nullptr), worst_b = cut(ends_b, nullptr);
+  const double worst_c = ends_c.empty() ? 1e300 : cut(ends_c, nullptr);
+  const std::vector<long long>* pick = &ends_a;
+  if (worst_c <= std::min(worst_a, worst_b) * 1.03) pick = &ends_c;
+  else if (worst_b <= worst_a * 1.03) pick = &ends_b;
+  cut(*pick, lists);
+  if (lists->empty()) lists->assign(1, {});
+}
+
+// Blocked list schedule for activations far larger than L2.  Tiles are taken in descending kept-K
+// order and cut into units of `cap` granules (the last unit of a tile may be narrower).  Every
+// tile's pass over At would come from HBM, so the tiles are taken in groups whose packed weights fit
+// comfortably in L2 (32 MiB) and, inside a group, the batch blocks become the outer loop: concurrent
+// CTAs then share one slab of At, whose rows are fetched from HBM once per group instead of once per
+// tile.  Units go to the CTAs by longest-processing-time list scheduling in that order.
+void partition_blocked(const std::vector<ts::TileDesc>& tiles, const std::vector<int>& order, long long at_rows,
+                       int M, int cap, int n_ctas, std::vector<std::vector<Unit>>* lists) {
+  const int granules = (M + 63) / 64;
+  const int full_per_tile = granules / cap;
+  const int tail_gran = granules - full_per_tile * cap;
+  const bool blocked = 2LL * at_rows * M > (192LL << 20);
+  long long wbytes = 0;
+  for (int t : order) wbytes += 2LL * tiles[t].k_count * 128;
+  const long long avg_tile = std::max<long long>(1, wbytes / std::max<size_t>(1, order.size()));
+  const int group = blocked ? static_cast<int>(std::max<long long>(8, std::min<long long>(order.size(), (32LL << 20) / avg_tile)))
+                            : 1;
+  std::vector<Unit> units;
+  const int blocks_per_tile = full_per_tile + (tail_gran > 0 ? 1 : 0);
+  for (size_t g0 = 0; g0 < order.size(); g0 += group) {
+    const size_t g1 = std::min(order.size(), g0 + group);
+    for (int u = 0; u < blocks_per_tile; ++u) {
+      for (size_t i = g0; i < g1; ++i) {
+        const int t = order[i];
+        const int len = u < full_per_tile ? cap : tail_gran;
+        units.push_back(Unit{t, u * cap * 64, len * 64, unit_cost(tiles[t].k_count, len)});
+      }
+    }
+  }
+  const int g = std::max<int>(1, std::min<int>(n_ctas, static_cast<int>(units.size())));
+  lists->assign(g, {});
+  typedef std::pair<float, int> Load;  // (load, cta), smallest load first, then lowest cta
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int b = 0; b < g; ++b) heap.push({0.0f, b});
+  for (const Unit& u : units) {
+    Load l = heap.top();
+    heap.pop();
+    (*lists)[l.second].push_back(u);
+    l.first += u.cost;
+    heap.push(l);
+  }
+}
+
+// Work distribution for the persistent kernel.  Units are (tile, run of batch rows); a run is a
+// multiple of 64 rows, at most *unit_rows (128 or 256: the kernel variant).  forced_unit_rows (0, 128,
+// 256) pins the variant; otherwise 256-row units are used unless no CTA would receive more than 128
+// batch rows of work.
 // Output: flat [rounds][grid] table; a CTA's units fill its column from round 0 without gaps,
 // tile = -1 marks the end.
-void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, int M, int unit_rows, int n_ctas,
-                    std::vector<ts::WorkItem>* flat, int* rounds, int* grid, int* n_units,
-                    std::vector<float>* cta_cost, std::vector<ts::BlockDesc>* blocks,
+void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, int M, int forced_unit_rows,
+                    int n_ctas, std::vector<ts::WorkItem>* flat, int* rounds, int* grid, int* n_units,
+                    int* unit_rows, std::vector<float>* cta_cost, std::vector<ts::BlockDesc>* blocks,
                     int* blk_stride) {
   std::vector<int> order;
   for (int t = 0; t < static_cast<int>(tiles.size()); ++t) {
@@ -155,67 +328,49 @@ void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, i
   }
   std::stable_sort(order.begin(), order.end(),
                    [&](int a, int b) { return tiles[a].k_count > tiles[b].k_count; });
-  struct U {
-    int tile, m_begin, m_len;
-    float cost;
-  };
-  const int gran_per_unit = unit_rows / 64;
-  const int granules = (M + 63) / 64;                       // 64-row granules per tile
-  const int full_per_tile = granules / gran_per_unit;       // full-width units per tile
-  const int tail_gran = granules - full_per_tile * gran_per_unit;
-  auto make = [&](int t, int g0, int glen) {
-    return U{t, g0 * 64, glen * 64, unit_cost(tiles[t].k_count) * glen / static_cast<float>(gran_per_unit)};
-  };
-  // Unit order = processing order.  While At fits in L2 the order is tile-major: the CTAs running at
-  // the same time work on one tile, i.e. on the same kept rows of At and the same packed weights.
-  // When At is much larger than L2 (K*M*2 bytes > 192 MiB) every tile's pass over At would come from
-  // HBM, so the tiles are taken in groups whose packed weights fit comfortably in L2 (32 MiB) and,
-  // inside a group, the batch blocks become the outer loop: concurrent CTAs then share one slab of
-  // At, whose rows are fetched from HBM once per group instead of once per tile.
-  const bool blocked = 2LL * at_rows * M > (192LL << 20);
-  long long wbytes = 0;
-  for (int t : order) wbytes += 2LL * tiles[t].k_count * 128;
-  const long long avg_tile = std::max<long long>(1, wbytes / std::max<size_t>(1, order.size()));
-  const int group = blocked ? static_cast<int>(std::max<long long>(8, std::min<long long>(order.size(), (32LL << 20) / avg_tile)))
-                            : 1;
-  std::vector<U> units;
-  const int blocks_per_tile = full_per_tile + (tail_gran > 0 ? 1 : 0);
-  for (size_t g0 = 0; g0 < order.size(); g0 += group) {
-    const size_t g1 = std::min(order.size(), g0 + group);
-    for (int u = 0; u < blocks_per_tile; ++u) {
-      for (size_t i = g0; i < g1; ++i) {
-        const int t = order[i];
-        if (u < full_per_tile) units.push_back(make(t, u * gran_per_unit, gran_per_unit));
-        else units.push_back(make(t, full_per_tile * gran_per_unit, tail_gran));
-      }
-    }
+  const long long granules = (M + 63) / 64;
+  const long long total = granules * static_cast<long long>(order.size());
+  const bool contiguous = small_activations(at_rows, M);
+  int cap;
+  if (forced_unit_rows == 128 || forced_unit_rows == 256) {
+    cap = forced_unit_rows / 64;
+  } else if (contiguous) {
+    cap = (total + n_ctas - 1) / std::max(1, n_ctas) <= 2 ? 2 : 4;
+  } else {
+    const long long units256 = static_cast<long long>(order.size()) * ((M + 255) / 256);
+    cap = 2 * units256 >= n_ctas ? 4 : 2;
   }
-  *n_units = static_cast<int>(units.size());
-  const int g = std::max(1, std::min(n_ctas, *n_units));
+  *unit_rows = cap * 64;
+  std::vector<std::vector<Unit>> ulists;
+  if (order.empty() || M <= 0) {
+    ulists.assign(1, {});
+  } else if (contiguous) {
+    partition_contiguous(tiles, order, M, cap, n_ctas, &ulists);
+  } else {
+    partition_blocked(tiles, order, at_rows, M, cap, n_ctas, &ulists);
+  }
+  const int g = std::max<int>(1, static_cast<int>(ulists.size()));
   std::vector<std::vector<ts::WorkItem>> lists(g);
-  typedef std::pair<float, int> Load;  // (load, cta), smallest load first, then lowest cta
-  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
-  for (int b = 0; b < g; ++b) heap.push({0.0f, b});
   cta_cost->assign(g, 0.0f);
-  for (const U& u : units) {
-    const ts::TileDesc& td = tiles[u.tile];
-    Load l = heap.top();
-    heap.pop();
-    ts::WorkItem w;
-    w.k_list = td.k_list;
-    w.n_list = td.n_list;
-    w.k_count = td.k_count;
-    w.n_count = td.n_count;
-    w.w_row0 = td.w_row0;
-    w.c_row0 = td.c_row0;
-    w.flags = (td.relative ? ts::kItemRelative : 0) | (td.pad_ ? ts::kItemDenseRows : 0);
-    w.m_begin = u.m_begin;
-    w.m_len = u.m_len;
-    w.tile = u.tile;
-    lists[l.second].push_back(w);
-    l.first += u.cost;
-    (*cta_cost)[l.second] = l.first;
-    heap.push(l);
+  *n_units = 0;
+  for (int b = 0; b < static_cast<int>(ulists.size()); ++b) {
+    for (const Unit& u : ulists[b]) {
+      const ts::TileDesc& td = tiles[u.tile];
+      ts::WorkItem w;
+      w.k_list = td.k_list;
+      w.n_list = td.n_list;
+      w.k_count = td.k_count;
+      w.n_count = td.n_count;
+      w.w_row0 = td.w_row0;
+      w.c_row0 = td.c_row0;
+      w.flags = (td.relative ? ts::kItemRelative : 0) | (td.pad_ ? ts::kItemDenseRows : 0);
+      w.m_begin = u.m_begin;
+      w.m_len = u.m_len;
+      w.tile = u.tile;
+      lists[b].push_back(w);
+      (*cta_cost)[b] += u.cost;
+      ++*n_units;
+    }
   }
   int r = 0;
   for (const auto& l : lists) r = std::max<int>(r, static_cast<int>(l.size()));
@@ -293,7 +448,13 @@ struct ts_layer {
   // Host-buffer path: copy-in, compute and copy-out streams and the events that chain them.
   cudaStream_t s_in = nullptr, s_mm = nullptr, s_out = nullptr;
   std::vector<cudaEvent_t> events;
-  bool ct_dirty = true;   // the staging output holds something other than zeros where no tile writes
+  // The host-buffer path zeroes its staging output once and then relies on the kernel overwriting the
+  // same places every call; that holds only while the batch size (the row pitch) and the tile set stay
+  // the same and no beta pass has brought the caller's values in.
+  bool ct_dirty = true;
+  int ct_zeroed_m = -1;
+  int forced_unit_rows = 0;    // 0: the scheduler chooses between 128- and 256-row units
+  bool wp_fresh = false;       // packed weights were (re)written on a stream since the last GEMM launch
   bool host_pending = false;   // events[1] marks the end of the latest host-buffer call
 };
 
@@ -314,6 +475,7 @@ void free_tiles(ts_layer* l) {
   }
   l->schedules.clear();
   l->packed = false;
+  l->ct_dirty = true;   // another tile set leaves other places of the staging output unwritten
 }
 
 int get_schedule(ts_layer* l, int M, Schedule** out) {
@@ -334,11 +496,8 @@ int get_schedule(ts_layer* l, int M, Schedule** out) {
   Schedule s;
   std::vector<ts::WorkItem> flat;
   std::vector<ts::BlockDesc> blocks;
-  int live = 0;
-  for (int v : l->n_counts) live += v > 0;
-  s.unit_rows = choose_unit_rows(live, M, l->sm_count);
-  build_schedule(l->h_tiles, l->K, M, s.unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
-                 &s.cta_cost, &blocks, &s.blk_stride);
+  build_schedule(l->h_tiles, l->K, M, l->forced_unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
+                 &s.unit_rows, &s.cta_cost, &blocks, &s.blk_stride);
   if (!flat.empty()) {
     TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkItem)));
     TS_CUDA(cudaMemcpy(s.d_units, flat.data(), flat.size() * sizeof(ts::WorkItem),
@@ -533,6 +692,25 @@ int ts_layer_pack_weights(ts_layer_t* l, const void* W_dev, int64_t ldw_in, int 
   TS_CUDA(ts::pack_weights_launch(w_dtype, l->dtype, W_dev, ldw_in, l->d_tiles, l->n_tiles, l->max_k,
                                   l->d_wp, l->ldw, s));
   l->packed = true;
+  l->wp_fresh = true;
+  return TS_OK;
+}
+
+int ts_layer_set_unit_rows(ts_layer_t* l, int unit_rows) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (unit_rows != 0 && unit_rows != 128 && unit_rows != 256) {
+    return fail(TS_ERR_INVALID, "unit_rows=%d must be 0 (automatic), 128 or 256", unit_rows);
+  }
+  if (unit_rows == l->forced_unit_rows) return TS_OK;
+  TS_CUDA(cudaSetDevice(l->device));
+  TS_CUDA(cudaDeviceSynchronize());   // cached schedules may be in use by queued launches
+  for (auto& kv : l->schedules) {
+    cudaFree(kv.second.d_units);
+    cudaFree(kv.second.d_blocks);
+    cudaFree(kv.second.d_meta);
+  }
+  l->schedules.clear();
+  l->forced_unit_rows = unit_rows;
   return TS_OK;
 }
 
@@ -590,14 +768,16 @@ int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* C
   if (rc != TS_OK) return rc;
   if (s->n_units == 0) return TS_OK;
   CUtensorMap tmap_c;
-  const bool tst = use_tma_store();
-  if (tst) {
-    rc = make_out_tmap(&tmap_c, l->dtype, Ct, l->N, M, ldc);
-    if (rc != TS_OK) return rc;
-  }
-  TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, l->tmap, tst ? &tmap_c : nullptr, s->d_units, s->rounds,
+  rc = make_out_tmap(&tmap_c, l->dtype, Ct, l->N, M, ldc);
+  if (rc != TS_OK) return rc;
+  // The kernel fetches packed weights before it waits for the kernel ahead of it in the stream.
+  // The first launch after ts_layer_pack_weights may directly follow the packing kernel, so it runs
+  // as an ordinary (fully ordered) launch; from then on the weights are old data.
+  const bool early = !l->wp_fresh;
+  TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, l->tmap, &tmap_c, s->d_units, s->rounds,
                                  s->grid, s->d_meta, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
-                                 /*early_start=*/true, static_cast<cudaStream_t>(stream)));
+                                 early, static_cast<cudaStream_t>(stream)));
+  l->wp_fresh = false;
   return TS_OK;
 }
 
@@ -651,11 +831,7 @@ int ts_masked_gemm_host_async(ts_layer_t* l, int M, const void* At_host, void* C
   }
   // The batch is cut into up to four column blocks that move through copy-in, GEMM and copy-out
   // on three streams, so the two directions of the link and the kernel overlap.
-  static const int want_chunks = [] {
-    const char* e = getenv("TS_HOST_CHUNKS");
-    const int v = e ? atoi(e) : 0;
-    return (v >= 1 && v <= 16) ? v : 4;
-  }();
+  const int want_chunks = 4;
   const int n_chunks = M >= 256 * want_chunks ? want_chunks : 1;
   const int mc = ((M / n_chunks) + 255) / 256 * 256;
   const size_t need_events = 2 + 2 * static_cast<size_t>(n_chunks);
@@ -673,8 +849,9 @@ int ts_masked_gemm_host_async(ts_layer_t* l, int M, const void* At_host, void* C
   TS_CUDA(cudaStreamWaitEvent(l->s_mm, e_begin, 0));
   TS_CUDA(cudaStreamWaitEvent(l->s_out, e_begin, 0));
   // Columns no tile keeps are never written by the kernel: with beta == 0 they must come back as zeros.
-  if (beta == 0.0f && l->ct_dirty) {
+  if (beta == 0.0f && (l->ct_dirty || l->ct_zeroed_m != M)) {
     TS_CUDA(cudaMemsetAsync(l->d_ct, 0, c_bytes, l->s_in));
+    l->ct_zeroed_m = M;
   }
   const size_t pitch = static_cast<size_t>(M) * 2;
   int c = 0;
@@ -837,10 +1014,9 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
     std::vector<ts::WorkItem> flat;
     std::vector<float> cost;
     std::vector<ts::BlockDesc> blocks;
-    int n_units = 0, live = 0;
-    for (int v : nc) live += v > 0;
-    ws.unit_rows = choose_unit_rows(live, M, sms);
-    build_schedule(td, K, M, ws.unit_rows, sms, &flat, &ws.rounds, &ws.grid, &n_units, &cost, &blocks, &ws.blk_stride);
+    int n_units = 0;
+    build_schedule(td, K, M, 0, sms, &flat, &ws.rounds, &ws.grid, &n_units, &ws.unit_rows, &cost, &blocks,
+                   &ws.blk_stride);
     ws.key.clear();
     if (n_units == 0) return TS_OK;
     if (flat.size() > ws.unit_cap) {
@@ -910,14 +1086,52 @@ int ts_transpose16(const void* in_dev, int64_t ld_in, void* out_dev, int64_t ld_
   return TS_OK;
 }
 
-#ifdef TS_KERNEL_TRACE
-// Debug builds only: the time stamps (160 CTAs x 64 slots) of the most recent traced launch.
-int ts_debug_read_trace(long long* out64, int clear) {
-  TS_CUDA(cudaDeviceSynchronize());
-  TS_CUDA(ts::masked_gemm_read_trace(out64, clear != 0));
+int ts_plan_schedule(int n_tiles, const int32_t* k_counts, const int32_t* n_counts, int64_t K, int M, int n_ctas,
+                     int unit_rows, int* unit_rows_out, int* n_ctas_out, int* n_units_out, int32_t* units_out,
+                     int max_units, float* cta_cost_out) {
+  if (n_tiles < 0 || M <= 0 || K <= 0 || n_ctas <= 0) {
+    return fail(TS_ERR_INVALID, "n_tiles=%d, K=%lld, M=%d, n_ctas=%d", n_tiles, (long long)K, M, n_ctas);
+  }
+  if (n_tiles > 0 && (!k_counts || !n_counts)) return fail(TS_ERR_INVALID, "NULL argument");
+  if (unit_rows != 0 && unit_rows != 128 && unit_rows != 256) {
+    return fail(TS_ERR_INVALID, "unit_rows=%d must be 0 (automatic), 128 or 256", unit_rows);
+  }
+  std::vector<ts::TileDesc> td(n_tiles);
+  for (int t = 0; t < n_tiles; ++t) {
+    if (k_counts[t] < 0 || n_counts[t] < 0 || n_counts[t] > 128) {
+      return fail(TS_ERR_INVALID, "tile %d: k_count=%d, n_count=%d", t, k_counts[t], n_counts[t]);
+    }
+    memset(&td[t], 0, sizeof(td[t]));
+    td[t].k_count = k_counts[t];
+    td[t].n_count = n_counts[t];
+    td[t].w_row0 = t * 128;
+  }
+  std::vector<ts::WorkItem> flat;
+  std::vector<ts::BlockDesc> blocks;
+  std::vector<float> cost;
+  int rounds = 0, grid = 0, n_units = 0, urows = 0, blk_stride = 0;
+  build_schedule(td, K, M, unit_rows, n_ctas, &flat, &rounds, &grid, &n_units, &urows, &cost, &blocks, &blk_stride);
+  if (unit_rows_out) *unit_rows_out = urows;
+  if (n_ctas_out) *n_ctas_out = grid;
+  if (n_units_out) *n_units_out = n_units;
+  if (cta_cost_out) memcpy(cta_cost_out, cost.data(), cost.size() * sizeof(float));
+  if (units_out) {
+    if (n_units > max_units) return fail(TS_ERR_INVALID, "units_out holds %d units, the schedule has %d", max_units, n_units);
+    int o = 0;
+    for (int b = 0; b < grid; ++b) {
+      for (int r = 0; r < rounds; ++r) {
+        const ts::WorkItem& w = flat[static_cast<size_t>(r) * grid + b];
+        if (w.tile < 0) break;
+        units_out[4 * o] = b;
+        units_out[4 * o + 1] = w.tile;
+        units_out[4 * o + 2] = w.m_begin;
+        units_out[4 * o + 3] = w.m_len;
+        ++o;
+      }
+    }
+  }
   return TS_OK;
 }
-#endif
 
 int ts_shard_plan(int n_tiles, const int64_t* cost, int n_parts, int32_t* owner_out) {
   if (n_tiles < 0 || n_parts <= 0) return fail(TS_ERR_INVALID, "n_tiles=%d, n_parts=%d", n_tiles, n_parts);

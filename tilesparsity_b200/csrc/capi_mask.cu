@@ -445,7 +445,7 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
                      ts_mask_result_t** out, void* stream) {
   if (!out) return ts_internal_fail(TS_ERR_INVALID, "out is NULL");
   *out = nullptr;
-  if (mode < TS_MASK_TW1 || mode > TS_MASK_TOPK_L1) return ts_internal_fail(TS_ERR_INVALID, "unknown mode %d", mode);
+  if (mode < TS_MASK_TW1 || mode > TS_MASK_TW_COLS_ROWS) return ts_internal_fail(TS_ERR_INVALID, "unknown mode %d", mode);
   if (n_layers <= 0 || !scores_dev || !Ks || !Ns) return ts_internal_fail(TS_ERR_INVALID, "no layers");
   if (G <= 0) return ts_internal_fail(TS_ERR_INVALID, "G=%d must be positive", G);
   if (!(sparsity >= 0.0 && sparsity <= 100.0)) {
@@ -465,6 +465,11 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
     L[l].N = Ns[l];
     L[l].ld = lds ? lds[l] : Ns[l];
     if (L[l].ld < L[l].N) return ts_internal_fail(TS_ERR_INVALID, "layer %d: ld smaller than N", l);
+    // launch geometry: column tiles, and 16-row blocks of K, are grid y dimensions (at most 65535)
+    if ((L[l].N + G - 1) / G > 65535 || L[l].K > 65535 * 16) {
+      return ts_internal_fail(TS_ERR_UNSUPPORTED, "layer %d: %d x %d at G=%d exceeds 65535 column tiles or 1048560 rows",
+                              l, L[l].K, L[l].N, G);
+    }
     L[l].mask = masks_dev ? masks_dev[l] : nullptr;
     L[l].ld_mask = (ld_masks && L[l].mask) ? ld_masks[l] : Ns[l];
     L[l].residual = residual_dev ? residual_dev[l] : nullptr;
@@ -481,7 +486,11 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
   TSM_OK(alloc_scratch(arena, &sc));
   ts_mask_result* res = new ts_mask_result();
 
-  const bool two_d = mode == TS_MASK_TW2 || mode == TS_MASK_TW2M || mode == TS_MASK_BERT_TW_KN;
+  if (mode == TS_MASK_TW_COLS_ROWS && !(g1percent >= 0.0 && g1percent <= 100.0)) {
+    return ts_internal_fail(TS_ERR_INVALID, "column sparsity %g must be in [0, 100]", g1percent);
+  }
+  const bool two_d = mode == TS_MASK_TW2 || mode == TS_MASK_TW2M || mode == TS_MASK_BERT_TW_KN ||
+                     mode == TS_MASK_TW_COLS_ROWS;
   double q = tew ? sparsity + g1percent : sparsity;
   bool wide = sparsity_is_f64 != 0;
   if (mode == TS_MASK_TW2 || mode == TS_MASK_TW2M) {
@@ -514,7 +523,8 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
         rc = ts_internal_fail(TS_ERR_CUDA, "column norm kernel failed: %s", cudaGetErrorString(e));
         break;
       }
-      if ((rc = percentile_to_device(cn, totalN, q, wide, false, sc, 0, s)) != TS_OK) break;
+      const double q_col = mode == TS_MASK_TW_COLS_ROWS ? g1percent : q;
+      if ((rc = percentile_to_device(cn, totalN, q_col, wide, false, sc, 0, s)) != TS_OK) break;
       e = ts::threshold_dev_launch(cn, totalN, sc.thr + 0, ck, s);
       std::vector<uint8_t> all(totalN);
       if (e == cudaSuccess) e = cudaMemcpyAsync(all.data(), ck, totalN, cudaMemcpyDeviceToHost, s);
@@ -718,6 +728,9 @@ int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_d
   long long total = 0;
   for (int l = 0; l < n_layers; ++l) {
     if (!scores_dev[l] || !masks_dev[l] || Ks[l] <= 0 || Ns[l] <= 0) return ts_internal_fail(TS_ERR_INVALID, "layer %d: bad argument", l);
+    if (Ks[l] > 65535 * 16) {   // vector-wise: 16-row blocks of K are a grid y dimension
+      return ts_internal_fail(TS_ERR_UNSUPPORTED, "layer %d: K=%d exceeds 1048560 rows", l, Ks[l]);
+    }
     if ((lds && lds[l] < Ns[l]) || (ld_masks && ld_masks[l] < Ns[l])) return ts_internal_fail(TS_ERR_INVALID, "layer %d: leading dimension too small", l);
     total += static_cast<long long>(Ks[l]) * Ns[l];
   }

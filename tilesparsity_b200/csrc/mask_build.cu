@@ -445,12 +445,13 @@ dense_mask_kernel(const uint8_t* __restrict__ rowkeep, const uint8_t* __restrict
                   const int* __restrict__ tile_of_col, int K, int N, uint8_t* __restrict__ mask,
                   long long ld_mask) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  const int k = blockIdx.y;
   if (n >= N) return;
   const int t = tile_of_col[n];
-  uint8_t m = rowkeep[static_cast<long long>(t) * K + k];
-  if (colkeep) m &= colkeep[n];
-  mask[static_cast<long long>(k) * ld_mask + n] = m;
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {   // gridDim.y is capped at 65535 rows
+    uint8_t m = rowkeep[static_cast<long long>(t) * K + k];
+    if (colkeep) m &= colkeep[n];
+    mask[static_cast<long long>(k) * ld_mask + n] = m;
+  }
 }
 
 // Same result, 16 mask bytes per thread and kDenseRows rows per block: needs N, ld_mask and the
@@ -506,9 +507,10 @@ dense_mask16_kernel(const uint8_t* __restrict__ rowkeep, const uint8_t* __restri
 __global__ void __launch_bounds__(256)
 abs_values_kernel(const float* __restrict__ score, long long ld, int K, int N, float* __restrict__ vals) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  const int k = blockIdx.y;
   if (n >= N) return;
-  vals[static_cast<long long>(k) * N + n] = fabsf(__ldg(score + static_cast<long long>(k) * ld + n));
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    vals[static_cast<long long>(k) * N + n] = fabsf(__ldg(score + static_cast<long long>(k) * ld + n));
+  }
 }
 
 // Vector-wise baseline (prune_algo.py:196-227): one thread per (block of 16 rows, column) keeps the
@@ -556,12 +558,13 @@ __global__ void __launch_bounds__(256)
 tew_values_kernel(const float* __restrict__ score, long long ld, const uint8_t* __restrict__ mask,
                   long long ld_mask, int K, int N, float* __restrict__ vals) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  const int k = blockIdx.y;
   if (n >= N) return;
-  const float x = __ldg(score + static_cast<long long>(k) * ld + n);
-  const float a = __fsqrt_rn(__fmul_rn(x, x));
-  const float m = mask[static_cast<long long>(k) * ld_mask + n] ? 1.0f : 0.0f;
-  vals[static_cast<long long>(k) * N + n] = __fsub_rn(a, m);
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    const float x = __ldg(score + static_cast<long long>(k) * ld + n);
+    const float a = __fsqrt_rn(__fmul_rn(x, x));
+    const float m = mask[static_cast<long long>(k) * ld_mask + n] ? 1.0f : 0.0f;
+    vals[static_cast<long long>(k) * N + n] = __fsub_rn(a, m);
+  }
 }
 
 // mask[k][n] |= v > thr; residual[k][n] = (v > thr) & !mask_before   (prune_algo.py:171-175)
@@ -569,14 +572,15 @@ __global__ void __launch_bounds__(256)
 tew_apply_kernel(const float* __restrict__ vals, const double* __restrict__ thr_dev, int K, int N,
                  uint8_t* __restrict__ mask, long long ld_mask, uint8_t* __restrict__ residual) {
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  const int k = blockIdx.y;
   if (n >= N) return;
   const double thr = *thr_dev;
-  const long long mi = static_cast<long long>(k) * ld_mask + n;
-  const bool extra = static_cast<double>(vals[static_cast<long long>(k) * N + n]) > thr;
-  const uint8_t before = mask[mi];
-  if (residual) residual[static_cast<long long>(k) * N + n] = (extra && !before) ? 1 : 0;
-  if (extra) mask[mi] = 1;
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    const long long mi = static_cast<long long>(k) * ld_mask + n;
+    const bool extra = static_cast<double>(vals[static_cast<long long>(k) * N + n]) > thr;
+    const uint8_t before = mask[mi];
+    if (residual) residual[static_cast<long long>(k) * N + n] = (extra && !before) ? 1 : 0;
+    if (extra) mask[mi] = 1;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -731,14 +735,14 @@ cudaError_t dense_mask_launch(const uint8_t* rowkeep, const uint8_t* colkeep, co
     dense_mask16_kernel<<<grid16, threads, 0, s>>>(rowkeep, colkeep, tile_of_col, K, N, mask, ld_mask);
     return cudaGetLastError();
   }
-  dim3 grid((N + 255) / 256, K);
+  dim3 grid((N + 255) / 256, K < 65535 ? K : 65535);
   dense_mask_kernel<<<grid, 256, 0, s>>>(rowkeep, colkeep, tile_of_col, K, N, mask, ld_mask);
   return cudaGetLastError();
 }
 
 cudaError_t abs_values_launch(const float* score, long long ld, int K, int N, float* vals, cudaStream_t s) {
   if (K <= 0 || N <= 0) return cudaSuccess;
-  dim3 grid((N + 255) / 256, K);
+  dim3 grid((N + 255) / 256, K < 65535 ? K : 65535);
   abs_values_kernel<<<grid, 256, 0, s>>>(score, ld, K, N, vals);
   return cudaGetLastError();
 }
@@ -754,7 +758,7 @@ cudaError_t vw_mask_launch(const float* score, long long ld, int K, int N, int t
 cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* mask, long long ld_mask,
                               int K, int N, float* vals, cudaStream_t s) {
   if (K <= 0 || N <= 0) return cudaSuccess;
-  dim3 grid((N + 255) / 256, K);
+  dim3 grid((N + 255) / 256, K < 65535 ? K : 65535);
   tew_values_kernel<<<grid, 256, 0, s>>>(score, ld, mask, ld_mask, K, N, vals);
   return cudaGetLastError();
 }
@@ -762,7 +766,7 @@ cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* m
 cudaError_t tew_apply_launch(const float* vals, const double* thr, int K, int N, uint8_t* mask,
                              long long ld_mask, uint8_t* residual, cudaStream_t s) {
   if (K <= 0 || N <= 0) return cudaSuccess;
-  dim3 grid((N + 255) / 256, K);
+  dim3 grid((N + 255) / 256, K < 65535 ? K : 65535);
   tew_apply_kernel<<<grid, 256, 0, s>>>(vals, thr, K, N, mask, ld_mask, residual);
   return cudaGetLastError();
 }

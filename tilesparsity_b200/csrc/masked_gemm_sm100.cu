@@ -33,8 +33,6 @@
 //
 // Warp roles (448 threads): warp 0 = weight TMA, warp 1 = TMEM allocation + MMA issue,
 // warps 2-5 = activation gather, warps 6-13 = epilogue.
-#include <cstdlib>
-
 #include "ts_common.cuh"
 #include "ts_kernels.h"
 
@@ -66,37 +64,6 @@ constexpr int kMetaInts = kBlockMetaInts;  // one block record: {m0, meta, 0, 0}
 constexpr int kAhead = 4;                // a warp requests its part of a record this many of its blocks ahead
 constexpr int kMetaSlots = 6;            // ring slots per warp (> kAhead)
 
-// Optional time-stamp trace (debug builds only: -DTS_KERNEL_TRACE).  Every CTA keeps 64 stamps in
-// shared memory (globaltimer nanoseconds; slot i is written the first time the CTA passes trace
-// point i) and copies them to g_trace[cta][64] when it retires, so tracing adds no global access
-// to the loops it observes.
-#ifdef TS_KERNEL_TRACE
-constexpr int kTraceSlots = 64;
-constexpr int kTraceCtas = 160;
-__device__ long long g_trace[kTraceCtas * kTraceSlots];
-__device__ __forceinline__ long long trace_now() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define TS_TRACE(id, leader)                                                                   \
-  do {                                                                                         \
-    if ((leader) && (id) < kTraceSlots && bars->trace[id] == 0) bars->trace[id] = trace_now(); \
-  } while (0)
-// Per-unit stamps: slot 8 + kind*4 + unit for the CTA's first four units (kinds 0..4).
-#define TS_TRACE_U(kind, unit, leader)                       \
-  do {                                                       \
-    if ((unit) < 4) TS_TRACE(8 + (kind)*4 + (unit), leader); \
-  } while (0)
-#else
-#define TS_TRACE(id, leader) \
-  do {                       \
-  } while (0)
-#define TS_TRACE_U(kind, unit, leader) \
-  do {                                 \
-  } while (0)
-#endif
-
 struct Barriers {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -107,9 +74,6 @@ struct Barriers {
   // Per gather warp: ring of the parts of the coming blocks' records that the warp needs: the
   // descriptor words and the row numbers of its slice.
   alignas(16) int meta_ring[kGW][kMetaSlots][4 + kRowsPerWarp];
-#ifdef TS_KERNEL_TRACE
-  long long trace[64];
-#endif
 };
 
 // Compile-time shape of one kernel variant: MT batch rows per work unit.
@@ -136,14 +100,25 @@ struct Cfg {
 
 __device__ __forceinline__ WorkItem load_item(const WorkItem* p) {
   const int4* q = reinterpret_cast<const int4*>(p);
+  const uint64_t keep = l2_policy_evict_last();
   union {
     int4 v[3];
     WorkItem w;
   } u;
-  u.v[0] = __ldg(q);
-  u.v[1] = __ldg(q + 1);
-  u.v[2] = __ldg(q + 2);
+  u.v[0] = ld_nc_hint(q, keep);
+  u.v[1] = ld_nc_hint(q + 1, keep);
+  u.v[2] = ld_nc_hint(q + 2, keep);
   return u.w;
+}
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Arrival without waiting: the thread's earlier writes are visible to the threads that later pass
+// bar.sync on the same barrier.
+__device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 // Work item of CTA `cta` in round r, or an empty item past the end of the schedule.
@@ -175,10 +150,6 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   return x;
 }
 
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
 template <int DT, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
@@ -186,7 +157,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    const WorkItem* __restrict__ sched, int rounds,
                    const int* __restrict__ block_meta, int blk_stride,
                    const uint16_t* __restrict__ At, long long lda,
-                   uint16_t* __restrict__ Ct, long long ldc, int M, const EpilogueArgs ep,
+                   uint16_t* __restrict__ Ct, long long ldc, int M, const __grid_constant__ EpilogueArgs ep,
                    int* __restrict__ status) {
   const float alpha = ep.alpha, beta = ep.beta;
   using C = Cfg<MT>;
@@ -208,11 +179,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   const int lane = threadIdx.x & 31;
   const int grid = gridDim.x;
   const int cta = blockIdx.x;
-#ifdef TS_KERNEL_TRACE
-  if (threadIdx.x < 64) bars->trace[threadIdx.x] = 0;
-  __syncthreads();
-#endif
-  TS_TRACE(0, threadIdx.x == 0);
 
   // First work item, and for the gather warps the record of their first block: requested before
   // the set-up below so their latency overlaps it.  The schedule is static data.
@@ -226,14 +192,20 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       if (lane < kMetaLanes) {
-        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][i][lane * 4]),
-                       recs + static_cast<size_t>(gw / kWarpsPerBlock + i * kWarpGroups) * kMetaInts + meta_piece);
+        cp_async_16_ca_hint(smem_u32(&bars->meta_ring[gw][i][lane * 4]),
+                            recs + static_cast<size_t>(gw / kWarpsPerBlock + i * kWarpGroups) * kMetaInts + meta_piece,
+                            l2_policy_evict_last());
       }
       cp_async_commit();
     }
   }
 
-  if (threadIdx.x == 0) {
+  // Set-up in two tiers.  The producers (weight TMA warp, gather warps) need only the mbarriers: the
+  // first lane of the first gather warp initialises them, the five producer warps meet on a barrier of
+  // their own and start copying, while warp 1 is still allocating tensor memory.  The MMA and epilogue
+  // warps meet on a second barrier, at which the producers merely arrive.
+  constexpr int kBarGather = 3, kBarAll = 4;
+  if (warp == 2 && lane == 0) {
     for (int s = 0; s < kStages; ++s) {
       // weight TMA thread + the cp.async lanes of the warps that fill the stage
       mbar_init(smem_u32(&bars->full[s]), 1 + 32 * kWarpsPerBlock);
@@ -246,15 +218,20 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     bars->abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(&bars->tmem_base), C::kTmemCols);
-    tmem_relinquish();
+  uint32_t tmem_base = 0;
+  if (warp == 0 || (warp >= 2 && warp < 6)) {
+    named_barrier_sync(kBarGather, 32 * (kGW + 1));
+    named_barrier_arrive(kBarAll, kThreads);
+  } else {
+    if (warp == 1) {
+      tmem_alloc(smem_u32(&bars->tmem_base), C::kTmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    named_barrier_sync(kBarAll, kThreads);
+    tc_fence_after_sync();
+    tmem_base = bars->tmem_base;
   }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_base;
-  TS_TRACE(1, threadIdx.x == 0);
   // The next kernel in the stream may begin its own set-up now (it cannot touch this kernel's
   // outputs before its grid_dependency_wait, which returns only when this grid has completed).
   grid_launch_dependents();
@@ -294,7 +271,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const uint32_t aph = (acc_it >> 1) & 1u;
       ok = mbar_wait(smem_u32(&bars->acc_empty[a]), aph ^ 1u, abort_flag);
       if (!ok) break;
-      TS_TRACE_U(0, acc_it, lane == 0);
       tc_fence_after_sync();
       const uint32_t tmem_d = tmem_base + a * MT;
       const uint32_t idesc = idesc0 | (static_cast<uint32_t>(w.m_len >> 3) << 17);
@@ -303,9 +279,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         const uint32_t ph = (it / kStages) & 1u;
         ok = mbar_wait(smem_u32(&bars->full[s]), ph, abort_flag);
         if (!ok) break;
-        TS_TRACE(40 + it, lane == 0);   // full barrier of block `it` passed
-        if (kb == 0) TS_TRACE_U(1, acc_it, lane == 0);
-        if (kb == nkb - 1) TS_TRACE_U(2, acc_it, lane == 0);
         // The gathered rows were written through the generic proxy; the MMA reads them through
         // the async proxy.
         fence_proxy_async_smem();
@@ -378,7 +351,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const uint32_t dst0 = smem_u32(smem + s * C::kStageBytes + kWBytes) + g * kALbo;
       const uint32_t bar = smem_u32(&bars->full[s]);
       if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag)) break;
-      TS_TRACE(52 + j, lane == 0 && row_base == 0);   // stage acquired for block j
       int rr[kRowsPerWarp];
 #pragma unroll
       for (int q4 = 0; q4 < kRowsPerWarp / 4; ++q4) {
@@ -423,11 +395,11 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       cp_async_arrive_noinc(bar);
       // request the warp's part of the record kAhead of its blocks ahead; one group per block
       if (lane < kMetaLanes) {
-        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][(it + kAhead) % kMetaSlots][lane * 4]),
-                       recs + static_cast<size_t>(j + kAhead * kWarpGroups) * kMetaInts + meta_piece);
+        cp_async_16_ca_hint(smem_u32(&bars->meta_ring[gw][(it + kAhead) % kMetaSlots][lane * 4]),
+                            recs + static_cast<size_t>(j + kAhead * kWarpGroups) * kMetaInts + meta_piece,
+                            l2_policy_evict_last());
       }
       cp_async_commit();
-      TS_TRACE(28 + j, lane == 0 && j < 8 && row_base == 0);   // copies of block j issued
     }
     cp_async_wait_all();  // nothing of this thread is in flight when the CTA retires
   } else if (warp >= 6) {
@@ -438,8 +410,8 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int j = q * 32 + lane;                 // tile column owned by this thread
     const bool leader = ((ew & 3) == 0 && lane == 0);   // one per half
-    uint8_t* stage_grp = epi + half * C::kEpiGroupBytes;
     const int half_bar = 1 + half;               // named barrier of this half (128 threads)
+    const int peer_rot = ep.n_peers > 0 ? cta % ep.n_peers : 0;   // the peer this CTA writes first
     uint32_t acc_it = 0;
     bool ok = true;
     grid_dependency_wait();   // Ct may still be read or written by the previous kernel
@@ -450,8 +422,12 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int m0 = w.m_begin;
       const int m_cnt = min(w.m_len, M - m0);
       const bool active = j < w.n_count;
-      // TMA store: consecutive Ct rows, nothing to read back, no peer copies
-      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f && ep.n_peers == 0;
+      // TMA store of the local copy: consecutive Ct rows, nothing to read back
+      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f;
+      // The CTA's last unit: every K block has been consumed, so the pipeline stages are free and
+      // each 64-column group gets a staging group of its own there; no group waits for the store
+      // of the one before it.
+      const bool last_unit = wn.tile < 0;
       const bool plain = beta == 0.0f && ep.bias == nullptr && ep.act == kActNone;
       const long long c_row = active ? c_row_of(w, j) : 0;
       const int c_row_or_none = active ? static_cast<int>(c_row) : -1;
@@ -460,7 +436,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int tile_row0 = w.c_row0 + ((tma_store && w.n_list) ? __ldg(w.n_list) : 0);
       ok = mbar_wait(smem_u32(&bars->acc_full[a]), aph, abort_flag);
       if (!ok) break;
-      TS_TRACE_U(3, acc_it, threadIdx.x == 192);
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + a * MT + (static_cast<uint32_t>(q * 32) << 16);
       const bool has_acc = w.k_count > 0;
@@ -492,10 +467,14 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
           mbar_arrive(smem_u32(&bars->acc_empty[a]));
         }
         if (!grp_live) continue;
-        // The half's staging group is free once its previous TMA store has read it (the leader
-        // waits for that) and every warp of the half has finished its previous copy-out.
-        if (leader) bulk_wait_read_all();
-        named_barrier_sync(half_bar, 128);
+        uint8_t* stage_grp = last_unit ? smem + (half * kGroups + gi) * C::kEpiGroupBytes
+                                       : epi + half * C::kEpiGroupBytes;
+        if (!last_unit) {
+          // The half's staging group is free once its previous TMA store has read it (the leader
+          // waits for that) and every warp of the half has finished its previous copy-out.
+          if (leader) bulk_wait_read_all();
+          named_barrier_sync(half_bar, 128);
+        }
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
           const int col0 = grp_col + b * 32;             // first batch column of the chunk
@@ -536,7 +515,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 make_uint4(o[e4 * 4], o[e4 * 4 + 1], o[e4 * 4 + 2], o[e4 * 4 + 3]);
           }
         }
-        TS_TRACE_U(4, acc_it, threadIdx.x == 192);
         if (tma_store) {
           fence_proxy_async_smem();
           named_barrier_sync(half_bar, 128);     // the whole group is staged
@@ -544,9 +522,13 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             tma_store_2d(&tmap_c, smem_u32(stage_grp), m0 + grp_col, tile_row0);
             bulk_commit();
           }
-        } else {
+        }
+        if (!tma_store || ep.n_peers > 0) {
           // copy-out through the kept-column list: this warp's own 32 rows, four rows per
-          // instruction, 16 bytes per lane
+          // instruction, 16 bytes per lane; to Ct unless the TMA store took it, and to every peer.
+          // Tile-sharded layers: the peers are the other GPUs' copies of Ct, written over NVLink;
+          // CTAs start at different peers so that the GPUs' stores do not converge on one
+          // destination at a time.
           __syncwarp();
           const int cchunk = lane & 7, rsub = lane >> 3;
           const bool m_ok = grp_col + cchunk * 8 < m_cnt;
@@ -565,15 +547,17 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             for (int e = 0; e < 4; ++e) {
               if (cr[e] >= 0 && m_ok) {
                 const long long off = static_cast<long long>(cr[e]) * ldc + m0 + grp_col + cchunk * 8;
-                *reinterpret_cast<uint4*>(Ct + off) = val[e];
-                // tile-sharded layers: the same rows go to the other GPUs' copies of Ct over NVLink
-                for (int p = 0; p < ep.n_peers; ++p) *reinterpret_cast<uint4*>(ep.peers[p] + off) = val[e];
+                if (!tma_store) *reinterpret_cast<uint4*>(Ct + off) = val[e];
+                for (int p = 0; p < ep.n_peers; ++p) {
+                  int pp = p + peer_rot;
+                  if (pp >= ep.n_peers) pp -= ep.n_peers;
+                  *reinterpret_cast<uint4*>(ep.peers[pp] + off) = val[e];
+                }
               }
             }
           }
           __syncwarp();
         }
-        TS_TRACE(36 + acc_it, threadIdx.x == 192 && acc_it < 4);   // group stored
       }
       ++acc_it;
       w = wn;
@@ -581,7 +565,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     // The CTA may retire once its last TMA stores have read the staging groups; the stores
     // themselves complete before the grid does.
     if (leader) bulk_wait_read_all();
-    TS_TRACE(3, threadIdx.x == 192);
   }
 
   tc_fence_before_sync();
@@ -589,11 +572,6 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   tc_fence_after_sync();
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
   if (threadIdx.x == 0 && bars->abort_flag) atomicExch(status, kErrTimeout);
-  TS_TRACE(2, threadIdx.x == 0);
-#ifdef TS_KERNEL_TRACE
-  __syncthreads();
-  if (threadIdx.x < 64 && blockIdx.x < kTraceCtas) g_trace[blockIdx.x * 64 + threadIdx.x] = bars->trace[threadIdx.x];
-#endif
 }
 
 // One record per K block of a schedule: {first batch row of the unit, meta word, 0, 0} followed by
@@ -621,13 +599,9 @@ cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_c,
                            const void* At, long long lda, void* Ct, long long ldc, int M,
                            const EpilogueArgs& ep, int* status, bool early_start, cudaStream_t stream) {
   // Programmatic dependent launch lets this kernel's set-up overlap the tail of the kernel before
-  // it in the stream.  The kernel reads its schedule before it waits for that kernel, so the caller
-  // allows this only when the schedule was not written by it.  TS_PDL=0 turns it off.
-  static const bool pdl_env = [] {
-    const char* e = getenv("TS_PDL");
-    return !(e && e[0] == '0');
-  }();
-  const bool pdl = pdl_env && early_start;
+  // it in the stream.  The kernel reads its schedule and its packed weights before it waits for that
+  // kernel, so the caller allows this only when neither was written by it.
+  const bool pdl = early_start;
   auto kern = masked_gemm_kernel<DT, MT>;
   // The dynamic shared-memory limit is a per-device, per-kernel attribute: set it once for each.
   static bool attr_set[64] = {};
@@ -675,17 +649,5 @@ cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks
   expand_block_meta_kernel<<<static_cast<unsigned>((n_blocks + 3) / 4), 256, 0, stream>>>(blocks, n_blocks, meta);
   return cudaGetLastError();
 }
-
-#ifdef TS_KERNEL_TRACE
-cudaError_t masked_gemm_read_trace(long long* out, bool clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
-  if (e == cudaSuccess && clear) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_trace);
-    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(g_trace));
-  }
-  return e;
-}
-#endif
 
 }  // namespace ts

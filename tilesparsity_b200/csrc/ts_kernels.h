@@ -18,8 +18,8 @@ namespace ts {
 // to blk_stride records) by end markers; expand_block_meta_launch writes it from the descriptors.
 // tmap_c != nullptr enables TMA stores (tensor map over Ct [N][ldc], box 64 x 128, 128-byte swizzle)
 // for the work items whose flags say their kept columns are consecutive rows of Ct.  early_start
-// allows programmatic dependent launch: the kernel reads sched and block_meta before it waits for the
-// kernel before it in the stream, so it must be false when that kernel wrote them.
+// allows programmatic dependent launch: the kernel reads sched, block_meta and the packed weights before
+// it waits for the kernel before it in the stream, so it must be false when that kernel wrote them.
 cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w, const CUtensorMap* tmap_c,
                                const WorkItem* sched, int rounds, int grid, const int* block_meta,
                                int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
@@ -28,10 +28,6 @@ cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap
 // meta[b*kBlockMetaInts ...] = record of block b, for all n_blocks (= grid*blk_stride) descriptors:
 // resolves the kept-row lists, relative or absolute, into row numbers of At.
 cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, cudaStream_t stream);
-
-#ifdef TS_KERNEL_TRACE
-cudaError_t masked_gemm_read_trace(long long* out64, bool clear);
-#endif
 
 // CUDA-core twin of the masked GEMM with the same operands (masked_gemm_simt.cu).
 cudaError_t masked_gemm_simt_launch(int dtype, const TileDesc* tiles, int n_tiles, const void* Wp,

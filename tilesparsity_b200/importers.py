@@ -8,6 +8,11 @@
   offsets (`...mask-o...`), the compacted kernel [kept_in, kept_out] and the masked bias.  Offsets are
   "index minus position" (convert_mask_to_offset, MyHook.py:66-74).
 
+* BERT: the `<name>.pkl` of dump_pruned_model.py (Pruning/BERT/utils/dump_pruned_model.py:118-140):
+  `model["transformer_ckpt"]` with `origin_ckpt` (kernel and bias per masked dense layer),
+  `masked_ckpt` (kernel * mask) and `absolute_mask` (the layer's 2-D 0/1 `mask-o` variable,
+  modeling.py:992-1007), keyed by TensorFlow variable names.
+
 Everything here is host-side format handling (NumPy only); the results are TileSets / dense masks that
 `TWLayer` and `ts_layer_set_tiles` take as they are.
 """
@@ -93,3 +98,38 @@ def dense_weights_from_bert_layer(layer: dict, K: int, N: int) -> np.ndarray:
     W = np.zeros((K, N), dtype=np.asarray(layer["kernel"]).dtype)
     W[np.ix_(layer["kept_in"], layer["kept_out"])] = layer["kernel"]
     return W
+
+
+def load_bert_dumped_model(path: str):
+    """The pickle of dump_pruned_model.py -> list of dicts {name, kernel [K, N], masked_kernel, mask
+    (bool [K, N]), bias or None}, one per masked dense layer, in stored order.
+
+    Layers are matched by variable scope: `<scope>/mask-o:0` in `absolute_mask` belongs to
+    `<scope>/kernel:0` (dump_pruned_model.py:52-76 reads kernel, bias, mask-o as neighbours)."""
+    with open(path, "rb") as f:
+        model = pickle.load(f)
+    try:
+        ck = model["transformer_ckpt"]
+        masks, masked, origin = ck["absolute_mask"], ck["masked_ckpt"], ck.get("origin_ckpt", {})
+    except (KeyError, TypeError) as e:
+        raise ValueError(f"{path}: not a dump_pruned_model pickle ({e})") from None
+    layers = []
+    for mname, mval in masks.items():
+        scope = mname.rsplit("/", 1)[0] if "/" in mname else ""
+        kname = next((k for k in masked if k.rsplit("/", 1)[0] == scope and "kernel" in k.rsplit("/", 1)[-1]), None)
+        if kname is None:
+            raise ValueError(f"{mname}: no masked kernel in the same scope")
+        mask = np.asarray(mval) != 0
+        mk = np.asarray(masked[kname])
+        if mask.shape != mk.shape:
+            raise ValueError(f"{mname}: mask {mask.shape} and kernel {mk.shape} differ in shape")
+        bname = next((k for k in origin if k.rsplit("/", 1)[0] == scope and "bias" in k.rsplit("/", 1)[-1]), None)
+        layers.append({"name": kname, "kernel": np.asarray(origin.get(kname, mk)), "masked_kernel": mk,
+                       "mask": mask, "bias": None if bname is None else np.asarray(origin[bname])})
+    return layers
+
+
+def tiles_from_dumped_layer(layer: dict, G: int = 128, strict: bool = False):
+    """One layer of `load_bert_dumped_model` as (TileSet, residual): its `absolute_mask` read like any
+    other reference mask (`tiles_from_reference_mask`); pack `layer["masked_kernel"]` or `layer["kernel"]`."""
+    return tiles_from_reference_mask(layer["mask"], G, strict)

@@ -46,6 +46,15 @@ class TWLayer:
         self._h = C.c_void_p()
         with torch.cuda.device(self.device):
             check(lib.ts_layer_create(C.byref(self._h), self.K, self.N, self.G, _TS_DTYPE[dtype]))
+        self.retile(tiles)
+
+    def retile(self, tiles: TileSet) -> None:
+        """Installs another tile structure of the same [K, N] matrix (ts_layer_set_tiles); the packed
+        weights are dropped, call `pack` again."""
+        if (tiles.K, tiles.N) != (self.K, self.N) or tiles.G > self.G:
+            raise ValueError("the new tiles describe another matrix")
+        self.tiles = tiles
+        with torch.cuda.device(self.device):
             self._kp, kp = _i32(tiles.tile_k_ptr)
             self._kk, kk = _i32(tiles.kept_k)
             self._np, npp = _i32(tiles.tile_n_ptr)
@@ -111,6 +120,11 @@ class TWLayer:
         with torch.cuda.device(self.device):
             check(lib.ts_layer_pack_weights(self._h, C.c_void_p(W.data_ptr()), W.stride(0), _TS_DTYPE[W.dtype],
                                             _stream_ptr(self.device)))
+
+    def set_unit_rows(self, unit_rows: int) -> None:
+        """Pins the kernel variant (work units of at most 128 or 256 batch rows); 0 = automatic."""
+        with torch.cuda.device(self.device):
+            check(lib.ts_layer_set_unit_rows(self._h, int(unit_rows)))
 
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:

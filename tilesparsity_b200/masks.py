@@ -41,6 +41,24 @@ def img2col_forward(weights):
     return out
 
 
+def img2col_back_ward(masks, mask_shape):
+    """2-D masks -> the shapes of the weights they belong to: masks of HWIO conv kernels are reshaped
+    to [kh, kw, cin, cout], 2-D ones pass through (prune_algo.py:27-37; the hooks hand the result
+    back to the graph's 4-D mask placeholders, Pruning/VGG/myhook.py:205-209).  `mask_shape` holds
+    the original weights (anything with a `.shape`), as in the reference."""
+    out = []
+    for m, w in zip(masks, mask_shape):
+        shp = tuple(w.shape)
+        if len(shp) == 4:
+            if m.shape[0] != shp[0] * shp[1] * shp[2] or m.shape[1] != shp[3]:
+                raise ValueError(f"a mask of shape {tuple(m.shape)} does not belong to a kernel of shape {shp}")
+            m = m.reshape(shp)
+        elif len(shp) != 2:
+            raise ValueError(f"weights of shape {shp} are neither a conv kernel nor a matrix")
+        out.append(m)
+    return out
+
+
 def _is_f64(x) -> bool:
     return isinstance(x, np.floating) and not isinstance(x, np.float32)
 
@@ -48,7 +66,8 @@ def _is_f64(x) -> bool:
 def build_mask(name: str, scores, sparsity, granularity: int = 128, g1percent=None, want_residual: bool = False,
                device=None) -> MaskResult:
     """Runs one of the mask algorithms on the GPU.  `name` is a reference name (tw1, tw2, tw1m, tw2m),
-    a BERT pruning type (bert_type2 / bert_type7 / bert_type8) or topk_l1."""
+    a BERT pruning type (bert_type2 / bert_type7 / bert_type8), topk_l1, or tw_cols_rows (column stage
+    at `g1percent` percent, tile-row stage at `sparsity` percent)."""
     if name not in _lib.MASK_MODES:
         raise KeyError(f"unknown mask algorithm {name!r}")
     if not torch.cuda.is_available():

@@ -139,18 +139,18 @@ class ShardedTWLayer:
     def masked_gemm_allgather(self, At, buf, handle):
         """One kernel computes this rank's slab and stores every kept row into all ranks' gathered
         buffers (plain stores to peer-mapped memory: the transfer over NVLink overlaps the tiles still
-        being computed).  The barriers around it are the only other communication: peers must have
-        finished with the buffer's previous contents before it is overwritten, and every rank's
-        stores must have landed before anyone reads it."""
-        import torch
+        being computed).  The two barriers around it are device-side (signal pads of the symmetric
+        allocation, enqueued on the current stream like the kernel, nothing blocks the host): peers
+        must have finished with the buffer's previous contents before it is overwritten, and every
+        rank's kernel, hence its stores, must have completed before anyone's stream goes on to read
+        the buffer.  Consecutive steps therefore queue up back to back."""
         row0 = self.rank * self.plan.n_pad
         n_loc = self.local.N
         pitch = buf.stride(0) * buf.element_size()
         peers = [int(handle.buffer_ptrs[p]) + row0 * pitch for p in range(self.world) if p != self.rank]
-        handle.barrier()
+        handle.barrier(channel=0)
         self.layer.masked_gemm(At, out=buf[row0:row0 + n_loc], peers=peers)
-        torch.cuda.current_stream(self.layer.device).synchronize()
-        handle.barrier()
+        handle.barrier(channel=1)
         return buf
 
     def assemble(self, gathered):

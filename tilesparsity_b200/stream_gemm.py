@@ -79,15 +79,25 @@ def checkout(test: torch.Tensor, ref: torch.Tensor, err: float, out=sys.stderr) 
     that cancel to almost zero, so here they apply where either magnitude reaches err (below that
     the absolute test is the only one that can mean anything).
     """
-    v2, v1 = test.float(), ref.float()
-    big = (v1.abs() >= err) | (v2.abs() >= err)
-    bad = (big & ((v1 / v2 > 1 + err) | (v2 / v1 > 1 + err))) | ((v2 - v1).abs() > err)
-    errors = int(bad.sum().item())
+    errors = checkout_counts(test, ref, err)[0]
     if errors > 0:
         print(f"CUTLASS results incorrect. Errors : {errors} / {test.numel()}\n", file=out)
     else:
         print("PASSED !!!\n", file=out)
     return errors
+
+
+def checkout_counts(test: torch.Tensor, ref: torch.Tensor, err: float):
+    """(errors under the rule `checkout` applies, errors under the reference's rule to the letter).
+
+    The second count includes the elements whose magnitudes are below err on both sides and whose
+    ratio alone trips the reference's test; the difference between the two is what the magnitude
+    guard lets through."""
+    v2, v1 = test.float(), ref.float()
+    ratio = (v1 / v2 > 1 + err) | (v2 / v1 > 1 + err)
+    far = (v2 - v1).abs() > err
+    big = (v1.abs() >= err) | (v2.abs() >= err)
+    return int(((big & ratio) | far).sum().item()), int((ratio | far).sum().item())
 
 
 def _time_us(fn, iters: int) -> float:
@@ -160,13 +170,15 @@ def run(M: int, N: int, K: int, N_pruned: int, K_pruned: int, dtype=torch.float1
     print(f"Stream  GEMM : {t_stream:f} us.", file=out)
     result = {"M": M, "N": N, "K": K, "N_pruned": N_pruned, "K_pruned": K_pruned, "block_num": block_num,
               "dense_us": t_dense, "stream_us": t_stream, "speedup": t_dense / t_stream,
-              "kept_tflops": 2.0 * M * sum(n * k for n, k in zip(N_cal, K_cal)) / t_stream / 1e6, "errors": []}
+              "kept_tflops": 2.0 * M * sum(n * k for n, k in zip(N_cal, K_cal)) / t_stream / 1e6, "errors": [],
+              "errors_reference_rule": []}
     if check_results:
         # (ii) compaction + cuBLAS per tile (CuBlas_Gemm_NN_reference, basic_nn.cu:507-557)
         C_ref = torch.zeros((N, M), dtype=dtype, device=dev)
         for t in range(block_num):
             C_ref[cols_l[t]] = torch.matmul(W[rows_l[t]][:, cols_l[t]].t().contiguous(), A[rows_l[t]])
         result["errors"].append(checkout(C_stream, C_ref, err))
+        result["errors_reference_rule"].append(checkout_counts(C_stream, C_ref, err)[1])
         # the CUDA-core twin through a layer handle built from the same index lists
         from .layer import TWLayer
         from .tiles import TileSet
@@ -179,9 +191,13 @@ def run(M: int, N: int, K: int, N_pruned: int, K_pruned: int, dtype=torch.float1
         layer.pack(W)
         C_simt = layer.masked_gemm(A, simt=True)
         result["errors"].append(checkout(C_stream, C_simt, err))
+        result["errors_reference_rule"].append(checkout_counts(C_stream, C_simt, err)[1])
         layer.close()
         # (iii) dense product on zero-filled weights
         result["errors"].append(checkout(C_stream, C_dense, err))
+        result["errors_reference_rule"].append(checkout_counts(C_stream, C_dense, err)[1])
+        print(f"elements only the magnitude guard lets through (reference rule to the letter): "
+              f"{result['errors_reference_rule']} of {C_stream.numel()}", file=sys.stderr)
     return result
 
 
