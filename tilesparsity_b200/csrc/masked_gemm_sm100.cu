@@ -100,54 +100,18 @@ struct Cfg {
 
 __device__ __forceinline__ WorkItem load_item(const WorkItem* p) {
   const int4* q = reinterpret_cast<const int4*>(p);
-  const uint64_t keep = l2_policy_evict_last();
   union {
     int4 v[3];
     WorkItem w;
   } u;
-  u.v[0] = ld_nc_hint(q, keep);
-  u.v[1] = ld_nc_hint(q + 1, keep);
-  u.v[2] = ld_nc_hint(q + 2, keep);
+  u.v[0] = __ldg(q);
+  u.v[1] = __ldg(q + 1);
+  u.v[2] = __ldg(q + 2);
   return u.w;
 }
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-// Arrival without waiting: the thread's earlier writes are visible to the threads that later pass
-// bar.sync on the same barrier.
-__device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
-  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-// Work item of CTA `cta` in round r, or an empty item past the end of the schedule.
-__device__ __forceinline__ WorkItem fetch_item(const WorkItem* sched, int rounds, int grid, int cta,
-                                               int r) {
-  if (r < rounds) return load_item(sched + static_cast<size_t>(r) * grid + cta);
-  WorkItem w;
-  w.k_list = nullptr;
-  w.n_list = nullptr;
-  w.k_count = w.n_count = w.w_row0 = w.c_row0 = w.flags = w.m_begin = w.m_len = 0;
-  w.tile = -1;
-  return w;
-}
-
-__device__ __forceinline__ int k_blocks(const WorkItem& w) { return (w.k_count + kKB - 1) / kKB; }
-
-// Ct row (global column of W) of tile column j of a work item.
-__device__ __forceinline__ long long c_row_of(const WorkItem& w, int j) {
-  return w.c_row0 + (w.n_list ? __ldg(w.n_list + j) + ((w.flags & kItemRelative) ? j : 0) : j);
-}
-
-__device__ __forceinline__ float apply_act(float x, int act) {
-  if (act == kActRelu) return fmaxf(x, 0.0f);
-  if (act == kActGelu) {
-    // x * 0.5 * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))   (Pruning/BERT/utils/modeling.py:264-277)
-    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-    return 0.5f * x * (1.0f + tanhf(u));
-  }
-  return x;
 }
 
 template <int DT, int MT>
@@ -192,20 +156,14 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       if (lane < kMetaLanes) {
-        cp_async_16_ca_hint(smem_u32(&bars->meta_ring[gw][i][lane * 4]),
-                            recs + static_cast<size_t>(gw / kWarpsPerBlock + i * kWarpGroups) * kMetaInts + meta_piece,
-                            l2_policy_evict_last());
+        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][i][lane * 4]),
+                       recs + static_cast<size_t>(gw / kWarpsPerBlock + i * kWarpGroups) * kMetaInts + meta_piece);
       }
       cp_async_commit();
     }
   }
 
-  // Set-up in two tiers.  The producers (weight TMA warp, gather warps) need only the mbarriers: the
-  // first lane of the first gather warp initialises them, the five producer warps meet on a barrier of
-  // their own and start copying, while warp 1 is still allocating tensor memory.  The MMA and epilogue
-  // warps meet on a second barrier, at which the producers merely arrive.
-  constexpr int kBarGather = 3, kBarAll = 4;
-  if (warp == 2 && lane == 0) {
+  if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       // weight TMA thread + the cp.async lanes of the warps that fill the stage
       mbar_init(smem_u32(&bars->full[s]), 1 + 32 * kWarpsPerBlock);
@@ -218,20 +176,14 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
     bars->abort_flag = 0;
     mbar_fence_init();
   }
-  uint32_t tmem_base = 0;
-  if (warp == 0 || (warp >= 2 && warp < 6)) {
-    named_barrier_sync(kBarGather, 32 * (kGW + 1));
-    named_barrier_arrive(kBarAll, kThreads);
-  } else {
-    if (warp == 1) {
-      tmem_alloc(smem_u32(&bars->tmem_base), C::kTmemCols);
-      tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    named_barrier_sync(kBarAll, kThreads);
-    tc_fence_after_sync();
-    tmem_base = bars->tmem_base;
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&bars->tmem_base), C::kTmemCols);
+    tmem_relinquish();
   }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
   // The next kernel in the stream may begin its own set-up now (it cannot touch this kernel's
   // outputs before its grid_dependency_wait, which returns only when this grid has completed).
   grid_launch_dependents();
@@ -395,9 +347,8 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       cp_async_arrive_noinc(bar);
       // request the warp's part of the record kAhead of its blocks ahead; one group per block
       if (lane < kMetaLanes) {
-        cp_async_16_ca_hint(smem_u32(&bars->meta_ring[gw][(it + kAhead) % kMetaSlots][lane * 4]),
-                            recs + static_cast<size_t>(j + kAhead * kWarpGroups) * kMetaInts + meta_piece,
-                            l2_policy_evict_last());
+        cp_async_16_ca(smem_u32(&bars->meta_ring[gw][(it + kAhead) % kMetaSlots][lane * 4]),
+                       recs + static_cast<size_t>(j + kAhead * kWarpGroups) * kMetaInts + meta_piece);
       }
       cp_async_commit();
     }

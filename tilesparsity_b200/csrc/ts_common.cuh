@@ -220,28 +220,6 @@ __device__ __forceinline__ void cp_async_16_ca(uint32_t dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-// L2 cache policy "keep these lines longer than ordinary ones": for the few hundred KiB of schedule
-// data every launch of a layer re-reads first thing, between launches that stream hundreds of MiB of
-// activations and outputs through L2.
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-
-__device__ __forceinline__ void cp_async_16_ca_hint(uint32_t dst, const void* src, uint64_t policy) {
-  asm volatile("cp.async.ca.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(policy)
-               : "memory");
-}
-
-__device__ __forceinline__ int4 ld_nc_hint(const int4* p, uint64_t policy) {
-  int4 v;
-  asm volatile("ld.global.nc.L2::cache_hint.v4.s32 {%0, %1, %2, %3}, [%4], %5;"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p), "l"(policy));
-  return v;
-}
-
 // Plain 16-byte copy (no zero-fill operand): the form the load/store unit issues fastest.
 __device__ __forceinline__ void cp_async_16_full(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
