@@ -114,6 +114,35 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Work item of CTA `cta` in round r, or an empty item past the end of the schedule.
+__device__ __forceinline__ WorkItem fetch_item(const WorkItem* sched, int rounds, int grid, int cta,
+                                               int r) {
+  if (r < rounds) return load_item(sched + static_cast<size_t>(r) * grid + cta);
+  WorkItem w;
+  w.k_list = nullptr;
+  w.n_list = nullptr;
+  w.k_count = w.n_count = w.w_row0 = w.c_row0 = w.flags = w.m_begin = w.m_len = 0;
+  w.tile = -1;
+  return w;
+}
+
+__device__ __forceinline__ int k_blocks(const WorkItem& w) { return (w.k_count + kKB - 1) / kKB; }
+
+// Ct row (global column of W) of tile column j of a work item.
+__device__ __forceinline__ long long c_row_of(const WorkItem& w, int j) {
+  return w.c_row0 + (w.n_list ? __ldg(w.n_list + j) + ((w.flags & kItemRelative) ? j : 0) : j);
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  if (act == kActRelu) return fmaxf(x, 0.0f);
+  if (act == kActGelu) {
+    // x * 0.5 * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))   (Pruning/BERT/utils/modeling.py:264-277)
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.0f + tanhf(u));
+  }
+  return x;
+}
+
 template <int DT, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
