@@ -111,3 +111,25 @@ def test_tiles_from_mask_and_back():
     with pytest.raises(ValueError):
         tiles_from_lists(50, 400, 64, [np.array([3, 2])] * nt, cm)
     assert ts.kept_flops_per_row() == 2 * int((ts.k_counts() * ts.n_counts()).sum())
+
+
+def test_img2col_round_trip_on_the_host():
+    """img2col_forward / img2col_back_ward (Pruning/VGG/prune_algo.py:16-37): HWIO kernels become
+    [(kh*kw*cin), cout] matrices of absolute values with row index (kh*KW + kw)*cin_total + cin, 2-D
+    weights pass through, and masks go back to the shapes of the weights they belong to."""
+    import torch
+    from tilesparsity_b200 import masks
+    g = synth.rng(1)
+    conv = g.standard_normal((3, 3, 8, 16)).astype(np.float32)
+    fc = g.standard_normal((32, 10)).astype(np.float32)
+    two_d = masks.img2col_forward([conv, fc])
+    assert tuple(two_d[0].shape) == (72, 16) and tuple(two_d[1].shape) == (32, 10)
+    assert float(two_d[0][(1 * 3 + 2) * 8 + 5, 7]) == abs(float(conv[1, 2, 5, 7]))
+    assert np.array_equal(two_d[1].numpy(), np.abs(fc))
+    m = [(t > 0.5) for t in two_d]
+    back = masks.img2col_back_ward(m, [conv, fc])
+    assert tuple(back[0].shape) == conv.shape and tuple(back[1].shape) == fc.shape
+    assert bool(back[0][1, 2, 5, 7]) == bool(abs(conv[1, 2, 5, 7]) > 0.5)
+    assert torch.equal(back[0].reshape(72, 16), m[0])
+    with pytest.raises(ValueError):
+        masks.img2col_back_ward([m[1]], [conv])

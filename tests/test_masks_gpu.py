@@ -147,3 +147,19 @@ def test_percentile_matches_numpy(n, q):
     ref = np.percentile([np.float32(x) for x in v] if n <= 5000 else v, q)
     got = tm.percentile(torch.from_numpy(v).cuda(), q)
     assert float(ref) == got
+
+
+def test_conv_kernel_masks_round_trip_through_pruning_fun():
+    """The hooks' call sequence (Pruning/VGG/myhook.py:199-209): img2col_forward, pruning_fun, then
+    img2col_back_ward hands 4-D HWIO masks back; checked against the reference's golden tw2 mask of a
+    3 x 3 x 32 x 160 kernel."""
+    from tilesparsity_b200 import masks as tm
+    algo, shapes, sparsity, gran, g1, seed, dist = CASES["tw2_conv"]
+    g = np.random.Generator(np.random.PCG64(seed))
+    w = (g.standard_normal(shapes[0], dtype=np.float32) * np.float32(np.sqrt(2.0 / np.prod(shapes[0][:-1])))).astype(np.float32)
+    scores = [t.numpy() for t in tm.img2col_forward([w])]
+    assert np.array_equal(scores[0], case_inputs("tw2_conv")[0])
+    masks2d = tm.pruning_fun(algo)(scores, sparsity, gran)
+    masks4d = tm.img2col_back_ward(masks2d, [w])
+    assert masks4d[0].shape == w.shape
+    assert np.array_equal(masks4d[0].reshape(-1, w.shape[3]), load_golden("tw2_conv")[0])
