@@ -252,6 +252,24 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
                      uint8_t* const* masks_dev, const int64_t* ld_masks, uint8_t* const* residual_dev,
                      ts_mask_result_t** out, void* stream);
 
+/* The same for float64 scores: scores_dev[l] is double [Ks[l]][lds[l]].  NumPy then computes every
+ * step in double (squares, pairwise sum, sqrt, division, percentile, comparison), and so does this
+ * entry point.  Offered for TS_MASK_TW1 and TS_MASK_BERT_TW_K (others: TS_ERR_UNSUPPORTED).  This is
+ * the path of the reference's Taylor scores, which its hooks accumulate in float64 arrays
+ * (Pruning/VGG/myhook.py:248-257) before handing them to pruning_fun. */
+int ts_build_tw_mask_f64(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                         const int64_t* lds, int G, double sparsity, uint8_t* const* masks_dev,
+                         const int64_t* ld_masks, ts_mask_result_t** out, void* stream);
+
+/* One step of the reference's first-order Taylor importance score, accumulated on the device:
+ *     acc[i] += square(grad[i] * weight[i])
+ * with the product and the square in float32 (compute_taylor_score: tf.math.square(v * m) on float32
+ * tensors, Pruning/VGG/myhook.py:44-48, Pruning/BERT/utils/MyHook.py:178-182) and the running sum in
+ * float64 (after_run adds each step's scores into np.zeros(shape) arrays, myhook.py:248-257).
+ * grad is dLoss/dmask, weight the layer's weights, both float32 with n elements; acc is double[n],
+ * zeroed by the caller before the first step.  Enqueued on `stream`, no synchronisation. */
+int ts_taylor_accumulate(const float* grad_dev, const float* weight_dev, double* acc_dev, int64_t n, void* stream);
+
 /* Sizes of one layer's tile structure. */
 int ts_mask_result_layer(const ts_mask_result_t* r, int layer, int* n_tiles, int* total_kept_k,
                          int* total_kept_n);

@@ -41,6 +41,11 @@ CASES = {
     # benchmark-configuration sizes: VGG16 conv5 as a 4608 x 512 matrix, the NMT LSTM gate matrix
     "tw2_vgg_conv5":    ("tw2", [(3, 3, 512, 512)], 75.0, 128, None, 3001, "he"),
     "tw1m_nmt_lstm":    ("tw1m", [(2048, 4096)], 75.0, 128, 1.5, 4001, "uniform"),
+    # Taylor scores: float64 arrays, three steps of square(grad * w) in float32 accumulated in double
+    # (what the reference's hooks hand to pruning_fun after score accumulation, myhook.py:248-257)
+    "tw1_taylor64":     ("tw1", [(96, 320)], 75.0, 128, None, 81, "taylor"),
+    "tw1_taylor64_grp": ("tw1", [(3, 3, 16, 96), (200, 333)], 62.5, 64, None, 82, "taylor"),
+    "tw1_taylor64_ffn": ("tw1", [(768, 3072)], 75.0, 128, None, 83, "taylor"),
     # baseline patterns (no granularity argument): element-wise and vector-wise
     "ew_small":         ("ew", [(96, 320)], 75.0, None, None, 51, "normal"),
     "ew_group":         ("ew", [(64, 256), (80, 200), (48, 130)], 62.5, None, None, 52, "normal"),
@@ -65,6 +70,20 @@ BERT_CASES = {
 }
 
 
+def taylor_steps(g, shp, steps: int = 3):
+    """(weights, accumulated scores): per step square(grad * w) in float32 (compute_taylor_score,
+    Pruning/VGG/myhook.py:44-48) added into a float64 array (after_run, :248-257)."""
+    w = (g.standard_normal(shp, dtype=np.float32) * np.float32(0.05)).astype(np.float32)
+    acc = np.zeros(shp)
+    grads = []
+    for _ in range(steps):
+        grad = g.standard_normal(shp, dtype=np.float32)
+        grads.append(grad)
+        t = (grad * w).astype(np.float32)
+        acc += (t * t).astype(np.float32)
+    return (w, grads), acc
+
+
 def case_inputs(name: str):
     """The seeded score matrices of a case, as the reference's hooks hand them over: 2-D arrays of
     absolute values (img2col_forward, prune_algo.py:16-24, reshapes HWIO kernels and takes abs)."""
@@ -75,6 +94,12 @@ def case_inputs(name: str):
     g = np.random.Generator(np.random.PCG64(seed))
     out = []
     for shp in shapes:
+        if dist == "taylor":
+            w, acc = taylor_steps(g, shp)
+            if acc.ndim == 4:
+                acc = acc.reshape(-1, acc.shape[3])
+            out.append(np.abs(acc))
+            continue
         if dist == "uniform":
             w = g.uniform(-0.1, 0.1, size=shp).astype(np.float32)
         elif dist == "he":

@@ -163,3 +163,27 @@ def test_conv_kernel_masks_round_trip_through_pruning_fun():
     masks4d = tm.img2col_back_ward(masks2d, [w])
     assert masks4d[0].shape == w.shape
     assert np.array_equal(masks4d[0].reshape(-1, w.shape[3]), load_golden("tw2_conv")[0])
+
+
+def test_taylor_scores_accumulate_on_the_device_and_prune_like_the_reference():
+    """square(dL/dmask * w) per step in float32, summed in float64 on the GPU, equals the NumPy
+    accumulation bit for bit; pruning from it equals the reference's masks for the same scores."""
+    from make_golden import taylor_steps
+    from tilesparsity_b200 import masks as tm
+    algo, shapes, sparsity, gran, g1, seed, dist = CASES["tw1_taylor64_grp"]
+    g = np.random.Generator(np.random.PCG64(seed))
+    layers = [taylor_steps(g, shp) for shp in shapes]            # ((w, grads), acc) per layer, in case order
+    weights = [torch.from_numpy(w).cuda() for (w, _), _ in layers]
+    ts = tm.TaylorScores(weights)
+    for step in range(3):
+        ts.accumulate([torch.from_numpy(grads[step]).cuda() for (_, grads), _ in layers], weights)
+    for a, (_, acc) in zip(ts.acc, layers):
+        assert np.array_equal(a.cpu().numpy(), acc)
+    masks, res = ts.prune("tw1", sparsity, gran)
+    gold = load_golden("tw1_taylor64_grp")
+    for m, gmask, shp in zip(masks, gold, shapes):
+        assert tuple(m.shape) == tuple(shp)
+        assert np.array_equal(m.cpu().numpy().reshape(gmask.shape), gmask)
+    assert all(float(a.abs().sum()) == 0.0 for a in ts.acc)       # cleared after pruning, as the hook does
+    with pytest.raises(ValueError):
+        tm.build_mask("tw2", [np.ones((8, 8))], 50.0)             # float64 scores: tw1 / type 7 only

@@ -78,6 +78,9 @@ SIGNATURES = {
     "ts_build_tw_mask": (C.c_int, [C.c_int, C.c_int, C.POINTER(_vp), C.POINTER(C.c_int), C.POINTER(C.c_int), _i64p,
                                    C.c_int, C.c_double, C.c_int, C.c_double, C.POINTER(_vp), _i64p, C.POINTER(_vp),
                                    C.POINTER(_vp), _vp]),
+    "ts_build_tw_mask_f64": (C.c_int, [C.c_int, C.c_int, C.POINTER(_vp), C.POINTER(C.c_int), C.POINTER(C.c_int), _i64p,
+                                       C.c_int, C.c_double, C.POINTER(_vp), _i64p, C.POINTER(_vp), _vp]),
+    "ts_taylor_accumulate": (C.c_int, [_vp, _vp, _vp, C.c_int64, _vp]),
     "ts_mask_result_layer": (C.c_int, [_vp, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "ts_mask_result_copy": (C.c_int, [_vp, C.c_int, _i32p, _i32p, _i32p, _i32p, _i32p]),
     "ts_mask_result_thresholds": (C.c_int, [_vp, C.POINTER(C.c_double)]),

@@ -238,7 +238,7 @@ std::vector<int> fixed_bounds(int N, int G) {
 }
 
 struct LayerIn {
-  const float* score;
+  const float* score;     // float32 scores, or (f64 row stage) the same pointer holding doubles
   int K, N;
   long long ld;
   uint8_t* mask;
@@ -261,6 +261,7 @@ struct ts_mask_result {
 namespace {
 
 struct Scratch {
+  ts::SelectState64* st64 = nullptr;   // state of the double-precision select
   unsigned int* hist = nullptr;
   unsigned long long* count = nullptr;
   unsigned int* min_gt = nullptr;
@@ -273,6 +274,7 @@ int alloc_scratch(Arena& arena, Scratch* sc) {
   TSM_OK(arena.alloc(&sc->count, 1));
   TSM_OK(arena.alloc(&sc->min_gt, 1));
   TSM_OK(arena.alloc(&sc->st, 1));
+  TSM_OK(arena.alloc(&sc->st64, 1));
   TSM_OK(arena.alloc(&sc->thr, 4));
   return TS_OK;
 }
@@ -305,7 +307,7 @@ int read_thresholds(const Scratch& sc, int slot, double* out, cudaStream_t s) {
 int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>& bounds,
               const std::vector<uint8_t*>& colkeep_dev, const std::vector<std::vector<uint8_t>>& colkeep_host,
               int sel, double q, bool wide, ts_mask_result* res, double* thr_out, Arena& arena,
-              const Scratch& sc, cudaStream_t s) {
+              const Scratch& sc, cudaStream_t s, bool f64 = false) {
   const int nl = static_cast<int>(L.size());
   std::vector<long long> off(nl + 1, 0);
   std::vector<int> tile_off(nl + 1, 0);
@@ -317,8 +319,16 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
   const long long total = off[nl];
   const int total_tiles = tile_off[nl];
   float* norms = nullptr;
+  double* norms64 = nullptr;   // float64 scores: norms, percentile and comparison all in double
   uint8_t* keep = nullptr;
-  TSM_OK(arena.alloc(&norms, total));
+  if (f64) {
+    if (sel != 0 || !colkeep_dev.empty()) {
+      return ts_internal_fail(TS_ERR_UNSUPPORTED, "float64 scores are supported by the tw1 row stage only");
+    }
+    TSM_OK(arena.alloc(&norms64, total));
+  } else {
+    TSM_OK(arena.alloc(&norms, total));
+  }
   TSM_OK(arena.alloc(&keep, total));
   std::vector<int*> bounds_dev(nl, nullptr);
   for (int l = 0; l < nl; ++l) {
@@ -326,7 +336,10 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
     TSM_CUDA(cudaMemcpyAsync(bounds_dev[l], bounds[l].data(), bounds[l].size() * sizeof(int),
                              cudaMemcpyHostToDevice, s));
     const int nt = static_cast<int>(bounds[l].size()) - 1;
-    if (sel == 2) {
+    if (f64) {
+      TSM_CUDA(ts::tile_row_norms64_launch(reinterpret_cast<const double*>(L[l].score), L[l].ld, L[l].K,
+                                           bounds_dev[l], nt, norms64 + off[l], 1, s));
+    } else if (sel == 2) {
       TSM_CUDA(ts::tile_row_l1_launch(L[l].score, L[l].ld, L[l].K, bounds_dev[l], nt, norms + off[l], s));
     } else {
       int uniform = 0;   // leading tiles that are exactly [128 t, 128 (t+1))
@@ -338,7 +351,16 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
                                          sel == 0 ? 1 : 0, uniform, s));
     }
   }
-  if (sel == 0) {
+  if (f64) {
+    const Ranks r = percentile_ranks(total, q, true);
+    TSM_CUDA(ts::percentile64_dev_launch(norms64, total, r.pi, r.ni, r.gamma_d, sc.st64, sc.hist, sc.thr + 1, s));
+    TSM_CUDA(ts::threshold64_dev_launch(norms64, total, sc.thr + 1, keep, s));
+    ts::SelectState64 st64;
+    TSM_CUDA(cudaMemcpyAsync(&st64, sc.st64, sizeof(st64), cudaMemcpyDeviceToHost, s));
+    if (thr_out) TSM_CUDA(cudaMemcpyAsync(thr_out, sc.thr + 1, sizeof(double), cudaMemcpyDeviceToHost, s));
+    TSM_CUDA(cudaStreamSynchronize(s));
+    if (st64.error) return ts_internal_fail(TS_ERR_CUDA, "radix select lost its rank (non-finite input?)");
+  } else if (sel == 0) {
     TSM_OK(percentile_to_device(norms, total, q, wide, false, sc, 1, s));
     TSM_CUDA(ts::threshold_dev_launch(norms, total, sc.thr + 1, keep, s));
     if (thr_out) TSM_OK(read_thresholds(sc, 1, thr_out, s));
@@ -439,10 +461,13 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
 
 extern "C" {
 
-int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
-                     const int64_t* lds, int G, double sparsity, int sparsity_is_f64, double g1percent,
-                     uint8_t* const* masks_dev, const int64_t* ld_masks, uint8_t* const* residual_dev,
-                     ts_mask_result_t** out, void* stream) {
+}  // extern "C"
+
+namespace {
+int build_tw_mask_impl(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                       const int64_t* lds, int G, double sparsity, int sparsity_is_f64, double g1percent,
+                       uint8_t* const* masks_dev, const int64_t* ld_masks, uint8_t* const* residual_dev,
+                       ts_mask_result_t** out, void* stream, bool f64) {
   if (!out) return ts_internal_fail(TS_ERR_INVALID, "out is NULL");
   *out = nullptr;
   if (mode < TS_MASK_TW1 || mode > TS_MASK_TW_COLS_ROWS) return ts_internal_fail(TS_ERR_INVALID, "unknown mode %d", mode);
@@ -546,7 +571,7 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
       for (int l = 0; l < n_layers; ++l) bounds[l] = fixed_bounds(L[l].N, G);
     }
     const int sel = mode == TS_MASK_BERT_PER_TILE ? 1 : (mode == TS_MASK_TOPK_L1 ? 2 : 0);
-    if ((rc = row_stage(L, bounds, colkeep_dev, colkeep_host, sel, q, wide, res, &res->thr[1], arena, sc, s)) != TS_OK) break;
+    if ((rc = row_stage(L, bounds, colkeep_dev, colkeep_host, sel, q, wide, res, &res->thr[1], arena, sc, s, f64)) != TS_OK) break;
 
     if (tew) {
       // element-wise residual (tw_mix_fn, prune_algo.py:151-177): rank |w| - mask over every
@@ -586,6 +611,36 @@ int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, cons
     return rc;
   }
   *out = res;
+  return TS_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int ts_build_tw_mask(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                     const int64_t* lds, int G, double sparsity, int sparsity_is_f64, double g1percent,
+                     uint8_t* const* masks_dev, const int64_t* ld_masks, uint8_t* const* residual_dev,
+                     ts_mask_result_t** out, void* stream) {
+  return build_tw_mask_impl(mode, n_layers, scores_dev, Ks, Ns, lds, G, sparsity, sparsity_is_f64, g1percent,
+                            masks_dev, ld_masks, residual_dev, out, stream, false);
+}
+
+int ts_build_tw_mask_f64(int mode, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
+                         const int64_t* lds, int G, double sparsity, uint8_t* const* masks_dev,
+                         const int64_t* ld_masks, ts_mask_result_t** out, void* stream) {
+  if (mode != TS_MASK_TW1 && mode != TS_MASK_BERT_TW_K) {
+    if (out) *out = nullptr;
+    return ts_internal_fail(TS_ERR_UNSUPPORTED, "float64 scores: only TS_MASK_TW1 and TS_MASK_BERT_TW_K are offered");
+  }
+  return build_tw_mask_impl(mode, n_layers, scores_dev, Ks, Ns, lds, G, sparsity, 1, 0.0, masks_dev, ld_masks,
+                            nullptr, out, stream, true);
+}
+
+int ts_taylor_accumulate(const float* grad_dev, const float* weight_dev, double* acc_dev, int64_t n, void* stream) {
+  if (n < 0) return ts_internal_fail(TS_ERR_INVALID, "n=%lld is negative", static_cast<long long>(n));
+  if (n == 0) return TS_OK;
+  if (!grad_dev || !weight_dev || !acc_dev) return ts_internal_fail(TS_ERR_INVALID, "NULL argument");
+  TSM_CUDA(ts::taylor_accumulate_launch(grad_dev, weight_dev, acc_dev, n, static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
 

@@ -43,6 +43,26 @@ cudaError_t percentile_dev_launch(const float* vals, long long n, long long pi, 
                                   double gamma_d, int arith, SelectState* st, unsigned int* hist,
                                   double* thr_out, float* ab_out, cudaStream_t s);
 
+// Double-precision twins for float64 scores (mask_build_f64.cu): tile-row norms by the general kernel,
+// the percentile with everything in double (eight digit passes over 64-bit keys), the threshold.
+struct SelectState64 {
+  unsigned long long prefix;
+  unsigned long long rank;
+  unsigned long long count_le;
+  unsigned long long min_gt;
+  uint32_t error;
+  uint32_t pad_;
+};
+cudaError_t tile_row_norms64_launch(const double* score, long long ld, int K, const int* bounds_dev, int n_tiles,
+                                    double* norms, int divide, cudaStream_t s);
+cudaError_t percentile64_dev_launch(const double* vals, long long n, long long pi, long long ni, double gamma,
+                                    SelectState64* st, unsigned int* hist, double* thr_out, cudaStream_t s);
+cudaError_t threshold64_dev_launch(const double* vals, long long n, const double* thr, uint8_t* keep,
+                                   cudaStream_t s);
+// acc[i] += square(grad[i] * weight[i]), the product and the square in float32, the sum in double.
+cudaError_t taylor_accumulate_launch(const float* grad, const float* weight, double* acc, long long n,
+                                     cudaStream_t s);
+
 // keep[i] = vals[i] > *thr, the threshold read from device memory.
 cudaError_t threshold_dev_launch(const float* vals, long long n, const double* thr, uint8_t* keep,
                                  cudaStream_t s);

@@ -34,7 +34,7 @@ def img2col_forward(weights):
     """HWIO conv kernels -> 2-D [(kh*kw*cin), cout]; absolute values (prune_algo.py:16-24)."""
     out = []
     for w in weights:
-        t = w if isinstance(w, torch.Tensor) else torch.from_numpy(np.asarray(w))
+        t = w if isinstance(w, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(w))
         if t.dim() == 4:
             t = t.reshape(t.shape[0] * t.shape[1] * t.shape[2], t.shape[3])
         out.append(t.abs())
@@ -82,10 +82,14 @@ def build_mask(name: str, scores, sparsity, granularity: int = 128, g1percent=No
         t = s if isinstance(s, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(s))
         if t.dim() != 2:
             raise ValueError("scores must be 2-D (use img2col_forward for conv kernels)")
-        t = t.to(device=dev, dtype=torch.float32)
-        if t.stride(1) != 1:
-            t = t.contiguous()
         sc.append(t)
+    # float64 scores (the reference's accumulated Taylor scores) keep their type: NumPy would do every
+    # step in double, and so does the library's float64 row stage
+    f64 = all(t.dtype == torch.float64 for t in sc)
+    if f64 and name not in ("tw1", "bert_type7"):
+        raise ValueError("float64 scores are supported by tw1 and bert_type7 only; cast them to float32 for " + name)
+    sc = [t.to(device=dev, dtype=torch.float64 if f64 else torch.float32) for t in sc]
+    sc = [t if t.stride(1) == 1 else t.contiguous() for t in sc]
     n = len(sc)
     masks = [torch.empty((t.shape[0], t.shape[1]), dtype=torch.uint8, device=dev) for t in sc]
     resid = [torch.zeros((t.shape[0], t.shape[1]), dtype=torch.uint8, device=dev) for t in sc] \
@@ -95,12 +99,19 @@ def build_mask(name: str, scores, sparsity, granularity: int = 128, g1percent=No
     LA = C.c_int64 * n
     handle = C.c_void_p()
     with torch.cuda.device(dev):
-        check(lib.ts_build_tw_mask(
-            mode, n, VP(*[t.data_ptr() for t in sc]), IA(*[t.shape[0] for t in sc]), IA(*[t.shape[1] for t in sc]),
-            LA(*[t.stride(0) for t in sc]), int(granularity), float(sparsity), int(_is_f64(sparsity) or _is_f64(g1percent)),
-            float(g1percent), VP(*[m.data_ptr() for m in masks]), LA(*[m.stride(0) for m in masks]),
-            VP(*[r.data_ptr() for r in resid]) if resid else None, C.byref(handle),
-            C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+        if f64:
+            check(lib.ts_build_tw_mask_f64(
+                mode, n, VP(*[t.data_ptr() for t in sc]), IA(*[t.shape[0] for t in sc]), IA(*[t.shape[1] for t in sc]),
+                LA(*[t.stride(0) for t in sc]), int(granularity), float(sparsity),
+                VP(*[m.data_ptr() for m in masks]), LA(*[m.stride(0) for m in masks]), C.byref(handle),
+                C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
+        else:
+            check(lib.ts_build_tw_mask(
+                mode, n, VP(*[t.data_ptr() for t in sc]), IA(*[t.shape[0] for t in sc]), IA(*[t.shape[1] for t in sc]),
+                LA(*[t.stride(0) for t in sc]), int(granularity), float(sparsity),
+                int(_is_f64(sparsity) or _is_f64(g1percent)), float(g1percent), VP(*[m.data_ptr() for m in masks]),
+                LA(*[m.stride(0) for m in masks]), VP(*[r.data_ptr() for r in resid]) if resid else None,
+                C.byref(handle), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
     try:
         tiles = []
         for l, t in enumerate(sc):
@@ -174,6 +185,47 @@ def pruning_fun(pruning_type: str):
         return res.masks
 
     return fn
+
+
+class TaylorScores:
+    """First-order Taylor importance scores kept on the GPU, as the reference's pruning hooks keep
+    them on the host: one float64 accumulator per masked layer, `accumulate` adds a step's
+    square(dL/dmask * w) (compute_taylor_score and after_run, Pruning/VGG/myhook.py:44-48,248-257),
+    `prune` builds the masks from the accumulated scores and clears them (myhook.py:191-235, 259-261).
+
+    Gradients and weights are float32 CUDA tensors of the layers' own shapes (HWIO conv kernels or
+    2-D matrices); the masks come back in those shapes."""
+
+    def __init__(self, weights):
+        self.shapes = [tuple(w.shape) for w in weights]
+        self.device = weights[0].device
+        self.acc = [torch.zeros(s, dtype=torch.float64, device=self.device) for s in self.shapes]
+        self.steps = 0
+
+    def accumulate(self, grads, weights) -> None:
+        if len(grads) != len(self.acc) or len(weights) != len(self.acc):
+            raise ValueError("one gradient and one weight tensor per layer")
+        with torch.cuda.device(self.device):
+            for g, w, a in zip(grads, weights, self.acc):
+                if g.dtype != torch.float32 or w.dtype != torch.float32 or tuple(g.shape) != tuple(a.shape) \
+                        or tuple(w.shape) != tuple(a.shape) or not (g.is_contiguous() and w.is_contiguous()):
+                    raise ValueError("gradients and weights must be contiguous float32 tensors of the layer's shape")
+                check(lib.ts_taylor_accumulate(C.c_void_p(g.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(a.data_ptr()),
+                                               a.numel(), C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+        self.steps += 1
+
+    def prune(self, pruning_type: str, sparsity, granularity: int = 128, layers=None, reset: bool = True):
+        """Masks (bool CUDA tensors in the layers' shapes) of the layers in `layers` (default: all),
+        pruned together under one threshold as the reference prunes a layer group (Pruning/VGG/
+        pruning.py:392-404)."""
+        layers = list(range(len(self.acc))) if layers is None else list(layers)
+        scores = img2col_forward([self.acc[l] for l in layers])
+        res = build_mask(pruning_type, scores, sparsity, granularity)
+        out = img2col_back_ward(res.masks, [self.acc[l] for l in layers])
+        if reset:
+            for l in layers:
+                self.acc[l].zero_()
+        return out, res
 
 
 def percentile(values: torch.Tensor, q) -> float:
