@@ -185,12 +185,10 @@ int ts_plan_schedule(int n_tiles, const int32_t* k_counts, const int32_t* n_coun
 /* Element-wise residual of a TEW mask as a sparse term, applied after ts_masked_gemm:
  *     Ct[n][m] = (col_written[n] ? Ct[n][m] : 0) + alpha * sum_p val[p] * At[row_idx[p]][m]
  * over the non-zeros p in col_ptr[n] .. col_ptr[n+1] of column n (device arrays; val is 16-bit in
- * `dtype`; col_written_dev may be NULL when the tile-wise part wrote every column).  K is the number
- * of rows of At (every row index lies below it); up to K = 3200 a shared-memory variant runs, K = 0
- * (unknown) or larger selects the variant that reads every row piece from L2.  The reference's
+ * `dtype`; col_written_dev may be NULL when the tile-wise part wrote every column).  The reference's
  * tw1m / tw2m masks (prune_algo.py:151-191) carry these elements only as extra ones in the dense 0/1
  * mask; its GPU driver has no kernel for them. */
-int ts_residual_gemm(int dtype, int M, int N, int K, const int32_t* col_ptr_dev, const int32_t* row_idx_dev,
+int ts_residual_gemm(int dtype, int M, int N, const int32_t* col_ptr_dev, const int32_t* row_idx_dev,
                      const void* val_dev, const uint8_t* col_written_dev, const void* At_dev, int64_t lda,
                      void* Ct_dev, int64_t ldc, float alpha, void* stream);
 

@@ -91,7 +91,7 @@ SIGNATURES = {
     "ts_percentile_f32": (C.c_int, [_vp, C.c_int64, C.c_double, C.c_int, C.POINTER(C.c_double), _vp]),
     "ts_tw1_row_keep_noalloc": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_double, C.c_int, _vp,
                                           C.POINTER(C.c_double), _vp]),
-    "ts_residual_gemm": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int64, _vp, C.c_int64,
+    "ts_residual_gemm": (C.c_int, [C.c_int, C.c_int, C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int64, _vp, C.c_int64,
                                    C.c_float, _vp]),
     "ts_transpose16": (C.c_int, [_vp, C.c_int64, _vp, C.c_int64, C.c_int, C.c_int, _vp]),
     "ts_shard_plan": (C.c_int, [C.c_int, _i64p, C.c_int, _i32p]),

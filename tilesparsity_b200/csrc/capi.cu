@@ -1063,7 +1063,7 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   return TS_OK;
 }
 
-int ts_residual_gemm(int dtype, int M, int N, int K, const int32_t* col_ptr_dev, const int32_t* row_idx_dev,
+int ts_residual_gemm(int dtype, int M, int N, const int32_t* col_ptr_dev, const int32_t* row_idx_dev,
                      const void* val_dev, const uint8_t* col_written_dev, const void* At_dev, int64_t lda,
                      void* Ct_dev, int64_t ldc, float alpha, void* stream) {
   if (dtype != TS_DTYPE_F16 && dtype != TS_DTYPE_BF16) return fail(TS_ERR_INVALID, "dtype must be f16 or bf16");
@@ -1077,7 +1077,7 @@ int ts_residual_gemm(int dtype, int M, int N, int K, const int32_t* col_ptr_dev,
     return fail(TS_ERR_INVALID, "At and Ct must be 16-byte aligned");
   }
   TS_CUDA(ts::residual_spmm_launch(dtype, col_ptr_dev, row_idx_dev, val_dev, col_written_dev, At_dev, lda, Ct_dev,
-                                   ldc, M, N, K, alpha, static_cast<cudaStream_t>(stream)));
+                                   ldc, M, N, alpha, static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
 

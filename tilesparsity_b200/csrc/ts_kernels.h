@@ -42,11 +42,9 @@ cudaError_t pack_weights_launch(int w_dtype, int out_dtype, const void* W, long 
 
 // Sparse residual term (residual.cu): Ct[n][m] = (col_written[n] ? Ct[n][m] : 0) + alpha * sum over the
 // non-zeros p of column n of val[p] * At[row_idx[p]][m].  col_written may be nullptr (all written).
-// K is the number of rows of At (every row_idx is below it), or 0 when unknown: with K * 64 bytes
-// fitting in shared memory the slab variant runs, otherwise every non-zero reads its row piece from L2.
 cudaError_t residual_spmm_launch(int dtype, const int* col_ptr, const int* row_idx, const void* val,
                                  const uint8_t* col_written, const void* At, long long lda, void* Ct,
-                                 long long ldc, int M, int N, int K, float alpha, cudaStream_t stream);
+                                 long long ldc, int M, int N, float alpha, cudaStream_t stream);
 
 // out[c][r] = in[r][c] for 16-bit elements (pack.cu).
 cudaError_t transpose16_launch(const void* in, long long ld_in, void* out, long long ld_out,

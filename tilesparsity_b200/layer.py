@@ -281,7 +281,7 @@ class TEWLayer:
         M = At.shape[1]
         if self.nnz:
             with torch.cuda.device(self.device):
-                check(lib.ts_residual_gemm(_TS_DTYPE[self.dtype], M, self.N, self.K, C.c_void_p(self.col_ptr.data_ptr()),
+                check(lib.ts_residual_gemm(_TS_DTYPE[self.dtype], M, self.N, C.c_void_p(self.col_ptr.data_ptr()),
                                            C.c_void_p(self.row_idx.data_ptr()), C.c_void_p(self.val.data_ptr()),
                                            C.c_void_p(self.col_written.data_ptr()), C.c_void_p(At.data_ptr()),
                                            At.stride(0), C.c_void_p(Ct.data_ptr()), Ct.stride(0), alpha,
