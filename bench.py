@@ -721,6 +721,57 @@ def sweep_case(name, M, K, N, dtype, layer_fn, iters, note="", w_scale=0.02, rel
     return row
 
 
+def conv_case(name, B, H, W, cin, cout, algo, sparsity, g1, iters, note=""):
+    """A 3 x 3 convolution as an implicit masked GEMM (no im2col matrix): input planes packed from NHWC,
+    the GEMM over the padded pixel space, the output brought back to NHWC; each part timed, next to
+    cuDNN's dense convolution through torch on the same NHWC (channels-last) tensors."""
+    import torch
+    from tilesparsity_b200 import ConvTWLayer, build_mask, masks
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator(device=dev).manual_seed(3001)
+    w = torch.randn((3, 3, cin, cout), generator=gen, device=dev, dtype=torch.float32) * float(np.sqrt(2.0 / (9 * cin)))
+    res = build_mask(algo, masks.img2col_forward([w]), sparsity, G, g1)
+    layer = ConvTWLayer(w, res.tiles[0], torch.bfloat16)
+    n_sets = 4
+    xs = [torch.randn((B, H, W, cin), generator=gen, device=dev, dtype=torch.float32).clamp_min(0).to(torch.bfloat16)
+          for _ in range(n_sets)]
+    planes, geo = layer.pack_input(xs[0])
+    pl = [planes] + [torch.empty_like(planes) for _ in range(n_sets - 1)]
+    cts = [torch.zeros((cout, geo["m_padded"]), dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    ys = [torch.empty((B, H, W, cout), dtype=torch.bfloat16, device=dev) for _ in range(n_sets)]
+    for i in range(n_sets):
+        layer.pack_input(xs[i], pl[i])
+    steps = max(n_sets, iters // n_sets * n_sets)
+    t_pack = time_us(lambda i: layer.pack_input(xs[i % n_sets], pl[i % n_sets]), steps, n_sets, n_sets)
+    t_gemm = time_us(lambda i: layer.masked_conv(pl[i % n_sets], geo, out=cts[i % n_sets]), steps, n_sets, n_sets)
+    t_unpack = time_us(lambda i: layer.unpack_output(cts[i % n_sets], geo, ys[i % n_sets]), steps, n_sets, n_sets)
+
+    def whole(i):
+        s = i % n_sets
+        layer.pack_input(xs[s], pl[s])
+        layer.masked_conv(pl[s], geo, out=cts[s])
+        layer.unpack_output(cts[s], geo, ys[s])
+    t_all = time_us(whole, steps, n_sets, n_sets)
+    # dense convolution by cuDNN on channels-last tensors (the same memory layout as NHWC)
+    xc = [x.permute(0, 3, 1, 2) for x in xs]
+    wc = w.permute(3, 2, 0, 1).contiguous(memory_format=torch.channels_last).to(torch.bfloat16)
+    t_dense = time_us(lambda i: torch.nn.functional.conv2d(xc[i % n_sets], wc, padding=1), steps, n_sets, n_sets)
+    kept = res.tiles[0].kept_flops_per_row() * B * H * W
+    alg = layer.algorithmic_bytes(B, H, W)
+    peaks = load_peaks()
+    row = {"config": name, "B": B, "H": H, "W": W, "cin": cin, "cout": cout, "dtype": "bfloat16",
+           "pack_us": round(t_pack, 2), "gemm_us": round(t_gemm, 2), "unpack_us": round(t_unpack, 2),
+           "conv_us": round(t_all, 2), "cudnn_dense_us": round(t_dense, 2), "speedup_vs_cudnn_dense": round(t_dense / t_all, 3),
+           "kept_tflops": round(kept / t_all / 1e6, 1), "kept_tflops_gemm_only": round(kept / t_gemm / 1e6, 1),
+           "algorithmic_bytes": alg, "gbs_on_algorithmic_bytes": round(alg / t_all / 1e3, 1),
+           "padded_pixels_over_pixels": round(geo["m_padded"] / (B * H * W), 3),
+           "tensor_frac_of_measured_peak": round(kept / t_all / 1e6 / peaks["bf16_tflops"], 3),
+           "kept_fraction": round(kept / (2.0 * B * H * W * 9 * cin * cout), 4), "tiles": res.tiles[0].n_tiles, "note": note}
+    print(json.dumps(row), flush=True)
+    layer.close()
+    return row
+
+
 def run_sweep(args):
     """The benchmark configurations other than the headline, and the perf driver's own shapes."""
     import torch
@@ -753,6 +804,10 @@ def run_sweep(args):
                    tw_layer(75.0, torch.bfloat16, "tw_cols_rows", 10.0), args.iters,
                    "10 % of columns pruned, then 75 % of the rows of every tile; GEMM over an im2col-sized matrix",
                    he, True)
+        conv_case("vgg16_conv5_implicit_tw2_75", 64, 14, 14, 512, 512, "tw2", 75.0, None, args.iters,
+                  "the convolution itself: NHWC in, NHWC out, no im2col matrix")
+        conv_case("vgg16_conv5_implicit_c10_k75", 64, 14, 14, 512, 512, "tw_cols_rows", 75.0, 10.0, args.iters,
+                  "the convolution itself: NHWC in, NHWC out, no im2col matrix")
     elif want == "lstm":
         def tew(W):
             res = build_mask("tw1m", [W.abs()], 75.0, G, 1.5, want_residual=True)

@@ -127,6 +127,39 @@ typedef struct ts_epilogue {
 int ts_masked_gemm_ex(ts_layer_t* layer, int M, const void* At_dev, int64_t lda, void* Ct_dev,
                       int64_t ldc, const ts_epilogue_t* epilogue, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Convolution as an implicit masked GEMM.  The reference prunes a conv kernel [kh][kw][cin][cout] as the
+ * matrix [(kh*kw*cin)][cout] with row k = (r*kw + j)*cin + c (img2col_forward, Pruning/VGG/
+ * prune_algo.py:16-24) and leaves the convolution itself to TensorFlow; its GEMM driver has no conv
+ * path.  Here a stride-1, same-padded convolution runs on the masked GEMM without an im2col matrix:
+ * the NHWC input is stored once per horizontal tap as zero-padded channel-major planes, and the
+ * GEMM's row gather reads row k of the virtual im2col matrix as a run of plane (j, c) shifted by r
+ * padded image rows.  Pixels live in a padded index space: Hp = H + kh - 1 rows of Wp = W + kw - 1
+ * (rounded up to 8) columns per image, m = (b*Hp + y)*Wp + x; outputs at y >= H or x >= W are scratch.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Sizes of the padded pixel space (pure host function): *m_padded = B*Hp*Wp is the GEMM's batch
+ * dimension, *plane_ld the elements every input plane must hold (m_padded + (kh-1)*Wp). */
+int ts_conv_geometry(int B, int H, int W, int kh, int kw, int* Hp, int* Wp, int64_t* m_padded, int64_t* plane_ld);
+
+/* Declares the layer's weights to be a kh x kw conv kernel over cin channels (K = kh*kw*cin; odd
+ * kh, kw <= 9), row order as img2col_forward produces it. */
+int ts_layer_set_conv(ts_layer_t* layer, int cin, int kh, int kw);
+
+/* planes[j][c][m] = Xpad[b][y][x + j][c] for the NHWC 16-bit input x_nhwc_dev [B][H][W][C]:
+ * planes_dev is [kw][C][plane_ld] 16-bit, plane_ld >= the value ts_conv_geometry reports. */
+int ts_conv_pack_input(const void* x_nhwc_dev, int B, int H, int W, int C, int kh, int kw, void* planes_dev,
+                       int64_t plane_ld, void* stream);
+
+/* Ct[n][m] = act(alpha * conv(X, W .* mask)[m][n] + beta * Ct[n][m] + bias[n]) over the padded pixel
+ * space, for the layer's kept output channels n; Ct_dev is [N][ldc], ldc >= m_padded. */
+int ts_masked_conv(ts_layer_t* layer, int B, int H, int W, const void* planes_dev, int64_t plane_ld, void* Ct_dev,
+                   int64_t ldc, const ts_epilogue_t* epilogue, void* stream);
+
+/* y[b][yy][xx][n] = Ct[n][(b*Hp + yy)*Wp + xx]: the padded-space output back to NHWC [B][H][W][N]. */
+int ts_conv_unpack_output(const void* Ct_dev, int64_t ldc, int B, int H, int W, int kh, int kw, int N, void* y_nhwc_dev,
+                          void* stream);
+
 /* Same operation on the CUDA cores in fp32 (the twin of the reference's CUDA_MODE build,
  * basic_nn.cu:55-71,239-246).  Cross-check path, not tuned. */
 int ts_masked_gemm_simt(ts_layer_t* layer, int M, const void* At_dev, int64_t lda, void* Ct_dev,

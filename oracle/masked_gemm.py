@@ -109,3 +109,16 @@ def elementwise_violations(test, ref, rtol=1e-2, floor=1e-3):
     ref = np.asarray(ref, dtype=np.float64)
     rms = float(np.sqrt(np.mean(ref * ref))) if ref.size else 0.0
     return int((np.abs(test - ref) > rtol * np.abs(ref) + floor * rms).sum())
+
+
+def im2col_nhwc(x, kh, kw):
+    """The matrix a stride-1, same-padded kh x kw convolution multiplies with the kernel viewed as
+    [(kh*kw*cin), cout] (img2col_forward, Pruning/VGG/prune_algo.py:16-24: row (r*kw + j)*cin + c):
+    x is NHWC [B, H, W, C]; the result is [B*H*W, kh*kw*C] with pixels in (b, y, x) order."""
+    x = np.asarray(x)
+    B, H, W, C = x.shape
+    ph, pw = (kh - 1) // 2, (kw - 1) // 2
+    xp = np.zeros((B, H + kh - 1, W + kw - 1, C), dtype=x.dtype)
+    xp[:, ph:ph + H, pw:pw + W, :] = x
+    cols = [xp[:, r:r + H, j:j + W, :] for r in range(kh) for j in range(kw)]
+    return np.concatenate(cols, axis=3).reshape(B * H * W, kh * kw * C)

@@ -1,0 +1,77 @@
+"""Implicit-GEMM convolution (ConvTWLayer) against the CPU oracle: im2col + the masked product.
+
+The oracle builds the im2col matrix the reference's row order implies (img2col_forward,
+Pruning/VGG/prune_algo.py:16-24) and multiplies it with W .* mask; the library never builds it."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import masked_gemm as og
+from tilesparsity_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype, seed, relu_in=True):
+    from tilesparsity_b200 import ConvTWLayer, build_mask, masks
+    g = synth.rng(seed)
+    x = g.standard_normal((B, H, W, cin), dtype=np.float32)
+    if relu_in:
+        x = np.maximum(x, 0)
+    w = (g.standard_normal((kh, kw, cin, cout), dtype=np.float32) * np.float32(np.sqrt(2.0 / (kh * kw * cin)))).astype(np.float32)
+    wd = torch.from_numpy(w).cuda()
+    scores = masks.img2col_forward([wd])
+    res = build_mask(algo, scores, sparsity, 128, g1)
+    layer = ConvTWLayer(wd, res.tiles[0], dtype)
+    xd = torch.from_numpy(x).to(dtype).cuda()
+    y = layer.forward(xd)
+    layer.layer.check()
+    x16 = xd.float().cpu().numpy()
+    w16 = wd.to(dtype).float().cpu().numpy().reshape(-1, cout)
+    ref = og.masked_matmul_dense(og.im2col_nhwc(x16, kh, kw), w16, res.masks[0].cpu().numpy()).reshape(B, H, W, cout)
+    out = y.float().cpu().numpy()
+    assert og.max_rel_error(out, ref) <= 1e-2
+    assert og.elementwise_violations(out, ref, rtol=1e-2, floor=1e-3) == 0
+    dead = ~res.tiles[0].col_mask()
+    assert not out[..., dead].any()
+    return layer, xd, y
+
+
+@pytest.mark.parametrize("B,H,W,cin,cout,kh,kw,algo,sparsity,g1,dtype", [
+    (2, 5, 7, 16, 40, 3, 3, "tw1", 50.0, None, torch.float16),            # ragged everything, one narrow tile
+    (3, 14, 14, 64, 256, 3, 3, "tw2", 75.0, None, torch.bfloat16),         # pruned output channels
+    (1, 9, 20, 32, 130, 5, 3, "tw1", 60.0, None, torch.float16),           # non-square kernel, Wp > W + kw - 1
+    (4, 8, 8, 128, 128, 1, 1, "tw1", 75.0, None, torch.bfloat16),          # 1 x 1: a plain GEMM over pixels
+])
+def test_small_convolutions_match_the_oracle(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype):
+    layer, _, _ = _run(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype, seed=B + H + W + cin)
+    layer.close()
+
+
+@pytest.mark.parametrize("algo,sparsity,g1", [("tw2", 75.0, None), ("tw_cols_rows", 75.0, 10.0)])
+def test_vgg16_conv5_at_full_batch(algo, sparsity, g1):
+    """Batch 64, 14 x 14, 3 x 3, 512 -> 512 channels, bf16, activations after a ReLU."""
+    layer, xd, y = _run(64, 14, 14, 512, 512, 3, 3, algo, sparsity, g1, torch.bfloat16, seed=3001)
+    assert tuple(y.shape) == (64, 14, 14, 512)
+    # algorithmic bytes count the NHWC input once (12.85 MB), not an im2col matrix (115.6 MB)
+    assert layer.algorithmic_bytes(64, 14, 14) < 40e6
+    layer.close()
+
+
+def test_geometry_and_bad_arguments():
+    from tilesparsity_b200 import ConvTWLayer, TileSparseError, conv
+    geo = conv.geometry(64, 14, 14, 3, 3)
+    assert geo == {"Hp": 16, "Wp": 16, "m_padded": 64 * 256, "plane_ld": 64 * 256 + 32}
+    geo = conv.geometry(1, 224, 224, 3, 3)
+    assert geo["Wp"] == 232 and geo["Hp"] == 226
+    from tilesparsity_b200.tiles import tiles_from_lists
+    ts = tiles_from_lists(72, 128, 128, [np.arange(0, 72, 2, dtype=np.int32)])
+    w = torch.zeros((3, 3, 8, 128), device="cuda")
+    layer = ConvTWLayer(w, ts, torch.float16)
+    with pytest.raises(ValueError):
+        layer.pack_input(torch.zeros((1, 4, 4, 9), dtype=torch.float16, device="cuda"))
+    layer.close()
+    with pytest.raises(ValueError):
+        ConvTWLayer(torch.zeros((3, 3, 4, 128), device="cuda"), ts, torch.float16)
+    with pytest.raises(TileSparseError):
+        conv.geometry(0, 4, 4, 3, 3)

@@ -12,7 +12,7 @@ from . import tiles  # noqa: F401  (pure NumPy, always importable)
 _LAZY = {
     "TileSparseError": "_lib", "lib": "_lib",
     "TEWLayer": "layer", "TWLayer": "layer", "masked_linear": "layer", "masked_matmul": "layer",
-    "transpose16": "layer",
+    "transpose16": "layer", "ConvTWLayer": "conv",
     "MaskResult": "masks", "build_mask": "masks", "pruning_fun": "masks",
 }
 

@@ -69,6 +69,12 @@ SIGNATURES = {
     "ts_masked_gemm_host_wait": (C.c_int, [_vp, _vp]),
     "ts_layer_check": (C.c_int, [_vp, _vp]),
     "ts_layer_schedule_stats": (C.c_int, [_vp, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float), C.POINTER(C.c_int)]),
+    "ts_conv_geometry": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                   _i64p, _i64p]),
+    "ts_layer_set_conv": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int]),
+    "ts_conv_pack_input": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp]),
+    "ts_masked_conv": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.POINTER(Epilogue), _vp]),
+    "ts_conv_unpack_output": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     "ts_layer_set_unit_rows": (C.c_int, [_vp, C.c_int]),
     "ts_plan_schedule": (C.c_int, [C.c_int, _i32p, _i32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int),
                                    C.POINTER(C.c_int), C.POINTER(C.c_int), _i32p, C.c_int, C.POINTER(C.c_float)]),

@@ -10,6 +10,7 @@
 #include <mutex>
 #include <queue>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "ts_kernels.h"
@@ -445,7 +446,9 @@ struct ts_layer {
   bool packed = false;
   CUtensorMap tmap;
   int* d_status = nullptr;
-  std::map<int, Schedule> schedules;
+  // keyed by (batch size, activation row pitch, 1 for the convolution row map)
+  std::map<std::tuple<int, long long, int>, Schedule> schedules;
+  int conv_cin = 0, conv_kh = 0, conv_kw = 0;   // set by ts_layer_set_conv: K = kh * kw * cin
   void* d_at = nullptr;
   size_t at_bytes = 0;
   void* d_ct = nullptr;
@@ -483,8 +486,11 @@ void free_tiles(ts_layer* l) {
   l->ct_dirty = true;   // another tile set leaves other places of the staging output unwritten
 }
 
-int get_schedule(ts_layer* l, int M, Schedule** out) {
-  auto it = l->schedules.find(M);
+// Schedule for batch size M over activations whose kept rows are `ld` elements apart (a matrix), or
+// over a convolution's input planes of pitch `ld` with padded image width conv_wp (conv_wp > 0).
+int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, Schedule** out) {
+  const auto key = std::make_tuple(M, ld, conv_wp);
+  auto it = l->schedules.find(key);
   if (it != l->schedules.end()) {
     *out = &it->second;
     return TS_OK;
@@ -501,7 +507,21 @@ int get_schedule(ts_layer* l, int M, Schedule** out) {
   Schedule s;
   std::vector<ts::WorkItem> flat;
   std::vector<ts::BlockDesc> blocks;
-  build_schedule(l->h_tiles, l->K, M, l->forced_unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
+  ts::RowMap map;
+  memset(&map, 0, sizeof(map));
+  map.ld8 = ld / 8;
+  long long at_rows = l->K;
+  if (conv_wp > 0) {
+    map.conv_cin = l->conv_cin;
+    map.conv_kw = l->conv_kw;
+    map.conv_wp8 = conv_wp / 8;
+    at_rows = static_cast<long long>(l->conv_kw) * l->conv_cin;   // the planes that exist in memory
+  }
+  if (at_rows * (ld / 8) + static_cast<long long>(l->conv_kh) * (conv_wp / 8) >= (1LL << 31)) {
+    return fail(TS_ERR_UNSUPPORTED, "activations of %lld rows x %lld elements exceed the 32 GiB the block records address",
+                at_rows, ld);
+  }
+  build_schedule(l->h_tiles, at_rows, M, l->forced_unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
                  &s.unit_rows, &s.cta_cost, &blocks, &s.blk_stride);
   if (!flat.empty()) {
     TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkItem)));
@@ -511,10 +531,10 @@ int get_schedule(ts_layer* l, int M, Schedule** out) {
     TS_CUDA(cudaMemcpy(s.d_blocks, blocks.data(), blocks.size() * sizeof(ts::BlockDesc),
                        cudaMemcpyHostToDevice));
     TS_CUDA(cudaMalloc(&s.d_meta, blocks.size() * ts::kBlockMetaInts * sizeof(int)));
-    TS_CUDA(ts::expand_block_meta_launch(s.d_blocks, static_cast<long long>(blocks.size()), s.d_meta, nullptr));
+    TS_CUDA(ts::expand_block_meta_launch(s.d_blocks, static_cast<long long>(blocks.size()), s.d_meta, map, nullptr));
     TS_CUDA(cudaStreamSynchronize(nullptr));
   }
-  auto ins = l->schedules.emplace(M, s);
+  auto ins = l->schedules.emplace(key, s);
   *out = &ins.first->second;
   return TS_OK;
 }
@@ -746,8 +766,12 @@ int ts_layer_stats(const ts_layer_t* l, int64_t* kept_flops_per_row, int64_t* pa
   return TS_OK;
 }
 
-int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
-                      const ts_epilogue_t* epi, void* stream) {
+}  // extern "C"
+
+namespace {
+// The masked GEMM over a matrix At[K][lda] (conv_wp == 0) or over a convolution's input planes.
+int run_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
+                    const ts_epilogue_t* epi, void* stream, int conv_wp) {
   int rc = check_gemm_args(l, M, At, lda, Ct, ldc);
   if (rc != TS_OK) return rc;
   if (!epi) return fail(TS_ERR_INVALID, "epilogue is NULL");
@@ -769,7 +793,7 @@ int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* C
   }
   if (M == 0 || l->n_tiles == 0) return TS_OK;
   Schedule* s = nullptr;
-  rc = get_schedule(l, M, &s);
+  rc = get_schedule(l, M, lda, conv_wp, &s);
   if (rc != TS_OK) return rc;
   if (s->n_units == 0) return TS_OK;
   CUtensorMap tmap_c;
@@ -783,6 +807,81 @@ int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* C
                                  s->grid, s->d_meta, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
                                  early, static_cast<cudaStream_t>(stream)));
   l->wp_fresh = false;
+  return TS_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int ts_masked_gemm_ex(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct, int64_t ldc,
+                      const ts_epilogue_t* epi, void* stream) {
+  return run_masked_gemm(l, M, At, lda, Ct, ldc, epi, stream, 0);
+}
+
+int ts_layer_set_conv(ts_layer_t* l, int cin, int kh, int kw) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (cin <= 0 || kh <= 0 || kw <= 0 || (kh % 2) == 0 || (kw % 2) == 0 || kw > 9 || kh > 9) {
+    return fail(TS_ERR_INVALID, "cin=%d, kh=%d, kw=%d: the kernel must be odd-sized, at most 9 x 9", cin, kh, kw);
+  }
+  if (static_cast<long long>(cin) * kh * kw != l->K) {
+    return fail(TS_ERR_INVALID, "kh*kw*cin = %lld differs from the layer's K = %d", static_cast<long long>(cin) * kh * kw, l->K);
+  }
+  l->conv_cin = cin;
+  l->conv_kh = kh;
+  l->conv_kw = kw;
+  return TS_OK;
+}
+
+int ts_conv_geometry(int B, int H, int W, int kh, int kw, int* Hp, int* Wp, int64_t* m_padded, int64_t* plane_ld) {
+  if (B <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0) return fail(TS_ERR_INVALID, "non-positive size");
+  const int hp = H + kh - 1, wp = (W + kw - 1 + 7) / 8 * 8;
+  const int64_t m = static_cast<int64_t>(B) * hp * wp;
+  if (m > 0x7fffffff - 4096) return fail(TS_ERR_UNSUPPORTED, "%lld padded pixels exceed the batch dimension's range", (long long)m);
+  if (Hp) *Hp = hp;
+  if (Wp) *Wp = wp;
+  if (m_padded) *m_padded = m;
+  if (plane_ld) *plane_ld = m + static_cast<int64_t>(kh - 1) * wp;
+  return TS_OK;
+}
+
+int ts_conv_pack_input(const void* x_nhwc_dev, int B, int H, int W, int C, int kh, int kw, void* planes_dev,
+                       int64_t plane_ld, void* stream) {
+  int hp = 0, wp = 0;
+  int64_t m = 0, need = 0;
+  int rc = ts_conv_geometry(B, H, W, kh, kw, &hp, &wp, &m, &need);
+  if (rc != TS_OK) return rc;
+  if (C <= 0 || (kh % 2) == 0 || (kw % 2) == 0 || kw > 9 || kh > 9) return fail(TS_ERR_INVALID, "C=%d, kh=%d, kw=%d", C, kh, kw);
+  if (!x_nhwc_dev || !planes_dev) return fail(TS_ERR_INVALID, "NULL pointer");
+  if (plane_ld < need || (plane_ld % 8) != 0) {
+    return fail(TS_ERR_INVALID, "plane_ld=%lld must be a multiple of 8 and >= %lld", (long long)plane_ld, (long long)need);
+  }
+  if (B > 65535 || hp > 65535) return fail(TS_ERR_UNSUPPORTED, "more than 65535 images or padded rows");
+  TS_CUDA(ts::conv_pack_input_launch(x_nhwc_dev, B, H, W, C, kh, kw, hp, wp, planes_dev, plane_ld,
+                                     static_cast<cudaStream_t>(stream)));
+  return TS_OK;
+}
+
+int ts_masked_conv(ts_layer_t* l, int B, int H, int W, const void* planes_dev, int64_t plane_ld, void* Ct_dev,
+                   int64_t ldc, const ts_epilogue_t* epi, void* stream) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  if (l->conv_cin <= 0) return fail(TS_ERR_INVALID, "the layer has no convolution geometry (call ts_layer_set_conv)");
+  int hp = 0, wp = 0;
+  int64_t m = 0, need = 0;
+  int rc = ts_conv_geometry(B, H, W, l->conv_kh, l->conv_kw, &hp, &wp, &m, &need);
+  if (rc != TS_OK) return rc;
+  if (plane_ld < need) return fail(TS_ERR_INVALID, "plane_ld=%lld is smaller than %lld", (long long)plane_ld, (long long)need);
+  return run_masked_gemm(l, static_cast<int>(m), planes_dev, plane_ld, Ct_dev, ldc, epi, stream, wp);
+}
+
+int ts_conv_unpack_output(const void* Ct_dev, int64_t ldc, int B, int H, int W, int kh, int kw, int N, void* y_nhwc_dev,
+                          void* stream) {
+  int hp = 0, wp = 0;
+  int64_t m = 0;
+  int rc = ts_conv_geometry(B, H, W, kh, kw, &hp, &wp, &m, nullptr);
+  if (rc != TS_OK) return rc;
+  if (N <= 0 || !Ct_dev || !y_nhwc_dev || ldc < m) return fail(TS_ERR_INVALID, "bad argument");
+  if (B > 65535 || H > 65535) return fail(TS_ERR_UNSUPPORTED, "more than 65535 images or rows");
+  TS_CUDA(ts::conv_unpack_output_launch(Ct_dev, ldc, B, H, W, hp, wp, N, y_nhwc_dev, static_cast<cudaStream_t>(stream)));
   return TS_OK;
 }
 
@@ -926,7 +1025,7 @@ int ts_layer_schedule_stats(ts_layer_t* l, int M, int* n_ctas, float* cta_cost, 
   if (M <= 0) return fail(TS_ERR_INVALID, "M=%d must be positive", M);
   if (!l->d_tiles) return fail(TS_ERR_INVALID, "layer has no tiles");
   Schedule* s = nullptr;
-  int rc = get_schedule(l, M, &s);
+  int rc = get_schedule(l, M, M, 0, &s);
   if (rc != TS_OK) return rc;
   if (n_ctas) *n_ctas = s->grid;
   if (n_units) *n_units = s->n_units;
@@ -964,6 +1063,9 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
     return fail(TS_ERR_INVALID, "block_num=%d out of [0, 32] (MAX_BLOCK_NUM of the reference)", block_num);
   }
   if (dtype != TS_DTYPE_F16 && dtype != TS_DTYPE_BF16) return fail(TS_ERR_INVALID, "dtype must be f16 or bf16");
+  if (static_cast<long long>(K) * (M / 8) >= (1LL << 31)) {
+    return fail(TS_ERR_UNSUPPORTED, "A of %d x %d elements exceeds the 32 GiB the block records address", K, M);
+  }
   if (block_num == 0) return TS_OK;
   if (!A || !B || !C || !N_cal || !K_cal || !mask_n || !mask_k || !off_B || !off_C) {
     return fail(TS_ERR_INVALID, "NULL argument");
@@ -1052,7 +1154,10 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   }
   // The caller owns the offset lists and may have rewritten them since the schedule was cached:
   // they are resolved again on every call.
-  TS_CUDA(ts::expand_block_meta_launch(ws.d_blocks, ws.n_blocks, ws.d_meta, s));
+  ts::RowMap map;
+  memset(&map, 0, sizeof(map));
+  map.ld8 = M / 8;
+  TS_CUDA(ts::expand_block_meta_launch(ws.d_blocks, ws.n_blocks, ws.d_meta, map, s));
   const int rounds = ws.rounds, grid = ws.grid, blk_stride = ws.blk_stride, unit_rows = ws.unit_rows;
   ts::EpilogueArgs ep;
   memset(&ep, 0, sizeof(ep));

@@ -6,7 +6,9 @@
 // launch over a work list.  Data layout is the reference's (column-major everywhere,
 // basic_nn.cu:412-426):
 //
-//   At : activations, stored [K][lda] with the batch dimension M contiguous (column-major M x K)
+//   At : activations, stored [K][lda] with the batch dimension M contiguous (column-major M x K);
+//        the kernel only sees where each kept row starts (16-byte segment numbers in the block records),
+//        which is how a convolution's shifted input planes stand in for an im2col matrix
 //   Wp : packed weights, stored [rows][ldw] with K contiguous; tile t owns rows w_row0 .. +n_count,
 //        entry (j, i) = W[kept_k[i], kept_n[j]]   (gen_masked_stream_weight, basic_nn.cu:757-769)
 //   Ct : output, stored [N][ldc] with M contiguous; kept column j of a tile lands in row c_row(j)
@@ -355,7 +357,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
               kr = sub ? rr[e * 2 + 1] : rr[e * 2];
             }
             cp_async_16_full(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
-                             src_col + static_cast<long long>(kr) * lda);
+                             src_col + (static_cast<long long>(kr) << 3));
           }
         }
       } else if (lane_live) {
@@ -370,7 +372,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
           }
           const bool valid = (row < nv) && m_ok;
           cp_async_16(dst0 + (row >> 3) * kASbo + (row & 7) * 128 + ((c ^ (row & 7)) << 4),
-                      valid ? src_col + static_cast<long long>(kr) * lda : At, valid ? 16u : 0u);
+                      valid ? src_col + (static_cast<long long>(kr) << 3) : At, valid ? 16u : 0u);
         }
       }
       cp_async_arrive_noinc(bar);
@@ -555,10 +557,16 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 }
 
 // One record per K block of a schedule: {first batch row of the unit, meta word, 0, 0} followed by
-// the 64 rows of At the block gathers (0 past the block's last row): the kept row number itself,
-// or list position + offset for lists in the reference's relative form.
+// the start of the 64 rows the block gathers (0 past the block's last row), each as a count of
+// 16-byte segments from the activation base pointer.  For a matrix At[K][lda] kept row k starts at
+// segment k * lda / 8.  For a convolution the "matrix" is never materialised: kept row
+// k = (r * kw + j) * cin + c of the im2col matrix (Pruning/VGG/prune_algo.py:16-24 fixes that order)
+// is channel c of the copy of the padded input shifted by j pixels, read r image rows further down:
+// segment ((j * cin + c) * plane_ld + r * Wp) / 8.  The kept row number itself comes from the tile's
+// list, or list position + offset for lists in the reference's relative form.
 __global__ void __launch_bounds__(256)
-expand_block_meta_kernel(const BlockDesc* __restrict__ blocks, long long n_blocks, int* __restrict__ meta) {
+expand_block_meta_kernel(const BlockDesc* __restrict__ blocks, long long n_blocks, int* __restrict__ meta,
+                         const RowMap map) {
   const long long b = blockIdx.x * 4LL + (threadIdx.x >> 6);
   const int r = threadIdx.x & 63;
   if (b >= n_blocks) return;
@@ -567,6 +575,13 @@ expand_block_meta_kernel(const BlockDesc* __restrict__ blocks, long long n_block
   if (d.meta != kBlockEnd && r < static_cast<int>(d.meta & 0x7fu)) {
     v = __ldg(d.idx + r);
     if (d.meta & 0x80u) v += static_cast<int>(d.meta >> 10) + r;
+    if (map.conv_cin > 0) {
+      const int c = v % map.conv_cin, rj = v / map.conv_cin;
+      const int j = rj % map.conv_kw, rr = rj / map.conv_kw;
+      v = static_cast<int>((static_cast<long long>(j) * map.conv_cin + c) * map.ld8 + static_cast<long long>(rr) * map.conv_wp8);
+    } else {
+      v = static_cast<int>(static_cast<long long>(v) * map.ld8);
+    }
   }
   int* rec = meta + b * kMetaInts;
   rec[4 + r] = v;
@@ -624,9 +639,10 @@ cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap
   return cudaErrorInvalidValue;
 }
 
-cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, cudaStream_t stream) {
+cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, const RowMap& map,
+                                     cudaStream_t stream) {
   if (n_blocks <= 0) return cudaSuccess;
-  expand_block_meta_kernel<<<static_cast<unsigned>((n_blocks + 3) / 4), 256, 0, stream>>>(blocks, n_blocks, meta);
+  expand_block_meta_kernel<<<static_cast<unsigned>((n_blocks + 3) / 4), 256, 0, stream>>>(blocks, n_blocks, meta, map);
   return cudaGetLastError();
 }
 

@@ -92,8 +92,19 @@ struct alignas(16) BlockDesc {
 static_assert(sizeof(BlockDesc) == 16, "BlockDesc is copied as one 16-byte word");
 constexpr uint32_t kBlockEnd = 0xFFFFFFFFu;
 // The gather warps read a block as one resolved record of kBlockMetaInts ints: {m0, meta, 0, 0}
-// followed by the 64 rows of At the block gathers.
+// followed by where each of the block's 64 kept rows starts, in 16-byte segments from the base pointer.
 constexpr int kBlockMetaInts = 4 + 64;
+
+// How a kept row number becomes a segment number.  Matrix: row * ld8 (ld8 = row pitch / 8 elements).
+// Convolution (conv_cin > 0): row = (r * conv_kw + j) * conv_cin + c  ->  (j * conv_cin + c) * ld8 + r * conv_wp8,
+// with ld8 the pitch of one input plane and conv_wp8 the padded image width, both in 8-element units.
+struct RowMap {
+  long long ld8;
+  int conv_cin;
+  int conv_kw;
+  int conv_wp8;
+  int pad_;
+};
 
 // ---------------------------------------------------------------------------------------------
 // Generic helpers

@@ -26,8 +26,10 @@ cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap
                                const EpilogueArgs& ep, int* status, bool early_start, cudaStream_t stream);
 
 // meta[b*kBlockMetaInts ...] = record of block b, for all n_blocks (= grid*blk_stride) descriptors:
-// resolves the kept-row lists, relative or absolute, into row numbers of At.
-cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, cudaStream_t stream);
+// resolves the kept-row lists, relative or absolute, into the 16-byte segment at which each kept row
+// of the activations starts (`map`: a matrix with its row pitch, or a convolution's input planes).
+cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, const RowMap& map,
+                                     cudaStream_t stream);
 
 // CUDA-core twin of the masked GEMM with the same operands (masked_gemm_simt.cu).
 cudaError_t masked_gemm_simt_launch(int dtype, const TileDesc* tiles, int n_tiles, const void* Wp,
@@ -45,6 +47,14 @@ cudaError_t pack_weights_launch(int w_dtype, int out_dtype, const void* W, long 
 cudaError_t residual_spmm_launch(int dtype, const int* col_ptr, const int* row_idx, const void* val,
                                  const uint8_t* col_written, const void* At, long long lda, void* Ct,
                                  long long ldc, int M, int N, float alpha, cudaStream_t stream);
+
+// Implicit-GEMM convolution (conv.cu): NHWC input -> kw shifted, zero-padded, channel-major planes
+// [kw][C][plane_ld] (16-bit), and the GEMM's padded-pixel output Ct[N][ldc] -> NHWC [B][H][W][N].
+// Hp = H + kh - 1, Wp = (W + kw - 1) rounded up to 8.
+cudaError_t conv_pack_input_launch(const void* x_nhwc, int B, int H, int W, int C, int kh, int kw, int Hp, int Wp,
+                                   void* planes, long long plane_ld, cudaStream_t stream);
+cudaError_t conv_unpack_output_launch(const void* ct, long long ldc, int B, int H, int W, int Hp, int Wp, int N,
+                                      void* y_nhwc, cudaStream_t stream);
 
 // out[c][r] = in[r][c] for 16-bit elements (pack.cu).
 cudaError_t transpose16_launch(const void* in, long long ld_in, void* out, long long ld_out,
