@@ -147,7 +147,8 @@ int ts_conv_geometry(int B, int H, int W, int kh, int kw, int* Hp, int* Wp, int6
 int ts_layer_set_conv(ts_layer_t* layer, int cin, int kh, int kw);
 
 /* planes[j][c][m] = Xpad[b][y][x + j][c] for the NHWC 16-bit input x_nhwc_dev [B][H][W][C]:
- * planes_dev is [kw][C][plane_ld] 16-bit, plane_ld >= the value ts_conv_geometry reports. */
+ * planes_dev is [kw][C][plane_ld] 16-bit, plane_ld >= the value ts_conv_geometry reports.  C must be a
+ * multiple of 8 and both pointers 16-byte aligned. */
 int ts_conv_pack_input(const void* x_nhwc_dev, int B, int H, int W, int C, int kh, int kw, void* planes_dev,
                        int64_t plane_ld, void* stream);
 
@@ -156,7 +157,8 @@ int ts_conv_pack_input(const void* x_nhwc_dev, int B, int H, int W, int C, int k
 int ts_masked_conv(ts_layer_t* layer, int B, int H, int W, const void* planes_dev, int64_t plane_ld, void* Ct_dev,
                    int64_t ldc, const ts_epilogue_t* epilogue, void* stream);
 
-/* y[b][yy][xx][n] = Ct[n][(b*Hp + yy)*Wp + xx]: the padded-space output back to NHWC [B][H][W][N]. */
+/* y[b][yy][xx][n] = Ct[n][(b*Hp + yy)*Wp + xx]: the padded-space output back to NHWC [B][H][W][N].
+ * N and ldc must be multiples of 8 and both pointers 16-byte aligned. */
 int ts_conv_unpack_output(const void* Ct_dev, int64_t ldc, int B, int H, int W, int kh, int kw, int N, void* y_nhwc_dev,
                           void* stream);
 

@@ -40,7 +40,7 @@ def _run(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype, seed, relu_in=Tr
 @pytest.mark.parametrize("B,H,W,cin,cout,kh,kw,algo,sparsity,g1,dtype", [
     (2, 5, 7, 16, 40, 3, 3, "tw1", 50.0, None, torch.float16),            # ragged everything, one narrow tile
     (3, 14, 14, 64, 256, 3, 3, "tw2", 75.0, None, torch.bfloat16),         # pruned output channels
-    (1, 9, 20, 32, 130, 5, 3, "tw1", 60.0, None, torch.float16),           # non-square kernel, Wp > W + kw - 1
+    (1, 9, 20, 32, 136, 5, 3, "tw1", 60.0, None, torch.float16),           # non-square kernel, Wp > W + kw - 1
     (4, 8, 8, 128, 128, 1, 1, "tw1", 75.0, None, torch.bfloat16),          # 1 x 1: a plain GEMM over pixels
 ])
 def test_small_convolutions_match_the_oracle(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype):

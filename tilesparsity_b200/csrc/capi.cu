@@ -850,8 +850,12 @@ int ts_conv_pack_input(const void* x_nhwc_dev, int B, int H, int W, int C, int k
   int64_t m = 0, need = 0;
   int rc = ts_conv_geometry(B, H, W, kh, kw, &hp, &wp, &m, &need);
   if (rc != TS_OK) return rc;
-  if (C <= 0 || (kh % 2) == 0 || (kw % 2) == 0 || kw > 9 || kh > 9) return fail(TS_ERR_INVALID, "C=%d, kh=%d, kw=%d", C, kh, kw);
-  if (!x_nhwc_dev || !planes_dev) return fail(TS_ERR_INVALID, "NULL pointer");
+  if (C <= 0 || (C % 8) != 0 || (kh % 2) == 0 || (kw % 2) == 0 || kw > 9 || kh > 9) {
+    return fail(TS_ERR_INVALID, "C=%d must be a multiple of 8; kh=%d, kw=%d must be odd and at most 9", C, kh, kw);
+  }
+  if (!x_nhwc_dev || !planes_dev || ((reinterpret_cast<uintptr_t>(x_nhwc_dev) | reinterpret_cast<uintptr_t>(planes_dev)) & 15u)) {
+    return fail(TS_ERR_INVALID, "the input and the planes must be non-NULL and 16-byte aligned");
+  }
   if (plane_ld < need || (plane_ld % 8) != 0) {
     return fail(TS_ERR_INVALID, "plane_ld=%lld must be a multiple of 8 and >= %lld", (long long)plane_ld, (long long)need);
   }
@@ -879,7 +883,10 @@ int ts_conv_unpack_output(const void* Ct_dev, int64_t ldc, int B, int H, int W, 
   int64_t m = 0;
   int rc = ts_conv_geometry(B, H, W, kh, kw, &hp, &wp, &m, nullptr);
   if (rc != TS_OK) return rc;
-  if (N <= 0 || !Ct_dev || !y_nhwc_dev || ldc < m) return fail(TS_ERR_INVALID, "bad argument");
+  if (N <= 0 || (N % 8) != 0 || !Ct_dev || !y_nhwc_dev || ldc < m || (ldc % 8) != 0 ||
+      ((reinterpret_cast<uintptr_t>(Ct_dev) | reinterpret_cast<uintptr_t>(y_nhwc_dev)) & 15u)) {
+    return fail(TS_ERR_INVALID, "N and ldc must be multiples of 8 (ldc >= the padded pixel count), pointers 16-byte aligned");
+  }
   if (B > 65535 || H > 65535) return fail(TS_ERR_UNSUPPORTED, "more than 65535 images or rows");
   TS_CUDA(ts::conv_unpack_output_launch(Ct_dev, ldc, B, H, W, hp, wp, N, y_nhwc_dev, static_cast<cudaStream_t>(stream)));
   return TS_OK;

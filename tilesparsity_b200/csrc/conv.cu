@@ -22,60 +22,91 @@ namespace {
 
 constexpr int kPackCh = 64;    // channels per block
 constexpr int kPackPx = 64;    // padded pixels of one image row per pass
+constexpr int kPackRows = 4;   // padded image rows per pass
+constexpr int kTilePitch = kPackPx + 10;   // halves per tile row: 37 words, odd, so a column is conflict-free
 
-// grid (Hp, B, ceil(C / 64)), block 256.  One block: one padded image row of one image, 64 channels.
+// grid (ceil(Hp / 4), B, ceil(C / 64)), block 256.  One pass: 4 padded image rows x 64 columns of one
+// image, 64 channels.  The input is read with 16-byte loads along the channels, transposed through
+// shared memory, and every plane row leaves with 16-byte stores along the pixels (Wp, the row
+// starts and plane_ld are multiples of 8 elements).  Needs C % 8 == 0 and 16-byte aligned pointers.
 __global__ void __launch_bounds__(256)
 conv_pack_input_kernel(const uint16_t* __restrict__ x, int B, int H, int W, int C, int kh, int kw, int Hp, int Wp,
                        uint16_t* __restrict__ planes, long long plane_ld) {
-  __shared__ uint16_t tile[kPackPx + 8][kPackCh + 2];   // [padded column][channel]
-  const int yp = blockIdx.x, b = blockIdx.y, c0 = blockIdx.z * kPackCh;
-  const int y = yp - (kh - 1) / 2, pw = (kw - 1) / 2;
-  const bool row_in = y >= 0 && y < H;
-  const long long out_row = (static_cast<long long>(b) * Hp + yp) * Wp;
+  __shared__ __align__(16) uint16_t tile[kPackRows][kPackCh][kTilePitch];   // [row][channel][padded column]
+  const int yp0 = blockIdx.x * kPackRows, b = blockIdx.y, c0 = blockIdx.z * kPackCh;
+  const int ph = (kh - 1) / 2, pw = (kw - 1) / 2;
+  const int span = kPackPx + kw - 1;
   for (int x0 = 0; x0 < Wp; x0 += kPackPx) {
-    // padded columns x0 .. x0 + 64 + kw - 1 of this row, all 64 channels (channels fastest in x)
-    const int span = kPackPx + kw - 1;
     __syncthreads();
-    for (int i = threadIdx.x; i < span * kPackCh; i += blockDim.x) {
-      const int cc = i % kPackCh, xx = i / kPackCh;
-      const int xs = x0 + xx - pw;                     // source column in the image
-      uint16_t v = 0;
-      if (row_in && xs >= 0 && xs < W && c0 + cc < C) {
-        v = __ldg(x + ((static_cast<long long>(b) * H + y) * W + xs) * C + c0 + cc);
+    // loads: (row, padded column, 8 channels) per thread and step
+    for (int i = threadIdx.x; i < kPackRows * span * (kPackCh / 8); i += blockDim.x) {
+      const int c8 = i % (kPackCh / 8), xx = (i / (kPackCh / 8)) % span, rr = i / ((kPackCh / 8) * span);
+      const int y = yp0 + rr - ph, xs = x0 + xx - pw;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (y >= 0 && y < H && xs >= 0 && xs < W && c0 + c8 * 8 < C) {
+        v = __ldg(reinterpret_cast<const uint4*>(x + ((static_cast<long long>(b) * H + y) * W + xs) * C + c0 + c8 * 8));
       }
-      tile[xx][cc] = v;
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        tile[rr][c8 * 8 + 2 * e][xx] = static_cast<uint16_t>(w[e] & 0xffffu);
+        tile[rr][c8 * 8 + 2 * e + 1][xx] = static_cast<uint16_t>(w[e] >> 16);
+      }
     }
     __syncthreads();
-    const int n_px = min(kPackPx, Wp - x0);
-    for (int i = threadIdx.x; i < kw * kPackCh * kPackPx; i += blockDim.x) {
-      const int px = i % kPackPx, cc = (i / kPackPx) % kPackCh, j = i / (kPackPx * kPackCh);
-      if (px < n_px && c0 + cc < C) {
-        planes[(static_cast<long long>(j) * C + c0 + cc) * plane_ld + out_row + x0 + px] = tile[px + j][cc];
-      }
+    const int n_px8 = (min(kPackPx, Wp - x0) + 7) / 8;
+    for (int i = threadIdx.x; i < kPackRows * kw * kPackCh * n_px8; i += blockDim.x) {
+      const int p8 = i % n_px8, cc = (i / n_px8) % kPackCh, j = (i / (n_px8 * kPackCh)) % kw;
+      const int rr = i / (n_px8 * kPackCh * kw);
+      const int yp = yp0 + rr;
+      if (yp >= Hp || c0 + cc >= C) continue;
+      const uint16_t* src = &tile[rr][cc][p8 * 8 + j];
+      uint4 o;
+      o.x = src[0] | (static_cast<uint32_t>(src[1]) << 16);
+      o.y = src[2] | (static_cast<uint32_t>(src[3]) << 16);
+      o.z = src[4] | (static_cast<uint32_t>(src[5]) << 16);
+      o.w = src[6] | (static_cast<uint32_t>(src[7]) << 16);
+      const long long off = (static_cast<long long>(j) * C + c0 + cc) * plane_ld +
+                            (static_cast<long long>(b) * Hp + yp) * Wp + x0 + p8 * 8;
+      *reinterpret_cast<uint4*>(planes + off) = o;
     }
   }
 }
 
-// y[b][yy][xx][n] = Ct[n][b*Hp*Wp + yy*Wp + xx] for yy < H, xx < W.  grid (H, B, ceil(N / 64)), block 256.
+// y[b][yy][xx][n] = Ct[n][b*Hp*Wp + yy*Wp + xx] for yy < H, xx < W.  grid (ceil(H / 4), B, ceil(N / 64)),
+// block 256: 16-byte loads along the pixels, 16-byte stores along the channels.  Needs N % 8 == 0,
+// ldc % 8 == 0 and 16-byte aligned pointers.
 __global__ void __launch_bounds__(256)
 conv_unpack_output_kernel(const uint16_t* __restrict__ ct, long long ldc, int B, int H, int W, int Hp, int Wp, int N,
                           uint16_t* __restrict__ y) {
-  __shared__ uint16_t tile[kPackCh][kPackPx + 2];       // [output channel][column]
-  const int yy = blockIdx.x, b = blockIdx.y, n0 = blockIdx.z * kPackCh;
-  const long long in_row = (static_cast<long long>(b) * Hp + yy) * Wp;
+  __shared__ __align__(16) uint16_t tile[kPackRows][kPackCh][kTilePitch];   // [row][output channel][column]
+  const int y0 = blockIdx.x * kPackRows, b = blockIdx.y, n0 = blockIdx.z * kPackCh;
   for (int x0 = 0; x0 < W; x0 += kPackPx) {
     const int n_px = min(kPackPx, W - x0);
+    const int n_px8 = (n_px + 7) / 8;      // Wp is a multiple of 8, so whole groups stay inside the padded row
     __syncthreads();
-    for (int i = threadIdx.x; i < kPackCh * kPackPx; i += blockDim.x) {
-      const int px = i % kPackPx, nn = i / kPackPx;
-      if (px < n_px && n0 + nn < N) tile[nn][px] = __ldg(ct + static_cast<long long>(n0 + nn) * ldc + in_row + x0 + px);
+    for (int i = threadIdx.x; i < kPackRows * kPackCh * n_px8; i += blockDim.x) {
+      const int p8 = i % n_px8, nn = (i / n_px8) % kPackCh, rr = i / (n_px8 * kPackCh);
+      if (y0 + rr >= H || n0 + nn >= N) continue;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(
+          ct + static_cast<long long>(n0 + nn) * ldc + (static_cast<long long>(b) * Hp + y0 + rr) * Wp + x0 + p8 * 8));
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[rr][nn][p8 * 8]);   // 4-byte aligned (odd word pitch)
+      dst[0] = v.x;
+      dst[1] = v.y;
+      dst[2] = v.z;
+      dst[3] = v.w;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < kPackCh * kPackPx; i += blockDim.x) {
-      const int nn = i % kPackCh, px = i / kPackCh;
-      if (px < n_px && n0 + nn < N) {
-        y[((static_cast<long long>(b) * H + yy) * W + x0 + px) * N + n0 + nn] = tile[nn][px];
+    for (int i = threadIdx.x; i < kPackRows * n_px * (kPackCh / 8); i += blockDim.x) {
+      const int n8 = i % (kPackCh / 8), px = (i / (kPackCh / 8)) % n_px, rr = i / ((kPackCh / 8) * n_px);
+      if (y0 + rr >= H || n0 + n8 * 8 >= N) continue;
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        w[e] = tile[rr][n8 * 8 + 2 * e][px] | (static_cast<uint32_t>(tile[rr][n8 * 8 + 2 * e + 1][px]) << 16);
       }
+      *reinterpret_cast<uint4*>(y + ((static_cast<long long>(b) * H + y0 + rr) * W + x0 + px) * N + n0 + n8 * 8) =
+          make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -92,7 +123,7 @@ cudaError_t conv_pack_input_launch(const void* x_nhwc, int B, int H, int W, int 
                                       static_cast<size_t>(kw) * C, stream);
     if (e != cudaSuccess) return e;
   }
-  dim3 grid(Hp, B, (C + kPackCh - 1) / kPackCh);
+  dim3 grid((Hp + kPackRows - 1) / kPackRows, B, (C + kPackCh - 1) / kPackCh);
   conv_pack_input_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x_nhwc), B, H, W, C, kh, kw, Hp, Wp,
                                                    static_cast<uint16_t*>(planes), plane_ld);
   return cudaGetLastError();
@@ -101,7 +132,7 @@ cudaError_t conv_pack_input_launch(const void* x_nhwc, int B, int H, int W, int 
 cudaError_t conv_unpack_output_launch(const void* ct, long long ldc, int B, int H, int W, int Hp, int Wp, int N,
                                       void* y_nhwc, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || W <= 0 || N <= 0) return cudaSuccess;
-  dim3 grid(H, B, (N + kPackCh - 1) / kPackCh);
+  dim3 grid((H + kPackRows - 1) / kPackRows, B, (N + kPackCh - 1) / kPackCh);
   conv_unpack_output_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, B, H, W, Hp, Wp, N,
                                                       static_cast<uint16_t*>(y_nhwc));
   return cudaGetLastError();
