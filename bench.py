@@ -396,8 +396,9 @@ def run_ours(args):
            "h2d_bytes_per_step": int(world * sum(h.numel() * 2 for h in hA)),
            "d2h_bytes_per_step": int(world * sum(h.numel() * 2 for h in hC)),
            "ms_per_step": ms_e2e, "n_gpus_timed": world,
-           "what": "ts_masked_gemm_host_async per GEMM (pinned host buffers, 4 column blocks each, copies of "
-                   "different GEMMs overlap), one wait per step; every rank moves its own batch, max over ranks"}
+           "what": "ts_masked_gemm_host_async per GEMM (pinned host buffers, contiguous copies; the copy-out of one "
+                   "GEMM overlaps the copy-in of the next), one wait per step; every rank moves its own batch, "
+                   "max over ranks"}
     if rank == 0:
         from oracle import masked_gemm as og
         ref = og.masked_matmul_compacted(hA[1].float().numpy(), work[1]["W16"].float().cpu().numpy(), work[1]["layer"].tiles)

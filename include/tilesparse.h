@@ -177,9 +177,9 @@ int ts_masked_gemm_host(ts_layer_t* layer, int M, const void* At_host, void* Ct_
                         float beta, void* stream);
 
 /* The same in two steps, for callers that keep several of these in flight.  _async queues the work:
- * the batch moves in up to four column blocks through copy-in, GEMM and copy-out on streams of the
- * layer's own (both directions of the link and the kernel overlap), ordered after what `stream` holds
- * at the call.  _wait makes `stream` wait (on the device, not the host) for the arrival of the last
+ * one contiguous copy in, the GEMM and one contiguous copy out on three streams of the layer's own,
+ * ordered after what `stream` holds at the call (calls on different layers overlap: one call's
+ * copy-out runs under the next call's copy-in, so both directions of the link stay busy).  _wait makes `stream` wait (on the device, not the host) for the arrival of the last
  * block of the layer's latest call; Ct_host is valid once the caller has then synchronised `stream`.
  * Calls on different layers overlap with each other; calls on one layer run one after the other.
  * No counterpart in the reference (its driver copies, computes and copies back in sequence,

@@ -143,7 +143,7 @@ def test_host_buffer_entry_point_and_row_major_op():
 
 
 def test_host_buffer_pipeline_blocks_beta_and_async():
-    """Four column blocks (M = 2048 + a ragged tail), beta != 0 through the host path, zeros in the
+    """A batch with a ragged tail (M = 2048 + 72), beta != 0 through the host path, zeros in the
     columns no tile keeps after a beta pass, and the asynchronous variant on two layers at once."""
     M = 2048 + 72
     layer, At, A16, W16 = _case(384, 512, M, 96, torch.float16, 33)

@@ -221,7 +221,7 @@ class TWLayer:
 
     def masked_gemm_host(self, At_host: torch.Tensor, Ct_host: torch.Tensor, alpha: float = 1.0,
                          beta: float = 0.0, wait: bool = True) -> torch.Tensor:
-        """Host-buffer variant: H2D copy, GEMM, D2H copy in overlapping column blocks (one C-ABI call).
+        """Host-buffer variant: contiguous H2D copy, GEMM, contiguous D2H copy (one C-ABI call).
         With wait=False the call returns once everything is queued; `host_wait()` then orders the
         current stream after the arrival of the output, and Ct_host is valid once that stream has
         been synchronised."""
