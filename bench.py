@@ -560,13 +560,20 @@ def sharded_outputs_match(n: int, device, rank: int, world: int) -> dict:
     for scale in (1.0, 0.5):
         out = shard.masked_gemm_allgather(At * scale, buf, handle)
         ok_fused = ok_fused and torch.equal(shard.assemble(out), full.masked_gemm(At * scale))
+    has_mc = shard.has_multicast(handle)
+    ok_mc = True
+    if has_mc:
+        for scale in (2.0, 1.0):
+            out = shard.masked_gemm_allgather(At * scale, buf, handle, multicast=True)
+            ok_mc = ok_mc and torch.equal(shard.assemble(out), full.masked_gemm(At * scale))
     torch.cuda.synchronize()
-    flags = torch.tensor([int(ok_nccl), int(ok_fused)], device=device)
+    flags = torch.tensor([int(ok_nccl), int(ok_fused), int(ok_mc), int(has_mc)], device=device)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     full.close()
     shard.close()
     del buf, handle
-    return {"nccl": bool(flags[0].item()), "fused": bool(flags[1].item()), "size": n}
+    return {"nccl": bool(flags[0].item()), "fused": bool(flags[1].item()),
+            "fused_multicast": bool(flags[2].item()) if flags[3].item() else None, "size": n}
 
 
 def tile_sharded_block(args, device, rank: int, world: int, n: int = 16384, steps: int = 20):
@@ -597,8 +604,8 @@ def tile_sharded_block(args, device, rank: int, world: int, n: int = 16384, step
     def run(mode):
         def step(i):
             s = i % n_sets
-            if mode == "fused":
-                shard.masked_gemm_allgather(At[s], buf, handle)
+            if mode in ("fused", "fused_mc"):
+                shard.masked_gemm_allgather(At[s], buf, handle, multicast=(mode == "fused_mc"))
                 return
             shard.masked_gemm(At[s], out=Ct[s])
             if mode == "nccl":
@@ -607,6 +614,7 @@ def tile_sharded_block(args, device, rank: int, world: int, n: int = 16384, step
         return float(np.median(ms)) / steps
 
     t_none, t_fused, t_nccl = run("none"), run("fused"), run("nccl")
+    t_mc = run("fused_mc") if (check["fused_multicast"] is not None) else None
     shard.layer.check()
     kept = ts.kept_flops_per_row() * n
     out_bytes = int(sum(shard.plan.n_local)) * n * 2
@@ -622,8 +630,12 @@ def tile_sharded_block(args, device, rank: int, world: int, n: int = 16384, step
                "gather_inbound_bytes_per_gpu": int(inbound),
                "gather_floor_ms_at_770GBs": inbound / 770e9 * 1e3,
                "fused_frac_of_nvlink_floor": (inbound / 770e9 * 1e3) / t_fused,
+               "fused_multicast_ms": t_mc,
+               "efficiency_fused_multicast": (one_gpu_ms / (world * t_mc)) if t_mc else None,
+               "fused_multicast_frac_of_nvlink_floor": ((inbound / 770e9 * 1e3) / t_mc) if t_mc else None,
                "binding": "with the gather: inbound bytes per GPU over NVLink; without: tensor cores / L2",
-               "verified": bool(check["nccl"] and check["fused"]), "verification": check,
+               "verified": bool(check["nccl"] and check["fused"] and check["fused_multicast"] is not False),
+               "verification": check,
                "l2": f"activations rotate over {n_sets} buffers of {n * n * 2 / 2**20:.0f} MiB"}
     shard.close()
     return res

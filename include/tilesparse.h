@@ -122,6 +122,10 @@ typedef struct ts_epilogue {
   int activation;
   int n_peers;
   void* peer_ct[7];
+  void* multicast_ct; /* NULL, or the NVSwitch multicast address that maps Ct on every GPU of the group
+                         (this one included): each kept row is then written once with multimem.st and
+                         delivered to all copies by the switch; Ct_dev and peer_ct are not written
+                         (beta must be 0).  Stores only: nothing is ever loaded through the mapping. */
 } ts_epilogue_t;
 
 int ts_masked_gemm_ex(ts_layer_t* layer, int M, const void* At_dev, int64_t lda, void* Ct_dev,

@@ -39,8 +39,14 @@ def _worker(rank, world, port, q):
             out = shard.masked_gemm_allgather(At * scale, buf, handle)
             want = full.masked_gemm(At * scale)
             ok_fused = ok_fused and torch.equal(shard.assemble(out), want)
+        # the same through the NVSwitch multicast mapping of the buffer, where the box has one
+        ok_mc = True
+        if shard.has_multicast(handle):
+            for scale in (3.0, 1.0):
+                out = shard.masked_gemm_allgather(At * scale, buf, handle, multicast=True)
+                ok_mc = ok_mc and torch.equal(shard.assemble(out), full.masked_gemm(At * scale))
         torch.cuda.synchronize()
-        q.put((rank, bool(ok_nccl), bool(ok_fused)))
+        q.put((rank, bool(ok_nccl), bool(ok_fused), bool(ok_mc)))
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -64,3 +70,4 @@ def test_sharded_layer_nccl_and_fused_allgather():
         assert p.exitcode == 0
     assert all(r[1] for r in res), "NCCL all-gather path differs from the unsharded layer"
     assert all(r[2] for r in res), "fused GEMM + all-gather differs from the unsharded layer"
+    assert all(r[3] for r in res), "fused GEMM + multicast all-gather differs from the unsharded layer"

@@ -42,7 +42,7 @@ lib = _load()
 class Epilogue(C.Structure):
     """ts_epilogue_t"""
     _fields_ = [("alpha", C.c_float), ("beta", C.c_float), ("bias_dev", C.c_void_p), ("activation", C.c_int),
-                ("n_peers", C.c_int), ("peer_ct", C.c_void_p * 7)]
+                ("n_peers", C.c_int), ("peer_ct", C.c_void_p * 7), ("multicast_ct", C.c_void_p)]
 
 
 ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "gelu": 2}

@@ -791,6 +791,10 @@ int run_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct,
       return fail(TS_ERR_INVALID, "peer buffer %d is NULL or not 16-byte aligned", p);
     }
   }
+  ep.multicast = static_cast<uint16_t*>(epi->multicast_ct);
+  if (ep.multicast && ((reinterpret_cast<uintptr_t>(ep.multicast) & 15u) || epi->beta != 0.0f)) {
+    return fail(TS_ERR_INVALID, "the multicast address must be 16-byte aligned and needs beta == 0");
+  }
   if (M == 0 || l->n_tiles == 0) return TS_OK;
   Schedule* s = nullptr;
   rc = get_schedule(l, M, lda, conv_wp, &s);

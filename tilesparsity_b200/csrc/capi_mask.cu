@@ -363,7 +363,7 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
   } else if (sel == 0) {
     TSM_OK(percentile_to_device(norms, total, q, wide, false, sc, 1, s));
     TSM_CUDA(ts::threshold_dev_launch(norms, total, sc.thr + 1, keep, s));
-    if (thr_out) TSM_OK(read_thresholds(sc, 1, thr_out, s));
+    // the threshold and the select's error flag are read back with the lists, further down
   } else {
     for (int l = 0; l < nl; ++l) {
       const int nt = static_cast<int>(bounds[l].size()) - 1;
@@ -391,7 +391,9 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
     }
   }
 
-  // kept-row lists: one segment per (layer, tile)
+  // kept-row lists: one segment per (layer, tile).  Counts, their prefix sums and the compaction all
+  // stay on the device; the dense masks are enqueued behind them; one blocking read-back at the end
+  // brings the thresholds, the select's error flag, the offsets and the lists.
   std::vector<long long> seg(total_tiles + 1, 0);
   for (int l = 0; l < nl; ++l) {
     const int nt = tile_off[l + 1] - tile_off[l];
@@ -400,25 +402,55 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
   long long* seg_dev = nullptr;
   int* counts_dev = nullptr;
   int* optr_dev = nullptr;
+  int* list_dev = nullptr;
   TSM_OK(arena.alloc(&seg_dev, seg.size()));
   TSM_OK(arena.alloc(&counts_dev, total_tiles));
   TSM_OK(arena.alloc(&optr_dev, total_tiles + 1));
+  TSM_OK(arena.alloc(&list_dev, total));      // room for every tile-row: the kept ones are a subset
   TSM_CUDA(cudaMemcpyAsync(seg_dev, seg.data(), seg.size() * sizeof(long long), cudaMemcpyHostToDevice, s));
   TSM_CUDA(ts::segment_count_launch(keep, seg_dev, total_tiles, counts_dev, s));
-  std::vector<int> counts(total_tiles);
-  TSM_CUDA(cudaMemcpyAsync(counts.data(), counts_dev, total_tiles * sizeof(int), cudaMemcpyDeviceToHost, s));
-  TSM_CUDA(cudaStreamSynchronize(s));
-  std::vector<int> optr(total_tiles + 1, 0);
-  for (int t = 0; t < total_tiles; ++t) optr[t + 1] = optr[t] + counts[t];
-  int* list_dev = nullptr;
-  TSM_OK(arena.alloc(&list_dev, optr[total_tiles]));
-  TSM_CUDA(cudaMemcpyAsync(optr_dev, optr.data(), optr.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+  TSM_CUDA(ts::segment_offsets_launch(counts_dev, total_tiles, optr_dev, s));
   TSM_CUDA(ts::segment_compact_launch(keep, seg_dev, total_tiles, optr_dev, list_dev, s));
-  std::vector<int> list(optr[total_tiles]);
-  if (!list.empty()) {
-    TSM_CUDA(cudaMemcpyAsync(list.data(), list_dev, list.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
+  std::vector<std::vector<int>> tile_of_col(nl);
+  for (int l = 0; l < nl; ++l) {
+    if (!L[l].mask) continue;
+    const int nt = tile_off[l + 1] - tile_off[l];
+    tile_of_col[l].resize(L[l].N);
+    for (int t = 0; t < nt; ++t) {
+      for (int c = bounds[l][t]; c < bounds[l][t + 1]; ++c) tile_of_col[l][c] = t;
+    }
+    int* toc_dev = nullptr;
+    TSM_OK(arena.alloc(&toc_dev, tile_of_col[l].size()));
+    TSM_CUDA(cudaMemcpyAsync(toc_dev, tile_of_col[l].data(), tile_of_col[l].size() * sizeof(int),
+                             cudaMemcpyHostToDevice, s));
+    TSM_CUDA(ts::dense_mask_launch(keep + off[l], colkeep_dev.empty() ? nullptr : colkeep_dev[l], toc_dev,
+                                   L[l].K, L[l].N, L[l].mask, L[l].ld_mask, s));
   }
-  TSM_CUDA(cudaStreamSynchronize(s));
+  ts::SelectState st_host;
+  memset(&st_host, 0, sizeof(st_host));
+  if (sel == 0 && !f64) {
+    if (thr_out) TSM_CUDA(cudaMemcpyAsync(thr_out, sc.thr + 1, sizeof(double), cudaMemcpyDeviceToHost, s));
+    TSM_CUDA(cudaMemcpyAsync(&st_host, sc.st, sizeof(st_host), cudaMemcpyDeviceToHost, s));
+  }
+  std::vector<int> optr(total_tiles + 1, 0);
+  TSM_CUDA(cudaMemcpyAsync(optr.data(), optr_dev, optr.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
+  // lists: with at most a million tile-rows the whole (upper-bound) array comes back in the same
+  // round trip; beyond that the exact size is awaited first
+  const bool one_trip = total <= (1 << 20);
+  std::vector<int> list;
+  if (one_trip) {
+    list.resize(total);
+    if (total > 0) TSM_CUDA(cudaMemcpyAsync(list.data(), list_dev, total * sizeof(int), cudaMemcpyDeviceToHost, s));
+  }
+  TSM_CUDA(cudaStreamSynchronize(s));   // seg, tile_of_col (host) must outlive their copies; everything is done
+  if (st_host.error) return ts_internal_fail(TS_ERR_CUDA, "radix select lost its rank (non-finite input?)");
+  if (!one_trip) {
+    list.resize(optr[total_tiles]);
+    if (!list.empty()) {
+      TSM_CUDA(cudaMemcpyAsync(list.data(), list_dev, list.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
+      TSM_CUDA(cudaStreamSynchronize(s));
+    }
+  }
 
   res->layers.resize(nl);
   for (int l = 0; l < nl; ++l) {
@@ -439,19 +471,6 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
         if (colkeep_host.empty() || colkeep_host[l][c]) R.kept_n.push_back(c);
       }
       R.tile_n_ptr[t + 1] = static_cast<int>(R.kept_n.size());
-    }
-    if (L[l].mask) {
-      std::vector<int> tile_of_col(L[l].N);
-      for (int t = 0; t < nt; ++t) {
-        for (int c = bounds[l][t]; c < bounds[l][t + 1]; ++c) tile_of_col[c] = t;
-      }
-      int* toc_dev = nullptr;
-      TSM_OK(arena.alloc(&toc_dev, tile_of_col.size()));
-      TSM_CUDA(cudaMemcpyAsync(toc_dev, tile_of_col.data(), tile_of_col.size() * sizeof(int),
-                               cudaMemcpyHostToDevice, s));
-      TSM_CUDA(ts::dense_mask_launch(keep + off[l], colkeep_dev.empty() ? nullptr : colkeep_dev[l], toc_dev,
-                                     L[l].K, L[l].N, L[l].mask, L[l].ld_mask, s));
-      TSM_CUDA(cudaStreamSynchronize(s));  // tile_of_col (host) must outlive the copy
     }
   }
   return TS_OK;

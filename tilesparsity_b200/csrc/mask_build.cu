@@ -410,6 +410,35 @@ segment_count_kernel(const uint8_t* __restrict__ keep, const long long* __restri
   if (threadIdx.x == 0) counts[blockIdx.x] = red[0];
 }
 
+// out_ptr[0..n] = exclusive prefix sums of counts[0..n): one block, so that the lists can be compacted
+// without the counts going to the host and back.
+__global__ void __launch_bounds__(256)
+segment_offsets_kernel(const int* __restrict__ counts, int n, int* __restrict__ out_ptr) {
+  __shared__ int part[256];
+  __shared__ int carry;
+  if (threadIdx.x == 0) {
+    carry = 0;
+    out_ptr[0] = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < n; base += 256) {
+    const int i = base + threadIdx.x;
+    const int c = i < n ? counts[i] : 0;
+    part[threadIdx.x] = c;
+    __syncthreads();
+    for (int o = 1; o < 256; o <<= 1) {
+      const int add = threadIdx.x >= o ? part[threadIdx.x - o] : 0;
+      __syncthreads();
+      part[threadIdx.x] += add;
+      __syncthreads();
+    }
+    if (i < n) out_ptr[i + 1] = carry + part[threadIdx.x];
+    __syncthreads();
+    if (threadIdx.x == 255) carry += part[255];
+    __syncthreads();
+  }
+}
+
 // One block per segment: list[out_ptr[s] + r] = position (inside the segment) of its r-th set flag.
 __global__ void __launch_bounds__(256)
 segment_compact_kernel(const uint8_t* __restrict__ keep, const long long* __restrict__ seg_ptr,
@@ -713,6 +742,11 @@ cudaError_t segment_count_launch(const uint8_t* keep, const long long* seg_ptr, 
                                  cudaStream_t s) {
   if (n_seg <= 0) return cudaSuccess;
   segment_count_kernel<<<n_seg, 256, 0, s>>>(keep, seg_ptr, counts);
+  return cudaGetLastError();
+}
+
+cudaError_t segment_offsets_launch(const int* counts, int n_seg, int* out_ptr, cudaStream_t s) {
+  segment_offsets_kernel<<<1, 256, 0, s>>>(counts, n_seg < 0 ? 0 : n_seg, out_ptr);
   return cudaGetLastError();
 }
 

@@ -405,7 +405,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const int m_cnt = min(w.m_len, M - m0);
       const bool active = j < w.n_count;
       // TMA store of the local copy: consecutive Ct rows, nothing to read back
-      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f;
+      const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f && ep.multicast == nullptr;
       // The CTA's last unit: every K block has been consumed, so the pipeline stages are free and
       // each 64-column group gets a staging group of its own there; no group waits for the store
       // of the one before it.
@@ -529,6 +529,10 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
             for (int e = 0; e < 4; ++e) {
               if (cr[e] >= 0 && m_ok) {
                 const long long off = static_cast<long long>(cr[e]) * ldc + m0 + grp_col + cchunk * 8;
+                if (ep.multicast != nullptr) {
+                  multimem_st_16(ep.multicast + off, val[e]);     // every GPU's copy, this one included
+                  continue;
+                }
                 if (!tma_store) *reinterpret_cast<uint4*>(Ct + off) = val[e];
                 for (int p = 0; p < ep.n_peers; ++p) {
                   int pp = p + peer_rot;

@@ -77,6 +77,10 @@ struct EpilogueArgs {
   int act;
   int n_peers;
   uint16_t* peers[7];
+  // Multicast address of Ct (an NVSwitch multicast mapping of the same buffer on every GPU of the
+  // group, this one included), or nullptr: every kept row is then stored once with multimem.st and
+  // the switch delivers it to all copies; Ct itself and peers[] are not written by plain stores.
+  uint16_t* multicast;
 };
 
 // One 64-row K block of a work unit.  A CTA's blocks are stored in processing order; the host
@@ -295,6 +299,14 @@ __device__ __forceinline__ void bulk_wait_read_all() {
 
 __device__ __forceinline__ void bulk_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// One 16-byte store to a multicast address: NVSwitch writes it into every GPU's copy of the buffer.
+// (A store only: nothing here ever loads through a multicast mapping.)
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -71,6 +71,8 @@ cudaError_t threshold_launch(const float* vals, long long n, double thr, uint8_t
                              cudaStream_t s);
 cudaError_t segment_count_launch(const uint8_t* keep, const long long* seg_ptr, int n_seg, int* counts,
                                  cudaStream_t s);
+// out_ptr[0..n_seg] = exclusive prefix sums of counts (device to device).
+cudaError_t segment_offsets_launch(const int* counts, int n_seg, int* out_ptr, cudaStream_t s);
 cudaError_t segment_compact_launch(const uint8_t* keep, const long long* seg_ptr, int n_seg,
                                    const int* out_ptr, int* list, cudaStream_t s);
 cudaError_t dense_mask_launch(const uint8_t* rowkeep, const uint8_t* colkeep, const int* tile_of_col,

@@ -175,13 +175,15 @@ class TWLayer:
     # ------------------------------------------------------------------ compute
     def masked_gemm(self, At: torch.Tensor, out: torch.Tensor | None = None, alpha: float = 1.0,
                     beta: float = 0.0, simt: bool = False, bias: torch.Tensor | None = None,
-                    activation: str | None = None, peers=None) -> torch.Tensor:
+                    activation: str | None = None, peers=None, multicast: int | None = None) -> torch.Tensor:
         """Ct[N, M] = act(alpha * (W .* mask)^T @ At[K, M] + beta * Ct + bias[:, None]), kept columns only.
 
         At is the reference's activation layout: [K, M] with M contiguous.  Without `out` a zeroed
         [N, M] tensor is allocated, so pruned columns read as zero.  bias is fp32 [N]; activation is
         None, "relu" or "gelu"; peers are raw device addresses of further [N, M] buffers (same row
-        pitch as `out`) that receive the same rows, e.g. the other GPUs' copies of a sharded output.
+        pitch as `out`) that receive the same rows, e.g. the other GPUs' copies of a sharded output;
+        `multicast` is instead the NVSwitch multicast address of `out` (the switch delivers every
+        store to all GPUs' copies, this one included).
         """
         if At.dim() != 2 or At.shape[0] != self.K or At.dtype != self.dtype or At.device != self.device:
             raise ValueError(f"At must be a [{self.K}, M] {self.dtype} tensor on {self.device}")
@@ -215,6 +217,9 @@ class TWLayer:
             ep.n_peers = len(peers)
             for i, p in enumerate(peers):
                 ep.peer_ct[i] = int(p)
+            if multicast:
+                # the multicast address of `out`: one multimem store per piece reaches every GPU's copy
+                ep.multicast_ct = int(multicast)
             check(lib.ts_masked_gemm_ex(self._h, M, C.c_void_p(At.data_ptr()), At.stride(0), C.c_void_p(out.data_ptr()),
                                         out.stride(0), C.byref(ep), _stream_ptr(self.device)))
         return out

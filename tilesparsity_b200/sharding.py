@@ -136,7 +136,7 @@ class ShardedTWLayer:
         handle.barrier()
         return buf, handle
 
-    def masked_gemm_allgather(self, At, buf, handle):
+    def masked_gemm_allgather(self, At, buf, handle, multicast: bool = False):
         """One kernel computes this rank's slab and stores every kept row into all ranks' gathered
         buffers (plain stores to peer-mapped memory: the transfer over NVLink overlaps the tiles still
         being computed).  The two barriers around it are device-side (signal pads of the symmetric
@@ -149,9 +149,20 @@ class ShardedTWLayer:
         pitch = buf.stride(0) * buf.element_size()
         peers = [int(handle.buffer_ptrs[p]) + row0 * pitch for p in range(self.world) if p != self.rank]
         handle.barrier(channel=0)
-        self.layer.masked_gemm(At, out=buf[row0:row0 + n_loc], peers=peers)
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0) if multicast else 0
+        if mc:
+            # one multimem store per 16-byte piece: NVSwitch writes it into all ranks' buffers, so a GPU
+            # sends its slab once instead of once per peer
+            self.layer.masked_gemm(At, out=buf[row0:row0 + n_loc], multicast=mc + row0 * pitch)
+        else:
+            self.layer.masked_gemm(At, out=buf[row0:row0 + n_loc], peers=peers)
         handle.barrier(channel=1)
         return buf
+
+    @staticmethod
+    def has_multicast(handle) -> bool:
+        """Whether the symmetric allocation has an NVSwitch multicast mapping."""
+        return bool(int(getattr(handle, "multicast_ptr", 0) or 0))
 
     def assemble(self, gathered):
         """Full Ct[N, M] in the original column order (pruned columns zero).  A consumer that can
