@@ -434,9 +434,9 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
   }
   std::vector<int> optr(total_tiles + 1, 0);
   TSM_CUDA(cudaMemcpyAsync(optr.data(), optr_dev, optr.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
-  // lists: with at most a million tile-rows the whole (upper-bound) array comes back in the same
-  // round trip; beyond that the exact size is awaited first
-  const bool one_trip = total <= (1 << 20);
+  // lists: up to 64 Ki tile-rows the whole (upper-bound) array comes back in the same round trip;
+  // beyond that the exact size is awaited first (a second round trip is cheaper than the extra bytes)
+  const bool one_trip = total <= (1 << 16);
   std::vector<int> list;
   if (one_trip) {
     list.resize(total);

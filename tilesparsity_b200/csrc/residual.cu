@@ -9,8 +9,10 @@
 //
 // stored column-wise (CSC of W = CSR of W^T): col_ptr[N+1], row_idx[nnz] (k), val[nnz] (16-bit).
 // With the batch contiguous in both At and Ct, one warp owns one output row segment Ct[n][m0..m0+256)
-// and every non-zero adds a scaled, fully coalesced 512-byte piece of an At row to it.  The work is
-// bound by the L2 -> SM traffic of those pieces (2*M bytes per non-zero).
+// and every non-zero adds a scaled, fully coalesced 512-byte piece of an At row to it: 2*M bytes of
+// L2 -> SM traffic per non-zero, with no reuse a register file could exploit (the rows of different
+// non-zeros are unrelated).  Measured on B200 (NMT LSTM shape, 125 829 non-zeros, M = 6400): SM
+// instruction issue 71 %, L1 60 %, L2 53 % of peak -- issue-bound first, L2-bound right behind.
 #include "ts_common.cuh"
 #include "ts_kernels.h"
 
@@ -48,19 +50,44 @@ residual_spmm_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ro
   int p = p0;
   for (; p + 4 <= p1; p += 4) {
     uint4 a[4];
-    float w[4];
+    uint16_t wraw[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int k = __ldg(row_idx + p + u);
-      w[u] = unpack1<DT>(__ldg(val + p + u));
+      wraw[u] = __ldg(val + p + u);
       a[u] = __ldg(reinterpret_cast<const uint4*>(At + static_cast<long long>(k) * lda + m));
     }
+    if constexpr (DT == kF16) {
+      // The kernel is bound by instruction issue (conversions and FMAs), not by L2: four products
+      // at a time are summed with packed half-precision FMAs and join the fp32 accumulators as one
+      // value, which halves the instruction count.  The four-term partial sum carries a relative
+      // error of about 2^-10 of a term that is itself a small share of the output.
+      __half2 part[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      float f[8];
-      unpack8<DT>(a[u], f);
+      for (int i = 0; i < 4; ++i) part[i] = __float2half2_rn(0.0f);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = fmaf(w[u], f[i], acc[i]);
+      for (int u = 0; u < 4; ++u) {
+        const __half wh = *reinterpret_cast<const __half*>(&wraw[u]);
+        const __half2 w2 = __half2half2(wh);
+        const __half2* av = reinterpret_cast<const __half2*>(&a[u]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) part[i] = __hfma2(w2, av[i], part[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(part[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float w = unpack1<DT>(wraw[u]);
+        float f[8];
+        unpack8<DT>(a[u], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, f[i], acc[i]);
+      }
     }
   }
   for (; p < p1; ++p) {
