@@ -333,18 +333,20 @@ int ts_order_statistics(const float* vals_dev, int64_t n, int64_t rank_lo, int64
 /* np.percentile(vals, q) (method "linear") of n float32 values on the device; q_is_f64 as above. */
 int ts_percentile_f32(const float* vals_dev, int64_t n, double q, int q_is_f64, double* out, void* stream);
 
-/* The reference's baseline patterns next to the tile-wise ones (pruning_fun names "ew" and "vw",
- * Pruning/VGG/prune_algo.py:267-278).  "bw" (block-wise, :229-264) is not offered: its block norms
- * come out of BLAS sdot, whose summation order depends on the host CPU, so there is nothing fixed to
- * be identical to. */
+/* The reference's baseline patterns next to the tile-wise ones (pruning_fun names "ew", "vw" and "bw",
+ * Pruning/VGG/prune_algo.py:267-278).  "ew" and "vw" are bit-identical to the reference.  "bw" is not
+ * and cannot be: its block norms come out of BLAS sdot, whose summation order depends on the host CPU,
+ * so a block whose norm lies within rounding distance of the threshold may fall on the other side. */
 #define TS_PATTERN_EW 0 /* element_wise, prune_algo.py:38-53: |score| above one percentile of all layers */
 #define TS_PATTERN_VW 1 /* vector_vise, prune_algo.py:196-227: top-k inside blocks of 16 rows of a column */
+#define TS_PATTERN_BW 2 /* block_wise, prune_algo.py:229-264: 32 x 32 blocks (its default granularity, the
+                           one its hooks use) whose Frobenius norm lies above one percentile of all layers */
 
-/* Builds element-wise or vector-wise masks on the GPU, bit-identical to
+/* Builds element-wise, vector-wise or block-wise masks on the GPU; "ew" and "vw" bit-identical to
  * pruning_fun("ew" | "vw")(scores, sparsity) of the reference with NumPy 2.3.
  *   scores_dev[l]  float32 [Ks[l]][lds[l]] (lds NULL: dense rows)
  *   masks_dev[l]   uint8 [Ks[l]][ld_masks[l]] (ld_masks NULL: dense rows), receives 0/1
- *   threshold_out  optional: the element-wise threshold (NaN for vector-wise)
+ *   threshold_out  optional: the element-wise / block-wise threshold (NaN for vector-wise)
  * Allocates device scratch for "ew", synchronises `stream`, returns when the masks are complete.
  * Limit: 1048560 rows per layer (TS_ERR_UNSUPPORTED beyond). */
 int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,

@@ -228,12 +228,40 @@ def percentile_f64(values, q):
     return np.float64(a + diff * gamma)
 
 
-ALGOS = {"tw1": tw1, "tw2": tw2, "tw1m": tw1m, "tw2m": tw2m, "ew": ew, "vw": vw}
+def bw(scores, sparsity, granularity=32, return_norms=False):
+    """Block-wise baseline (prune_algo.py:229-264): Frobenius norm of every granularity x granularity
+    block, one percentile over the blocks of all layers, blocks above it kept.  The norm of a 2-D slice
+    goes through BLAS sdot, so its last bits depend on the host CPU; `return_norms` also returns the
+    block norms in float64 and the threshold, with which a test can tell the blocks that sit within
+    rounding distance of the threshold."""
+    norms, exact = [], []
+    for s in scores:
+        for i in range(0, s.shape[0], granularity):
+            for j in range(0, s.shape[1], granularity):
+                blk = s[i:i + granularity, j:j + granularity]
+                norms.append(np.linalg.norm(blk))
+                exact.append(np.sqrt(np.sum(blk.astype(np.float64) ** 2)))
+    threshold = np.percentile(norms, sparsity)
+    block_mask = norms > threshold
+    out, idx = [], 0
+    for s in scores:
+        mask = np.zeros(s.shape)
+        for i in range(0, s.shape[0], granularity):
+            for j in range(0, s.shape[1], granularity):
+                if block_mask[idx]:
+                    mask[i:i + granularity, j:j + granularity] = 1
+                idx += 1
+        out.append(mask)
+    if return_norms:
+        return out, np.asarray(exact), float(threshold)
+    return out
+
+
+ALGOS = {"tw1": tw1, "tw2": tw2, "tw1m": tw1m, "tw2m": tw2m, "ew": ew, "vw": vw, "bw": bw}
 
 
 def pruning_fun(name):
-    """Same dispatch as the reference (prune_algo.py:267-278); `bw` is not restated (its block
-    norms go through BLAS sdot, whose summation order depends on the host CPU)."""
+    """Same dispatch as the reference (prune_algo.py:267-278)."""
     return ALGOS[name]
 
 

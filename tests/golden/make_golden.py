@@ -53,6 +53,10 @@ CASES = {
     "vw_small":         ("vw", [(96, 320)], 75.0, None, None, 61, "normal"),
     "vw_ragged":        ("vw", [(70, 130), (16, 40), (9, 33)], 50.0, None, None, 62, "uniform"),
     "vw_90":            ("vw", [(128, 96)], 90.0, None, None, 63, "normal"),
+    # block-wise (32 x 32 blocks, the default its hooks use); norms via the generating host's BLAS
+    "bw_small":         ("bw", [(96, 320)], 75.0, None, None, 91, "normal"),
+    "bw_ragged":        ("bw", [(70, 130), (40, 33)], 50.0, None, None, 92, "uniform"),
+    "bw_bert_attn":     ("bw", [(768, 768)], 90.0, None, None, 2002, "bert"),
 }
 
 

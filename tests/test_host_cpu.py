@@ -54,10 +54,10 @@ def test_argument_validation_needs_no_gpu():
 
 def test_pruning_fun_dispatch_matches_the_reference_names():
     from tilesparsity_b200 import masks
-    for name in ("tw1", "tw2", "tw1m", "tw2m", "ew", "vw"):
+    for name in ("tw1", "tw2", "tw1m", "tw2m", "ew", "vw", "bw"):
         assert callable(masks.pruning_fun(name))
     with pytest.raises(KeyError):
-        masks.pruning_fun("bw")          # block-wise: host-BLAS-dependent norms, not offered
+        masks.pruning_fun("tw3")
 
 
 def test_shard_plan_is_lpt_and_balanced():

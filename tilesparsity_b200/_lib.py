@@ -20,7 +20,7 @@ MASK_MODES = {"tw1": 0, "tw2": 1, "tw1m": 2, "tw2m": 3, "bert_type2": 4, "bert_t
               "topk_l1": 7, "tw_cols_rows": 8}
 
 
-PATTERN_MODES = {"ew": 0, "vw": 1}
+PATTERN_MODES = {"ew": 0, "vw": 1, "bw": 2}
 
 
 class TileSparseError(RuntimeError):

@@ -795,7 +795,9 @@ int ts_tw1_row_keep_noalloc(const float* score_dev, int64_t ld, int K, int N, in
 int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_dev, const int* Ks, const int* Ns,
                           const int64_t* lds, double sparsity, uint8_t* const* masks_dev, const int64_t* ld_masks,
                           double* threshold_out, void* stream) {
-  if (pattern != TS_PATTERN_EW && pattern != TS_PATTERN_VW) return ts_internal_fail(TS_ERR_INVALID, "unknown pattern %d", pattern);
+  if (pattern != TS_PATTERN_EW && pattern != TS_PATTERN_VW && pattern != TS_PATTERN_BW) {
+    return ts_internal_fail(TS_ERR_INVALID, "unknown pattern %d", pattern);
+  }
   if (n_layers <= 0 || !scores_dev || !Ks || !Ns || !masks_dev) return ts_internal_fail(TS_ERR_INVALID, "NULL or empty argument");
   if (!(sparsity >= 0.0 && sparsity <= 100.0)) return ts_internal_fail(TS_ERR_INVALID, "sparsity=%g must be in [0, 100]", sparsity);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -819,6 +821,36 @@ int ts_build_pattern_mask(int pattern, int n_layers, const void* const* scores_d
                                   masks_dev[l], ld_masks ? ld_masks[l] : Ns[l], s));
     }
     TSM_CUDA(cudaStreamSynchronize(s));
+    return TS_OK;
+  }
+  if (pattern == TS_PATTERN_BW) {
+    // block-wise: one percentile over the Frobenius norms of the 32 x 32 blocks of all layers (a list
+    // of float32 values and a Python-number q: float32 percentile arithmetic), blocks above it are kept
+    Arena arena;
+    Scratch sc;
+    TSM_OK(alloc_scratch(arena, &sc));
+    long long n_blocks = 0;
+    std::vector<long long> boff(n_layers + 1, 0);
+    for (int l = 0; l < n_layers; ++l) {
+      n_blocks += static_cast<long long>((Ks[l] + 31) / 32) * ((Ns[l] + 31) / 32);
+      boff[l + 1] = n_blocks;
+    }
+    float* norms = nullptr;
+    uint8_t* keep = nullptr;
+    TSM_OK(arena.alloc(&norms, static_cast<size_t>(n_blocks)));
+    TSM_OK(arena.alloc(&keep, static_cast<size_t>(n_blocks)));
+    for (int l = 0; l < n_layers; ++l) {
+      TSM_CUDA(ts::block_norms_launch(static_cast<const float*>(scores_dev[l]), lds ? lds[l] : Ns[l], Ks[l], Ns[l],
+                                      norms + boff[l], s));
+    }
+    TSM_OK(percentile_to_device(norms, n_blocks, sparsity, /*wide=*/false, /*f64_values=*/false, sc, 3, s));
+    TSM_CUDA(ts::threshold_dev_launch(norms, n_blocks, sc.thr + 3, keep, s));
+    for (int l = 0; l < n_layers; ++l) {
+      TSM_CUDA(ts::block_mask_launch(keep + boff[l], Ks[l], Ns[l], masks_dev[l], ld_masks ? ld_masks[l] : Ns[l], s));
+    }
+    double thr = 0.0;
+    TSM_OK(read_thresholds(sc, 3, &thr, s));
+    if (threshold_out) *threshold_out = thr;
     return TS_OK;
   }
   // element-wise: one percentile over |score| of all layers.  The reference flattens through Python

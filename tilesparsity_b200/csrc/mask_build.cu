@@ -582,6 +582,41 @@ vw_mask_kernel(const float* __restrict__ score, long long ld, int K, int N, int 
   }
 }
 
+// Block-wise baseline (prune_algo.py:229-264): Frobenius norm of every 32 x 32 block (ragged at the
+// edges), blocks numbered row-major.  The reference's norm of a 2-D slice goes through BLAS sdot, whose
+// summation order depends on the host CPU, so there is no order to reproduce: one warp per block, lane =
+// column, rows in order, then a shuffle tree.  grid (ceil(nbj / 8), nbi), block 256 = 8 warps.
+constexpr int kBwBlock = 32;
+
+__global__ void __launch_bounds__(256)
+block_norms_kernel(const float* __restrict__ score, long long ld, int K, int N, int nbj, float* __restrict__ out) {
+  const int bj = blockIdx.x * 8 + (threadIdx.x >> 5), bi = blockIdx.y;
+  if (bj >= nbj) return;
+  const int lane = threadIdx.x & 31;
+  const int n = bj * kBwBlock + lane;
+  const int k0 = bi * kBwBlock, k1 = min(K, k0 + kBwBlock);
+  float acc = 0.0f;
+  if (n < N) {
+    for (int k = k0; k < k1; ++k) {
+      const float x = __ldg(score + static_cast<long long>(k) * ld + n);
+      acc = fmaf(x, x, acc);
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) out[static_cast<long long>(bi) * nbj + bj] = sqrtf(acc);
+}
+
+// mask[k][n] = keep[(k / 32) * nbj + n / 32]
+__global__ void __launch_bounds__(256)
+block_mask_kernel(const uint8_t* __restrict__ keep, int K, int N, int nbj, uint8_t* __restrict__ mask,
+                  long long ld_mask) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  for (int k = blockIdx.y; k < K; k += gridDim.y) {
+    mask[static_cast<long long>(k) * ld_mask + n] = keep[static_cast<long long>(k / kBwBlock) * nbj + n / kBwBlock];
+  }
+}
+
 // TEW ranking values: v[k*N + n] = sqrt(w*w) - mask[k][n]   (prune_algo.py:156-159)
 __global__ void __launch_bounds__(256)
 tew_values_kernel(const float* __restrict__ score, long long ld, const uint8_t* __restrict__ mask,
@@ -786,6 +821,20 @@ cudaError_t vw_mask_launch(const float* score, long long ld, int K, int N, int t
   if (K <= 0 || N <= 0) return cudaSuccess;
   dim3 grid((N + 127) / 128, (K + kVwBlock - 1) / kVwBlock);
   vw_mask_kernel<<<grid, 128, 0, s>>>(score, ld, K, N, topk, mask, ld_mask);
+  return cudaGetLastError();
+}
+
+cudaError_t block_norms_launch(const float* score, long long ld, int K, int N, float* out, cudaStream_t s) {
+  const int nbi = (K + kBwBlock - 1) / kBwBlock, nbj = (N + kBwBlock - 1) / kBwBlock;
+  dim3 grid((nbj + 7) / 8, nbi);
+  block_norms_kernel<<<grid, 256, 0, s>>>(score, ld, K, N, nbj, out);
+  return cudaGetLastError();
+}
+
+cudaError_t block_mask_launch(const uint8_t* keep, int K, int N, uint8_t* mask, long long ld_mask, cudaStream_t s) {
+  const int nbj = (N + kBwBlock - 1) / kBwBlock;
+  dim3 grid((N + 255) / 256, K < 65535 ? K : 65535);
+  block_mask_kernel<<<grid, 256, 0, s>>>(keep, K, N, nbj, mask, ld_mask);
   return cudaGetLastError();
 }
 

@@ -84,6 +84,11 @@ cudaError_t abs_values_launch(const float* score, long long ld, int K, int N, fl
 cudaError_t vw_mask_launch(const float* score, long long ld, int K, int N, int topk, uint8_t* mask,
                            long long ld_mask, cudaStream_t s);
 
+// Block-wise baseline: out[bi * nbj + bj] = Frobenius norm of the 32 x 32 block (bi, bj) of score;
+// mask[k][n] = keep[block of (k, n)].
+cudaError_t block_norms_launch(const float* score, long long ld, int K, int N, float* out, cudaStream_t s);
+cudaError_t block_mask_launch(const uint8_t* keep, int K, int N, uint8_t* mask, long long ld_mask, cudaStream_t s);
+
 cudaError_t tew_values_launch(const float* score, long long ld, const uint8_t* mask, long long ld_mask,
                               int K, int N, float* vals, cudaStream_t s);
 cudaError_t tew_apply_launch(const float* vals, const double* thr, int K, int N, uint8_t* mask,

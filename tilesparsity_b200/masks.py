@@ -134,10 +134,11 @@ def build_mask(name: str, scores, sparsity, granularity: int = 128, g1percent=No
 
 
 def build_pattern_mask(name: str, scores, sparsity, device=None):
-    """The reference's baseline patterns on the GPU: "ew" (element-wise, prune_algo.py:38-53) and "vw"
-    (vector-wise, prune_algo.py:196-227).  Returns (list of CUDA bool masks, threshold or NaN)."""
+    """The reference's baseline patterns on the GPU: "ew" (element-wise, prune_algo.py:38-53), "vw"
+    (vector-wise, :196-227) and "bw" (block-wise with its default 32 x 32 blocks, :229-264).  Returns
+    (list of CUDA bool masks, threshold or NaN)."""
     if name not in _lib.PATTERN_MODES:
-        raise KeyError(f"unknown pattern {name!r} (ew, vw)")
+        raise KeyError(f"unknown pattern {name!r} (ew, vw, bw)")
     if not torch.cuda.is_available():
         raise RuntimeError("build_pattern_mask needs a CUDA device (there is no CPU fallback)")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -163,20 +164,21 @@ def build_pattern_mask(name: str, scores, sparsity, device=None):
 
 def pruning_fun(pruning_type: str):
     """Same dispatch as the reference (prune_algo.py:267-278): the tile-wise algorithms and the
-    element-wise / vector-wise baselines ("bw" is not offered: its block norms depend on the host
-    BLAS).  The returned function takes (scores, sparsity[, granularity][, g1percent]) and returns
-    the masks as NumPy arrays when given NumPy scores (bool; float64 0/1 for "vw", as the reference
-    does), as CUDA bool tensors otherwise."""
-    if pruning_type in ("ew", "vw"):
+    element-wise / vector-wise / block-wise baselines.  "bw" equals the reference up to blocks whose
+    norm lies within rounding distance of the threshold (its norms come out of the host's BLAS).  The
+    returned function takes (scores, sparsity[, granularity][, g1percent]) and returns the masks as
+    NumPy arrays when given NumPy scores (bool; float64 0/1 for "vw" and "bw", as the reference does),
+    as CUDA bool tensors otherwise."""
+    if pruning_type in ("ew", "vw", "bw"):
         def pattern_fn(accumulated_scores, sparsity):
             masks, _ = build_pattern_mask(pruning_type, accumulated_scores, sparsity)
             if all(isinstance(s, np.ndarray) for s in accumulated_scores):
                 out = [m.cpu().numpy() for m in masks]
-                return [m.astype(np.float64) for m in out] if pruning_type == "vw" else out
+                return [m.astype(np.float64) for m in out] if pruning_type in ("vw", "bw") else out
             return masks
         return pattern_fn
     if pruning_type not in ("tw1", "tw2", "tw1m", "tw2m"):
-        raise KeyError(f"{pruning_type!r} is not one of tw1, tw2, tw1m, tw2m, ew, vw")
+        raise KeyError(f"{pruning_type!r} is not one of tw1, tw2, tw1m, tw2m, ew, vw, bw")
 
     def fn(accumulated_scores, sparsity, granularity=128, g1percent=None):
         res = build_mask(pruning_type, accumulated_scores, sparsity, granularity, g1percent)
