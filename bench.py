@@ -661,6 +661,7 @@ def run_square(args):
     check = sharded_outputs_match(min(n, 2048), device, rank, world) if world > 1 else None
     ts, W, gen = square_layer(n, device)
     shard = sharding.ShardedTWLayer(W, ts, rank, world, torch.bfloat16)
+    Wt = W.t().contiguous().to(torch.bfloat16) if world == 1 else None    # for the cuBLAS dense line
     del W
     n_sets = max(2, min(4, (3 * L2_BYTES) // (n * n * 2) + 1))
     At = [torch.randn((n, n), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16) for _ in range(n_sets)]
@@ -685,6 +686,11 @@ def run_square(args):
     ms_med = float(np.median(ms))
     kept = ts.kept_flops_per_row() * n
     value = kept * args.steps / (ms_med * 1e-3) / 1e12
+    dense_ms = None
+    if Wt is not None:
+        Cd = torch.empty((n, n), dtype=torch.bfloat16, device=device)
+        dense_ms = float(np.median(timed_repeats(lambda i: torch.matmul(Wt, At[i % n_sets], out=Cd), args.steps,
+                                                 max(3, args.warmup), 5))) / args.steps
     if rank == 0:
         peaks = load_peaks()
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -694,6 +700,8 @@ def run_square(args):
                            "parallelism": f"tile-sharded x{world}", "shard_balance": round(shard.plan.balance(), 4),
                            "l2": f"activations rotate over {n_sets} buffers of {n * n * 2 / 2**20:.0f} MiB"},
                 "tensor_frac_of_measured_peak": value / world / peaks["bf16_tflops_sustained"],
+                "cublas_dense_ms_per_step": dense_ms,
+                "speedup_vs_cublas_dense": (dense_ms / (ms_med / args.steps)) if dense_ms else None,
                 "verified": None if check is None else bool(check["nccl"] and check["fused"]),
                 "gpu_launches": args.steps * len(ms), "clocks": clocks}
         print(json.dumps(line), flush=True)
