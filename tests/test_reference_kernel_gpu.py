@@ -137,3 +137,40 @@ def test_reference_drivers_rule_between_the_two_kernels_on_positive_data(tmp_pat
     mine = run_this_library(p, 1.0, 0.0, C0)
     kept = np.concatenate(p["cols"])
     assert og.checkout_errors(mine[kept], ref_c[kept], 1e-2) == 0
+
+
+@needs_ref
+@pytest.mark.parametrize("shape", [(12800, 768, 768, 384, 384), (12800, 3072, 768, 1536, 384), (12800, 768, 3072, 384, 1536)])
+def test_readme_shapes_agree_and_report_both_kernels_times(tmp_path, shape, capsys):
+    """The shapes the reference's README quotes (StreamMaskedGEMM/README.md:14-27): results agree, and
+    the microseconds of both kernels on this GPU are printed (run with -s to see them): the reference's
+    kernel timed its own way (a stream per tile, a device synchronisation per pass, mean of 20 passes),
+    this library's entry point with CUDA events over 20 back-to-back calls."""
+    M, N, K, Np, Kp = shape
+    p = make_problem(M, N, K, Np, Kp, seed=sum(shape))
+    C0 = np.zeros((N, M), dtype=np.float16)
+    ref_c, ref_us = run_reference_kernel(tmp_path, p, 1.0, 0.0, C0, iters=20)
+    mine = run_this_library(p, 1.0, 0.0, C0)
+    kept = np.concatenate(p["cols"])
+    assert og.max_rel_error(mine[kept], ref_c[kept].astype(np.float64)) <= 1e-2
+    from tilesparsity_b200.stream_gemm import prepare_stream_gemm_nn
+    dev = torch.device("cuda", torch.cuda.current_device())
+    A, B = torch.from_numpy(p["A"]).to(dev), torch.from_numpy(p["B"]).to(dev)
+    C = torch.zeros((N, M), dtype=torch.float16, device=dev)
+    mk = [torch.from_numpy(np.asarray(m, dtype=np.int32)).to(dev) for m in p["mk"]]
+    mn = [torch.from_numpy(m).to(dev) for m in p["mn"]]
+    call = prepare_stream_gemm_nn(M, N, K, 1.0, A, B, 0.0, C, p["bn"], p["N_cal"], p["K_cal"], mn, mk, p["off_B"], p["off_C"])
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    mine_us = e0.elapsed_time(e1) * 1e3 / 20
+    with capsys.disabled():
+        print(f"\nREADME shape M={M} N={N} K={K} N_pruned={Np} K_pruned={Kp}: reference kernel {ref_us:.1f} us, "
+              f"this library {mine_us:.1f} us ({ref_us / mine_us:.1f}x)")
+    assert ref_us > 0 and mine_us > 0
