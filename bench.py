@@ -766,6 +766,20 @@ def conv_case(name, B, H, W, cin, cout, algo, sparsity, g1, iters, note=""):
     t_pack = time_us(lambda i: layer.pack_input(xs[i % n_sets], pl[i % n_sets]), steps, n_sets, n_sets)
     t_gemm = time_us(lambda i: layer.masked_conv(pl[i % n_sets], geo, out=cts[i % n_sets]), steps, n_sets, n_sets)
     t_unpack = time_us(lambda i: layer.unpack_output(cts[i % n_sets], geo, ys[i % n_sets]), steps, n_sets, n_sets)
+    # inside a chain of convolutions the input comes from the previous layer's padded-space output
+    # (ts_conv_repack) and the output stays there: neither pack nor unpack
+    chain_ok = cin == cout
+    t_repack = t_chain = None
+    if chain_ok:
+        t_repack = time_us(lambda i: layer.repack_input(cts[i % n_sets], geo, pl[(i + 1) % n_sets]), steps, n_sets, n_sets)
+
+        def chained(i):
+            s = i % n_sets
+            layer.repack_input(cts[s], geo, pl[s])
+            layer.masked_conv(pl[s], geo, out=cts[(s + 1) % n_sets])
+        t_chain = time_us(chained, steps, n_sets, n_sets)
+        for i in range(n_sets):
+            layer.pack_input(xs[i], pl[i])
 
     def whole(i):
         s = i % n_sets
@@ -783,6 +797,9 @@ def conv_case(name, B, H, W, cin, cout, algo, sparsity, g1, iters, note=""):
     row = {"config": name, "B": B, "H": H, "W": W, "cin": cin, "cout": cout, "dtype": "bfloat16",
            "pack_us": round(t_pack, 2), "gemm_us": round(t_gemm, 2), "unpack_us": round(t_unpack, 2),
            "conv_us": round(t_all, 2), "cudnn_dense_us": round(t_dense, 2), "speedup_vs_cudnn_dense": round(t_dense / t_all, 3),
+           "repack_us": round(t_repack, 2) if t_repack else None,
+           "chained_conv_us": round(t_chain, 2) if t_chain else None,
+           "chained_speedup_vs_cudnn_dense": round(t_dense / t_chain, 3) if t_chain else None,
            "kept_tflops": round(kept / t_all / 1e6, 1), "kept_tflops_gemm_only": round(kept / t_gemm / 1e6, 1),
            "algorithmic_bytes": alg, "gbs_on_algorithmic_bytes": round(alg / t_all / 1e3, 1),
            "padded_pixels_over_pixels": round(geo["m_padded"] / (B * H * W), 3),

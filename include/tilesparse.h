@@ -156,6 +156,13 @@ int ts_layer_set_conv(ts_layer_t* layer, int cin, int kh, int kw);
 int ts_conv_pack_input(const void* x_nhwc_dev, int B, int H, int W, int C, int kh, int kw, void* planes_dev,
                        int64_t plane_ld, void* stream);
 
+/* The padded-space output of one convolution, Ct_dev [C][ldc], as the input planes of the next
+ * convolution with the same image size and a kh x kw kernel: planes[j][c][m] = Ct[c][m shifted by the
+ * tap], zero where the tap leaves the image (which also clears the scratch positions of Ct).  A chain
+ * of convolutions therefore stays in the channel-major padded layout: no NHWC round trip between layers. */
+int ts_conv_repack(const void* Ct_dev, int64_t ldc, int B, int H, int W, int C, int kh, int kw, void* planes_dev,
+                   int64_t plane_ld, void* stream);
+
 /* Ct[n][m] = act(alpha * conv(X, W .* mask)[m][n] + beta * Ct[n][m] + bias[n]) over the padded pixel
  * space, for the layer's kept output channels n; Ct_dev is [N][ldc], ldc >= m_padded. */
 int ts_masked_conv(ts_layer_t* layer, int B, int H, int W, const void* planes_dev, int64_t plane_ld, void* Ct_dev,

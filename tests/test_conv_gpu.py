@@ -75,3 +75,38 @@ def test_geometry_and_bad_arguments():
         ConvTWLayer(torch.zeros((3, 3, 4, 128), device="cuda"), ts, torch.float16)
     with pytest.raises(TileSparseError):
         conv.geometry(0, 4, 4, 3, 3)
+
+
+def test_two_convolutions_chained_in_the_padded_layout():
+    """conv -> ReLU -> conv without an NHWC round trip: the first layer's padded-space output goes
+    through ts_conv_repack straight into the second layer's input planes."""
+    from tilesparsity_b200 import ConvTWLayer, build_mask, masks
+    g = synth.rng(909)
+    B, H, W, c0, c1, c2 = 2, 6, 10, 32, 64, 128
+    x = np.maximum(g.standard_normal((B, H, W, c0), dtype=np.float32), 0)
+    w1 = (g.standard_normal((3, 3, c0, c1), dtype=np.float32) * np.float32(np.sqrt(2.0 / (9 * c0)))).astype(np.float32)
+    w2 = (g.standard_normal((3, 3, c1, c2), dtype=np.float32) * np.float32(np.sqrt(2.0 / (9 * c1)))).astype(np.float32)
+    dt = torch.float16
+    wd1, wd2 = torch.from_numpy(w1).cuda(), torch.from_numpy(w2).cuda()
+    r1 = build_mask("tw2", masks.img2col_forward([wd1]), 50.0, 128)       # prunes output channels of layer 1 too
+    r2 = build_mask("tw1", masks.img2col_forward([wd2]), 60.0, 128)
+    l1, l2 = ConvTWLayer(wd1, r1.tiles[0], dt), ConvTWLayer(wd2, r2.tiles[0], dt)
+    xd = torch.from_numpy(x).to(dt).cuda()
+    planes1, geo = l1.pack_input(xd)
+    ct1 = l1.masked_conv(planes1, geo, activation="relu")
+    planes2, geo2 = l2.repack_input(ct1, geo)
+    y = l2.unpack_output(l2.masked_conv(planes2, geo2), geo2).float().cpu().numpy()
+    # oracle: layer 1 in float32 on the 16-bit inputs, rounded to 16 bit as the GPU stores it, then layer 2
+    x16 = xd.float().cpu().numpy()
+    a1 = og.masked_matmul_dense(og.im2col_nhwc(x16, 3, 3), wd1.to(dt).float().cpu().numpy().reshape(-1, c1),
+                                r1.masks[0].cpu().numpy())
+    a1 = np.maximum(a1, 0).astype(np.float16).astype(np.float32).reshape(B, H, W, c1)
+    # the GPU's own layer-1 output must be that, up to the last bit of the 16-bit rounding
+    got1 = l1.unpack_output(ct1, geo).float().cpu().numpy()
+    assert og.max_rel_error(got1, a1) <= 1e-2
+    ref = og.masked_matmul_dense(og.im2col_nhwc(got1, 3, 3), wd2.to(dt).float().cpu().numpy().reshape(-1, c2),
+                                 r2.masks[0].cpu().numpy()).reshape(B, H, W, c2)
+    assert og.max_rel_error(y, ref) <= 1e-2
+    assert og.elementwise_violations(y, ref, rtol=1e-2, floor=1e-3) == 0
+    l1.close()
+    l2.close()

@@ -73,6 +73,7 @@ SIGNATURES = {
                                    _i64p, _i64p]),
     "ts_layer_set_conv": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int]),
     "ts_conv_pack_input": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp]),
+    "ts_conv_repack": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp]),
     "ts_masked_conv": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.POINTER(Epilogue), _vp]),
     "ts_conv_unpack_output": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     "ts_layer_set_unit_rows": (C.c_int, [_vp, C.c_int]),

@@ -58,6 +58,22 @@ class ConvTWLayer:
         geo.update(B=B, H=H, W=W)
         return planes, geo
 
+    def repack_input(self, ct_prev: torch.Tensor, geo: dict, planes: torch.Tensor | None = None):
+        """The padded-space output Ct [cin, m_padded] of the previous convolution (same image size) as
+        this layer's input planes: the chain conv -> conv stays channel-major, no NHWC round trip."""
+        if ct_prev.dim() != 2 or ct_prev.shape[0] != self.cin or ct_prev.dtype != self.dtype or ct_prev.stride(1) != 1:
+            raise ValueError(f"ct_prev must be a [{self.cin}, m_padded] {self.dtype} tensor with contiguous rows")
+        g = geometry(geo["B"], geo["H"], geo["W"], self.kh, self.kw)
+        if ct_prev.shape[1] < g["m_padded"] or g["Wp"] != geo["Wp"] or g["Hp"] != geo["Hp"]:
+            raise ValueError("the previous output lives in another padded pixel space (different kernel size?)")
+        if planes is None:
+            planes = torch.empty((self.kw, self.cin, g["plane_ld"]), dtype=self.dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            check(lib.ts_conv_repack(C.c_void_p(ct_prev.data_ptr()), ct_prev.stride(0), geo["B"], geo["H"], geo["W"], self.cin,
+                                     self.kh, self.kw, C.c_void_p(planes.data_ptr()), g["plane_ld"], _stream_ptr(self.device)))
+        g.update(B=geo["B"], H=geo["H"], W=geo["W"])
+        return planes, g
+
     def masked_conv(self, planes: torch.Tensor, geo: dict, out: torch.Tensor | None = None, bias: torch.Tensor | None = None,
                     activation: str | None = None) -> torch.Tensor:
         """Ct [cout, m_padded] over the padded pixel space (pruned output channels stay as they are in `out`)."""

@@ -869,6 +869,26 @@ int ts_conv_pack_input(const void* x_nhwc_dev, int B, int H, int W, int C, int k
   return TS_OK;
 }
 
+int ts_conv_repack(const void* Ct_dev, int64_t ldc, int B, int H, int W, int C, int kh, int kw, void* planes_dev,
+                   int64_t plane_ld, void* stream) {
+  int hp = 0, wp = 0;
+  int64_t m = 0, need = 0;
+  int rc = ts_conv_geometry(B, H, W, kh, kw, &hp, &wp, &m, &need);
+  if (rc != TS_OK) return rc;
+  if (C <= 0 || C > 65535 || (kh % 2) == 0 || (kw % 2) == 0 || kw > 9 || kh > 9) {
+    return fail(TS_ERR_INVALID, "C=%d must be in [1, 65535]; kh=%d, kw=%d must be odd and at most 9", C, kh, kw);
+  }
+  if (!Ct_dev || !planes_dev || (reinterpret_cast<uintptr_t>(planes_dev) & 15u) || ldc < m) {
+    return fail(TS_ERR_INVALID, "NULL pointer, unaligned planes, or ldc smaller than the padded pixel count");
+  }
+  if (plane_ld < need || (plane_ld % 8) != 0) {
+    return fail(TS_ERR_INVALID, "plane_ld=%lld must be a multiple of 8 and >= %lld", (long long)plane_ld, (long long)need);
+  }
+  TS_CUDA(ts::conv_repack_launch(Ct_dev, ldc, B, H, W, hp, wp, kh, kw, C, planes_dev, plane_ld,
+                                 static_cast<cudaStream_t>(stream)));
+  return TS_OK;
+}
+
 int ts_masked_conv(ts_layer_t* l, int B, int H, int W, const void* planes_dev, int64_t plane_ld, void* Ct_dev,
                    int64_t ldc, const ts_epilogue_t* epi, void* stream) {
   if (!l) return fail(TS_ERR_INVALID, "layer is NULL");

@@ -111,7 +111,57 @@ conv_unpack_output_kernel(const uint16_t* __restrict__ ct, long long ldc, int B,
   }
 }
 
+// Padded-space output of one convolution -> input planes of the next (same image size and padding
+// geometry): planes[j][c][m] = Ct[c][m - ph*Wp + j - pw] where that position is a real pixel, else 0.
+// Both sides are channel-major, so this is a shifted, masked copy: 16-byte stores, the one-pixel
+// shifts of the taps assembled from two aligned 16-byte loads.  grid (ceil(m_pad / 8 / 256), C, kw).
+__global__ void __launch_bounds__(256)
+conv_repack_kernel(const uint16_t* __restrict__ ct, long long ldc, int H, int W, int Hp, int Wp, int kh, int kw,
+                   long long m_pad, uint16_t* __restrict__ planes, long long plane_ld, int C) {
+  const long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;   // group of 8 padded pixels
+  const long long m0 = g * 8;
+  if (m0 >= m_pad) return;
+  const int c = blockIdx.y, j = blockIdx.z;
+  const int ph = (kh - 1) / 2, pw = (kw - 1) / 2;
+  const int x0 = static_cast<int>(m0 % Wp);
+  const int yp = static_cast<int>((m0 / Wp) % Hp);
+  const int y = yp - ph;
+  uint16_t out[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) out[e] = 0;
+  if (y >= 0 && y < H) {
+    const long long s0 = m0 - static_cast<long long>(ph) * Wp + (j - pw);   // source index of element 0
+    const uint16_t* row = ct + static_cast<long long>(c) * ldc;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int xs = x0 + e + j - pw;
+      if (xs >= 0 && xs < W) out[e] = __ldg(row + s0 + e);
+    }
+  }
+  uint4 o;
+  o.x = out[0] | (static_cast<uint32_t>(out[1]) << 16);
+  o.y = out[2] | (static_cast<uint32_t>(out[3]) << 16);
+  o.z = out[4] | (static_cast<uint32_t>(out[5]) << 16);
+  o.w = out[6] | (static_cast<uint32_t>(out[7]) << 16);
+  *reinterpret_cast<uint4*>(planes + (static_cast<long long>(j) * C + c) * plane_ld + m0) = o;
+}
+
 }  // namespace
+
+cudaError_t conv_repack_launch(const void* ct, long long ldc, int B, int H, int W, int Hp, int Wp, int kh, int kw,
+                               int C, void* planes, long long plane_ld, cudaStream_t stream) {
+  if (B <= 0 || C <= 0) return cudaSuccess;
+  const long long m_pad = static_cast<long long>(B) * Hp * Wp;
+  if (plane_ld > m_pad) {
+    cudaError_t e = cudaMemset2DAsync(static_cast<uint16_t*>(planes) + m_pad, plane_ld * 2, 0, (plane_ld - m_pad) * 2,
+                                      static_cast<size_t>(kw) * C, stream);
+    if (e != cudaSuccess) return e;
+  }
+  dim3 grid(static_cast<unsigned>((m_pad / 8 + 255) / 256), C, kw);
+  conv_repack_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, H, W, Hp, Wp, kh, kw, m_pad,
+                                               static_cast<uint16_t*>(planes), plane_ld, C);
+  return cudaGetLastError();
+}
 
 cudaError_t conv_pack_input_launch(const void* x_nhwc, int B, int H, int W, int C, int kh, int kw, int Hp, int Wp,
                                    void* planes, long long plane_ld, cudaStream_t stream) {

@@ -53,6 +53,10 @@ cudaError_t residual_spmm_launch(int dtype, const int* col_ptr, const int* row_i
 // Hp = H + kh - 1, Wp = (W + kw - 1) rounded up to 8.
 cudaError_t conv_pack_input_launch(const void* x_nhwc, int B, int H, int W, int C, int kh, int kw, int Hp, int Wp,
                                    void* planes, long long plane_ld, cudaStream_t stream);
+// The padded-space output Ct[C][ldc] of one convolution as the input planes of the next one (same
+// image size, same kernel size): a shifted, masked copy, no NHWC round trip.
+cudaError_t conv_repack_launch(const void* ct, long long ldc, int B, int H, int W, int Hp, int Wp, int kh, int kw,
+                               int C, void* planes, long long plane_ld, cudaStream_t stream);
 cudaError_t conv_unpack_output_launch(const void* ct, long long ldc, int B, int H, int W, int Hp, int Wp, int N,
                                       void* y_nhwc, cudaStream_t stream);
 
