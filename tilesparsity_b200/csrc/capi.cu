@@ -878,8 +878,9 @@ int ts_conv_repack(const void* Ct_dev, int64_t ldc, int B, int H, int W, int C, 
   if (C <= 0 || C > 65535 || (kh % 2) == 0 || (kw % 2) == 0 || kw > 9 || kh > 9) {
     return fail(TS_ERR_INVALID, "C=%d must be in [1, 65535]; kh=%d, kw=%d must be odd and at most 9", C, kh, kw);
   }
-  if (!Ct_dev || !planes_dev || (reinterpret_cast<uintptr_t>(planes_dev) & 15u) || ldc < m) {
-    return fail(TS_ERR_INVALID, "NULL pointer, unaligned planes, or ldc smaller than the padded pixel count");
+  if (!Ct_dev || !planes_dev || ((reinterpret_cast<uintptr_t>(planes_dev) | reinterpret_cast<uintptr_t>(Ct_dev)) & 15u) ||
+      ldc < m || (ldc % 8) != 0) {
+    return fail(TS_ERR_INVALID, "NULL or unaligned pointer, or ldc not a multiple of 8 >= the padded pixel count");
   }
   if (plane_ld < need || (plane_ld % 8) != 0) {
     return fail(TS_ERR_INVALID, "plane_ld=%lld must be a multiple of 8 and >= %lld", (long long)plane_ld, (long long)need);
