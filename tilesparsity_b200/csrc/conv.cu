@@ -126,35 +126,23 @@ conv_repack_kernel(const uint16_t* __restrict__ ct, long long ldc, int H, int W,
   const int x0 = static_cast<int>(m0 % Wp);
   const int yp = static_cast<int>((m0 / Wp) % Hp);
   const int y = yp - ph;
-  uint4 o = make_uint4(0, 0, 0, 0);
+  uint16_t out[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) out[e] = 0;
   if (y >= 0 && y < H) {
-    // source elements s0 .. s0+7 with s0 = m0 - ph*Wp + (j - pw): five aligned 32-bit words cover them
-    // whatever the parity of the shift; a funnel shift by 16 bits realigns the odd case
-    const int d = j - pw;
-    const long long s0 = m0 - static_cast<long long>(ph) * Wp + d;
+    const long long s0 = m0 - static_cast<long long>(ph) * Wp + (j - pw);   // source index of element 0
     const uint16_t* row = ct + static_cast<long long>(c) * ldc;
-    const long long w0 = (s0 - (d & 1)) >> 1;             // first 32-bit word (s0 - (d&1) is even)
-    const uint32_t* rw = reinterpret_cast<const uint32_t*>(row);
-    const bool odd = (d & 1) != 0;
-    uint32_t w[5];
 #pragma unroll
-    for (int k = 0; k < 5; ++k) {
-      // words wholly outside the row's padded pixel range are never selected below; clamp the address
-      const long long wi = w0 + k;
-      w[k] = (wi >= 0 && wi * 2 + 1 < ldc) ? __ldg(rw + wi) : 0u;
+    for (int e = 0; e < 8; ++e) {
+      const int xs = x0 + e + j - pw;
+      if (xs >= 0 && xs < W) out[e] = __ldg(row + s0 + e);
     }
-    uint32_t r[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) r[k] = odd ? __funnelshift_r(w[k], w[k + 1], 16) : w[k];
-    // zero the elements whose tap leaves the image
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int xa = x0 + 2 * k + d, xb = xa + 1;
-      if (xa < 0 || xa >= W) r[k] &= 0xffff0000u;
-      if (xb < 0 || xb >= W) r[k] &= 0x0000ffffu;
-    }
-    o = make_uint4(r[0], r[1], r[2], r[3]);
   }
+  uint4 o;
+  o.x = out[0] | (static_cast<uint32_t>(out[1]) << 16);
+  o.y = out[2] | (static_cast<uint32_t>(out[3]) << 16);
+  o.z = out[4] | (static_cast<uint32_t>(out[5]) << 16);
+  o.w = out[6] | (static_cast<uint32_t>(out[7]) << 16);
   *reinterpret_cast<uint4*>(planes + (static_cast<long long>(j) * C + c) * plane_ld + m0) = o;
 }
 
