@@ -34,7 +34,8 @@
 // warp writes its 32 rows with 16-byte coalesced stores through the kept-column list.
 //
 // Warp roles (448 threads): warp 0 = weight TMA, warp 1 = TMEM allocation + MMA issue,
-// warps 2-5 = activation gather, warps 6-13 = epilogue.
+// warps 2-5 = activation gather, warps 6-13 = epilogue.  (Eight gather warps were measured: 18 warps
+// leave 96 registers per thread, the kernel spills, and every workload got slower.)
 #include "ts_common.cuh"
 #include "ts_kernels.h"
 
@@ -45,13 +46,17 @@ namespace {
 constexpr int kNT = 128;                 // columns per tile (MMA M, TMEM lanes)
 constexpr int kKB = 64;                  // kept rows per pipeline stage
 constexpr int kWBytes = kNT * kKB * 2;   // 16 KiB of packed weights per stage
-constexpr int kThreads = 448;
 constexpr int kEpiThreads = 256;
 constexpr uint32_t kASbo = 1024;         // bytes between 8-row K groups of the gathered operand
 constexpr uint32_t kALbo = kKB * 128;    // bytes between its 64-column batch groups
 constexpr uint32_t kWSbo = 1024;         // bytes between 8-row groups of the weight operand
 constexpr int kMaxStages = 6;
-constexpr int kGW = 4;                   // gather warps
+#ifndef TS_GATHER_WARPS
+#define TS_GATHER_WARPS 4
+#endif
+constexpr int kGW = TS_GATHER_WARPS;     // gather warps
+constexpr int kEpiWarp0 = 2 + kGW;       // first epilogue warp
+constexpr int kThreads = 32 * kEpiWarp0 + kEpiThreads;
 // Gather warps that share one K block.  Measured on B200 with 1, 2 and 4: 4 is best or within 3 % of
 // the best on every workload tried (1 loses up to 30 % where the activations stream from DRAM,
 // because the blocks of different warps then land out of order and the MMA warp consumes them in
@@ -183,7 +188,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // lanes 0..: one 16-byte piece each: the descriptor, then the warp's slice of the row numbers
   const int meta_piece = lane == 0 ? 0 : 4 + (gw % kWarpsPerBlock) * kRowsPerWarp + (lane - 1) * 4;
   constexpr int kMetaLanes = 1 + kRowsPerWarp / 4;
-  if (warp >= 2 && warp < 6) {
+  if (warp >= 2 && warp < kEpiWarp0) {
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       if (lane < kMetaLanes) {
@@ -294,7 +299,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       ++acc_it;
       w = wn;
     }
-  } else if (warp < 6) {
+  } else if (warp < kEpiWarp0) {
     // ------------------------------------------------------------------ activation gather
     // kWarpsPerBlock warps share one block (a slice of its rows each); group p of warps takes the
     // blocks p, p+kWarpGroups, ... of the CTA's stream, block j lives in stage j % kStages.  Per block: wait
@@ -384,10 +389,10 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       cp_async_commit();
     }
     cp_async_wait_all();  // nothing of this thread is in flight when the CTA retires
-  } else if (warp >= 6) {
+  } else if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------------ epilogue
     constexpr int kGroups = MT / 128;            // 64-column groups per epilogue thread
-    const int ew = warp - 6;                     // 0..7
+    const int ew = warp - kEpiWarp0;             // 0..7
     const int half = ew >> 2;                    // takes the 64-column groups half, half+2, ...
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int j = q * 32 + lane;                 // tile column owned by this thread
