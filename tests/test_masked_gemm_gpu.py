@@ -173,6 +173,28 @@ def test_host_buffer_pipeline_blocks_beta_and_async():
     layer2.close()
 
 
+def test_host_buffer_calls_queued_back_to_back_on_one_layer():
+    """Several asynchronous host-buffer calls on the same layer without a wait in between (different
+    inputs, outputs alternating between two host buffers, a change of batch size in the middle): the
+    library's events hand the staging buffers from call to call, one wait at the end suffices."""
+    layer, At, A16, W16 = _case(512, 640, 1024, lambda g, nt: [128 + 32 * (t % 3) for t in range(nt)], torch.float16, 41)
+    g = synth.rng(41)
+    hAs, hCs, refs = [], [], []
+    for i, M in enumerate((1024, 1024, 512, 1024, 1024)):
+        a = torch.from_numpy(g.standard_normal((512, M), dtype=np.float32)).to(torch.float16)
+        hAs.append(a.pin_memory())
+        hCs.append(torch.full((640, M), 7.0, dtype=torch.float16).pin_memory())
+        refs.append(og.masked_matmul_compacted(a.float().numpy(), W16, layer.tiles))
+    for a, c in zip(hAs, hCs):
+        layer.masked_gemm_host(a, c, wait=False)
+    layer.host_wait()
+    torch.cuda.current_stream().synchronize()
+    for c, ref in zip(hCs, refs):
+        _accept(c.float().numpy(), ref)
+    layer.check()
+    layer.close()
+
+
 def test_grouped_layers_equal_separate_launches():
     """Independent layers as one block-structured layer over stacked activations and outputs."""
     from tilesparsity_b200 import TWLayer
