@@ -464,6 +464,13 @@ struct ts_layer {
   int forced_unit_rows = 0;    // 0: the scheduler chooses between 128- and 256-row units
   bool wp_fresh = false;       // packed weights were (re)written on a stream since the last GEMM launch
   bool host_pending = false;   // events[1] marks the end of the latest host-buffer call
+  // Tensor maps over the peers' output buffers of a tile-sharded layer (device copy, and the host
+  // copy it was uploaded from with the arguments it was encoded for).
+  CUtensorMap* d_peer_maps = nullptr;
+  CUtensorMap h_peer_maps[7];
+  void* peer_map_ptrs[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  long long peer_map_m = -1, peer_map_ldc = -1;
+  int peer_map_count = 0;
 };
 
 namespace {
@@ -608,6 +615,7 @@ int ts_layer_destroy(ts_layer_t* l) {
   cudaDeviceSynchronize();
   free_tiles(l);
   cudaFree(l->d_status);
+  cudaFree(l->d_peer_maps);
   cudaFree(l->d_at);
   cudaFree(l->d_ct);
   for (cudaEvent_t e : l->events) cudaEventDestroy(e);
@@ -803,6 +811,29 @@ int run_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct,
   CUtensorMap tmap_c;
   rc = make_out_tmap(&tmap_c, l->dtype, Ct, l->N, M, ldc);
   if (rc != TS_OK) return rc;
+  // Tile-sharded layers: the peers' copies of a full tile leave by TMA stores as well.  The maps are
+  // encoded once per set of peer buffers and kept on the device.
+  ep.peer_maps = nullptr;
+  if (ep.n_peers > 0 && ep.multicast == nullptr && ep.beta == 0.0f) {
+    bool same = l->d_peer_maps && l->peer_map_count == ep.n_peers && l->peer_map_m == M && l->peer_map_ldc == ldc;
+    for (int p = 0; same && p < ep.n_peers; ++p) same = l->peer_map_ptrs[p] == ep.peers[p];
+    if (!same) {
+      if (!l->d_peer_maps) TS_CUDA(cudaMalloc(&l->d_peer_maps, sizeof(l->h_peer_maps)));
+      l->peer_map_count = 0;
+      for (int p = 0; p < ep.n_peers; ++p) {
+        rc = make_out_tmap(&l->h_peer_maps[p], l->dtype, ep.peers[p], l->N, M, ldc);
+        if (rc != TS_OK) return rc;
+        l->peer_map_ptrs[p] = ep.peers[p];
+      }
+      // in stream order ahead of the launch below (the host copy lives in the layer)
+      TS_CUDA(cudaMemcpyAsync(l->d_peer_maps, l->h_peer_maps, sizeof(CUtensorMap) * ep.n_peers,
+                              cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+      l->peer_map_count = ep.n_peers;
+      l->peer_map_m = M;
+      l->peer_map_ldc = ldc;
+    }
+    ep.peer_maps = l->d_peer_maps;
+  }
   // The kernel fetches packed weights before it waits for the kernel ahead of it in the stream.
   // The first launch after ts_layer_pack_weights may directly follow the packing kernel, so it runs
   // as an ordinary (fully ordered) launch; from then on the weights are old data.

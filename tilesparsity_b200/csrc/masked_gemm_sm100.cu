@@ -411,6 +411,7 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const bool active = j < w.n_count;
       // TMA store of the local copy: consecutive Ct rows, nothing to read back
       const bool tma_store = use_tma_store && (w.flags & kItemDenseRows) && beta == 0.0f && ep.multicast == nullptr;
+      const bool tma_peers = tma_store && ep.peer_maps != nullptr;   // the peers' copies leave by TMA too
       // The CTA's last unit: every K block has been consumed, so the pipeline stages are free and
       // each 64-column group gets a staging group of its own there; no group waits for the store
       // of the one before it.
@@ -507,10 +508,17 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
           named_barrier_sync(half_bar, 128);     // the whole group is staged
           if (leader) {
             tma_store_2d(&tmap_c, smem_u32(stage_grp), m0 + grp_col, tile_row0);
+            if (tma_peers) {
+              for (int p = 0; p < ep.n_peers; ++p) {
+                int pp = p + peer_rot;
+                if (pp >= ep.n_peers) pp -= ep.n_peers;
+                tma_store_2d(ep.peer_maps + pp, smem_u32(stage_grp), m0 + grp_col, tile_row0);
+              }
+            }
             bulk_commit();
           }
         }
-        if (!tma_store || ep.n_peers > 0) {
+        if (!tma_store || (ep.n_peers > 0 && !tma_peers)) {
           // copy-out through the kept-column list: this warp's own 32 rows, four rows per
           // instruction, 16 bytes per lane; to Ct unless the TMA store took it, and to every peer.
           // Tile-sharded layers: the peers are the other GPUs' copies of Ct, written over NVLink;

@@ -81,6 +81,10 @@ struct EpilogueArgs {
   // group, this one included), or nullptr: every kept row is then stored once with multimem.st and
   // the switch delivers it to all copies; Ct itself and peers[] are not written by plain stores.
   uint16_t* multicast;
+  // One tensor map per peer (in global memory, same box and swizzle as the map over Ct), or nullptr:
+  // a tile whose kept columns are consecutive rows of Ct then leaves for every peer as TMA tile
+  // stores issued by one thread, like the local copy, instead of 16-byte stores from every lane.
+  const CUtensorMap* peer_maps;
 };
 
 // One 64-row K block of a work unit.  A CTA's blocks are stored in processing order; the host
