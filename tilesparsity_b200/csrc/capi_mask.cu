@@ -47,6 +47,8 @@ namespace {
 struct ScratchBlock {
   void* base = nullptr;
   size_t cap = 0;
+  void* pinned = nullptr;      // page-locked host block for the read-backs (asynchronous copies)
+  size_t pinned_cap = 0;
   std::mutex mu;
 };
 ScratchBlock g_scratch[64];
@@ -74,6 +76,24 @@ struct Arena {
       if (cudaMalloc(&blk->base, want) == cudaSuccess) blk->cap = want;
       else cudaGetLastError();
     }
+  }
+  // Page-locked host memory of at least `bytes` (kept between calls, grown on demand), or nullptr when
+  // it cannot be had or the request is unreasonably large: the caller then copies to pageable memory.
+  void* pinned(size_t bytes) {
+    if (!blk || bytes > (static_cast<size_t>(8) << 20)) return nullptr;
+    if (bytes > blk->pinned_cap) {
+      if (blk->pinned) cudaFreeHost(blk->pinned);
+      blk->pinned = nullptr;
+      blk->pinned_cap = 0;
+      const size_t want = std::max<size_t>(bytes + bytes / 2, static_cast<size_t>(1) << 18);
+      if (cudaHostAlloc(&blk->pinned, want, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        blk->pinned = nullptr;
+        return nullptr;
+      }
+      blk->pinned_cap = want;
+    }
+    return blk->pinned;
   }
   template <typename T>
   int alloc(T** out, size_t count) {
@@ -426,23 +446,52 @@ int row_stage(const std::vector<LayerIn>& L, const std::vector<std::vector<int>>
     TSM_CUDA(ts::dense_mask_launch(keep + off[l], colkeep_dev.empty() ? nullptr : colkeep_dev[l], toc_dev,
                                    L[l].K, L[l].N, L[l].mask, L[l].ld_mask, s));
   }
+  // Read-back: threshold, the select's error flag, the offsets and (up to 64 Ki tile-rows) the whole
+  // upper-bound list array in one round trip; beyond that the exact size is awaited first (a second
+  // round trip is cheaper than the extra bytes).  The copies land in page-locked memory when it can be
+  // had, so they are asynchronous and the host blocks once.
   ts::SelectState st_host;
   memset(&st_host, 0, sizeof(st_host));
-  if (sel == 0 && !f64) {
-    if (thr_out) TSM_CUDA(cudaMemcpyAsync(thr_out, sc.thr + 1, sizeof(double), cudaMemcpyDeviceToHost, s));
-    TSM_CUDA(cudaMemcpyAsync(&st_host, sc.st, sizeof(st_host), cudaMemcpyDeviceToHost, s));
-  }
-  std::vector<int> optr(total_tiles + 1, 0);
-  TSM_CUDA(cudaMemcpyAsync(optr.data(), optr_dev, optr.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
-  // lists: up to 64 Ki tile-rows the whole (upper-bound) array comes back in the same round trip;
-  // beyond that the exact size is awaited first (a second round trip is cheaper than the extra bytes)
+  const bool want_sel = sel == 0 && !f64;
   const bool one_trip = total <= (1 << 16);
+  std::vector<int> optr(total_tiles + 1, 0);
   std::vector<int> list;
-  if (one_trip) {
-    list.resize(total);
-    if (total > 0) TSM_CUDA(cudaMemcpyAsync(list.data(), list_dev, total * sizeof(int), cudaMemcpyDeviceToHost, s));
+  const size_t head_bytes = 256;   // [0, 8): threshold, [64, 64 + sizeof(SelectState)): select state
+  static_assert(sizeof(ts::SelectState) <= head_bytes - 64, "select state does not fit the read-back header");
+  const size_t optr_bytes = (optr.size() * sizeof(int) + 255) & ~static_cast<size_t>(255);
+  const size_t list_bytes = one_trip ? static_cast<size_t>(total) * sizeof(int) : 0;
+  char* pin = static_cast<char*>(arena.pinned(head_bytes + optr_bytes + list_bytes));
+  if (pin) {
+    if (want_sel) {
+      TSM_CUDA(cudaMemcpyAsync(pin, sc.thr + 1, sizeof(double), cudaMemcpyDeviceToHost, s));
+      TSM_CUDA(cudaMemcpyAsync(pin + 64, sc.st, sizeof(st_host), cudaMemcpyDeviceToHost, s));
+    }
+    TSM_CUDA(cudaMemcpyAsync(pin + head_bytes, optr_dev, optr.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
+    if (one_trip && total > 0) {
+      TSM_CUDA(cudaMemcpyAsync(pin + head_bytes + optr_bytes, list_dev, list_bytes, cudaMemcpyDeviceToHost, s));
+    }
+    TSM_CUDA(cudaStreamSynchronize(s));   // seg, tile_of_col (host) must outlive their copies; everything is done
+    if (want_sel) {
+      if (thr_out) memcpy(thr_out, pin, sizeof(double));
+      memcpy(&st_host, pin + 64, sizeof(st_host));
+    }
+    memcpy(optr.data(), pin + head_bytes, optr.size() * sizeof(int));
+    if (one_trip) {
+      const int* lp = reinterpret_cast<const int*>(pin + head_bytes + optr_bytes);
+      list.assign(lp, lp + optr[total_tiles]);     // the kept ones: a prefix of the upper-bound array
+    }
+  } else {
+    if (want_sel) {
+      if (thr_out) TSM_CUDA(cudaMemcpyAsync(thr_out, sc.thr + 1, sizeof(double), cudaMemcpyDeviceToHost, s));
+      TSM_CUDA(cudaMemcpyAsync(&st_host, sc.st, sizeof(st_host), cudaMemcpyDeviceToHost, s));
+    }
+    TSM_CUDA(cudaMemcpyAsync(optr.data(), optr_dev, optr.size() * sizeof(int), cudaMemcpyDeviceToHost, s));
+    if (one_trip) {
+      list.resize(total);
+      if (total > 0) TSM_CUDA(cudaMemcpyAsync(list.data(), list_dev, total * sizeof(int), cudaMemcpyDeviceToHost, s));
+    }
+    TSM_CUDA(cudaStreamSynchronize(s));
   }
-  TSM_CUDA(cudaStreamSynchronize(s));   // seg, tile_of_col (host) must outlive their copies; everything is done
   if (st_host.error) return ts_internal_fail(TS_ERR_CUDA, "radix select lost its rank (non-finite input?)");
   if (!one_trip) {
     list.resize(optr[total_tiles]);

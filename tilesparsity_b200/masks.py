@@ -130,7 +130,9 @@ def build_mask(name: str, scores, sparsity, granularity: int = 128, g1percent=No
         check(lib.ts_mask_result_thresholds(handle, thr))
     finally:
         lib.ts_mask_result_destroy(handle)
-    return MaskResult([m.bool() for m in masks], tiles, [r.bool() for r in resid] if resid else None, tuple(thr))
+    # the kernels write 0 / 1 bytes: reinterpreted, not converted
+    return MaskResult([m.view(torch.bool) for m in masks], tiles,
+                      [r.view(torch.bool) for r in resid] if resid else None, tuple(thr))
 
 
 def build_pattern_mask(name: str, scores, sparsity, device=None):
@@ -159,7 +161,7 @@ def build_pattern_mask(name: str, scores, sparsity, device=None):
             IA(*[t.shape[1] for t in sc]), LA(*[t.stride(0) for t in sc]), float(sparsity),
             VP(*[m.data_ptr() for m in masks]), LA(*[m.stride(0) for m in masks]), C.byref(thr),
             C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)))
-    return [m.bool() for m in masks], thr.value
+    return [m.view(torch.bool) for m in masks], thr.value
 
 
 def pruning_fun(pruning_type: str):
