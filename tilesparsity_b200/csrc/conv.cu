@@ -13,6 +13,8 @@
 // planes[j][c][m + r*Wp]: a contiguous run that starts on a 16-byte boundary for every (r, j, c).
 // The masked GEMM gathers those runs exactly as it gathers the rows of an activation matrix; its
 // output Ct[cout][m] lives in the same padded pixel space (positions with y >= H or x >= W are scratch).
+#include <algorithm>
+
 #include "ts_common.cuh"
 #include "ts_kernels.h"
 
@@ -24,6 +26,19 @@ constexpr int kPackCh = 64;    // channels per block
 constexpr int kPackPx = 64;    // padded pixels of one image row per pass
 constexpr int kPackRows = 4;   // padded image rows per pass
 constexpr int kTilePitch = kPackPx + 10;   // halves per tile row: 37 words, odd, so a column is conflict-free
+// halves between the image rows of a tile: 8 words past a multiple of 32, so that lanes which differ in
+// the image row (0..3), the channel (4 neighbours) and the 8-pixel group (0..1) hit 32 different banks
+constexpr int kTileRow = kPackCh * kTilePitch + 16;
+
+// Division of a small index by a small run-time divisor without the integer-division sequence (the
+// pack kernel was bound by its index arithmetic): floor(i / d) = umulhi(i, ceil(2^32 / d)) for
+// d <= 2^16 and i < 2^16.
+struct SmallDiv {
+  uint32_t mul, d;
+  __device__ __forceinline__ explicit SmallDiv(int div) : mul(div > 1 ? 0xffffffffu / static_cast<uint32_t>(div) + 1u : 0u),
+                                                          d(static_cast<uint32_t>(div)) {}
+  __device__ __forceinline__ int quot(int i) const { return d > 1 ? static_cast<int>(__umulhi(static_cast<uint32_t>(i), mul)) : i; }
+};
 
 // grid (ceil(Hp / 4), B, ceil(C / 64)), block 256.  One pass: 4 padded image rows x 64 columns of one
 // image, 64 channels.  The input is read with 16-byte loads along the channels, transposed through
@@ -32,35 +47,55 @@ constexpr int kTilePitch = kPackPx + 10;   // halves per tile row: 37 words, odd
 __global__ void __launch_bounds__(256)
 conv_pack_input_kernel(const uint16_t* __restrict__ x, int B, int H, int W, int C, int kh, int kw, int Hp, int Wp,
                        uint16_t* __restrict__ planes, long long plane_ld) {
-  __shared__ __align__(16) uint16_t tile[kPackRows][kPackCh][kTilePitch];   // [row][channel][padded column]
+  __shared__ __align__(16) uint16_t tile[kPackRows * kTileRow];   // [row][channel][padded column]
   const int yp0 = blockIdx.x * kPackRows, b = blockIdx.y, c0 = blockIdx.z * kPackCh;
   const int ph = (kh - 1) / 2, pw = (kw - 1) / 2;
   const int span = kPackPx + kw - 1;
   for (int x0 = 0; x0 < Wp; x0 += kPackPx) {
     __syncthreads();
-    // loads: (row, padded column, 8 channels) per thread and step
-    for (int i = threadIdx.x; i < kPackRows * span * (kPackCh / 8); i += blockDim.x) {
-      const int c8 = i % (kPackCh / 8), xx = (i / (kPackCh / 8)) % span, rr = i / ((kPackCh / 8) * span);
-      const int y = yp0 + rr - ph, xs = x0 + xx - pw;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (y >= 0 && y < H && xs >= 0 && xs < W && c0 + c8 * 8 < C) {
-        v = __ldg(reinterpret_cast<const uint4*>(x + ((static_cast<long long>(b) * H + y) * W + xs) * C + c0 + c8 * 8));
-      }
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    // The copy-out below reads columns [0, n_px8 * 8 + kw - 1) of every tile row.  Zero them (halo, the
+    // rows above and below the image, the padding of Wp), then load only the pixels that exist: for a
+    // 14-pixel image row that is a fifth of the pass's 64 + kw - 1 columns.
+    const int n_cols = min(span, ((min(kPackPx, Wp - x0) + 7) / 8) * 8 + kw - 1);
+    const int n_w32 = (n_cols + 1) / 2;
+    const SmallDiv by_w32(n_w32);
+    for (int i = threadIdx.x; i < kPackRows * kPackCh * n_w32; i += blockDim.x) {
+      const int rc = by_w32.quot(i), w32 = i - rc * n_w32;
+      reinterpret_cast<uint32_t*>(tile + (rc / kPackCh) * kTileRow + (rc % kPackCh) * kTilePitch)[w32] = 0u;
+    }
+    __syncthreads();
+    const int xx_lo = max(0, pw - x0), xx_hi = min(n_cols, W + pw - x0);   // padded columns that hold pixels
+    const int rr_lo = max(0, ph - yp0), rr_hi = min(kPackRows, H + ph - yp0);
+    const int n_xx = xx_hi - xx_lo, n_rr = rr_hi - rr_lo;
+    if (n_xx > 0 && n_rr > 0) {
+      // loads: (row, padded column, 8 channels) per thread and step
+      const SmallDiv by_xx(n_xx);
+      for (int i = threadIdx.x; i < n_rr * n_xx * (kPackCh / 8); i += blockDim.x) {
+        const int c8 = i % (kPackCh / 8), px = i / (kPackCh / 8), r_ = by_xx.quot(px);
+        const int xx = xx_lo + px - r_ * n_xx, rr = rr_lo + r_;
+        if (c0 + c8 * 8 >= C) continue;
+        const int y = yp0 + rr - ph, xs = x0 + xx - pw;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + ((static_cast<long long>(b) * H + y) * W + xs) * C + c0 + c8 * 8));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        tile[rr][c8 * 8 + 2 * e][xx] = static_cast<uint16_t>(w[e] & 0xffffu);
-        tile[rr][c8 * 8 + 2 * e + 1][xx] = static_cast<uint16_t>(w[e] >> 16);
+        for (int e = 0; e < 4; ++e) {
+          tile[rr * kTileRow + (c8 * 8 + 2 * e) * kTilePitch + xx] = static_cast<uint16_t>(w[e] & 0xffffu);
+          tile[rr * kTileRow + (c8 * 8 + 2 * e + 1) * kTilePitch + xx] = static_cast<uint16_t>(w[e] >> 16);
+        }
       }
     }
     __syncthreads();
     const int n_px8 = (min(kPackPx, Wp - x0) + 7) / 8;
+    // lanes run over the 8-pixel groups of a row first, then over the image rows: where a padded row is
+    // narrower than the pass (small images) consecutive rows are consecutive in the plane, and a warp's
+    // stores fall into a few long runs instead of one 16-byte piece per channel
+    const SmallDiv by_px8(n_px8);
     for (int i = threadIdx.x; i < kPackRows * kw * kPackCh * n_px8; i += blockDim.x) {
-      const int p8 = i % n_px8, cc = (i / n_px8) % kPackCh, j = (i / (n_px8 * kPackCh)) % kw;
-      const int rr = i / (n_px8 * kPackCh * kw);
+      const int q_ = by_px8.quot(i), p8 = i - q_ * n_px8;
+      const int rr = q_ % kPackRows, cc = (q_ / kPackRows) % kPackCh, j = q_ / (kPackRows * kPackCh);
       const int yp = yp0 + rr;
       if (yp >= Hp || c0 + cc >= C) continue;
-      const uint16_t* src = &tile[rr][cc][p8 * 8 + j];
+      const uint16_t* src = &tile[rr * kTileRow + cc * kTilePitch + p8 * 8 + j];
       uint4 o;
       o.x = src[0] | (static_cast<uint32_t>(src[1]) << 16);
       o.y = src[2] | (static_cast<uint32_t>(src[3]) << 16);
@@ -79,18 +114,20 @@ conv_pack_input_kernel(const uint16_t* __restrict__ x, int B, int H, int W, int 
 __global__ void __launch_bounds__(256)
 conv_unpack_output_kernel(const uint16_t* __restrict__ ct, long long ldc, int B, int H, int W, int Hp, int Wp, int N,
                           uint16_t* __restrict__ y) {
-  __shared__ __align__(16) uint16_t tile[kPackRows][kPackCh][kTilePitch];   // [row][output channel][column]
+  __shared__ __align__(16) uint16_t tile[kPackRows * kTileRow];   // [row][output channel][column]
   const int y0 = blockIdx.x * kPackRows, b = blockIdx.y, n0 = blockIdx.z * kPackCh;
   for (int x0 = 0; x0 < W; x0 += kPackPx) {
     const int n_px = min(kPackPx, W - x0);
     const int n_px8 = (n_px + 7) / 8;      // Wp is a multiple of 8, so whole groups stay inside the padded row
     __syncthreads();
+    const SmallDiv by_px8(n_px8), by_px(n_px);
     for (int i = threadIdx.x; i < kPackRows * kPackCh * n_px8; i += blockDim.x) {
-      const int p8 = i % n_px8, nn = (i / n_px8) % kPackCh, rr = i / (n_px8 * kPackCh);
+      const int q_ = by_px8.quot(i), p8 = i - q_ * n_px8;
+      const int rr = q_ % kPackRows, nn = q_ / kPackRows;   // rows before channels, as in the pack
       if (y0 + rr >= H || n0 + nn >= N) continue;
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(
           ct + static_cast<long long>(n0 + nn) * ldc + (static_cast<long long>(b) * Hp + y0 + rr) * Wp + x0 + p8 * 8));
-      uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[rr][nn][p8 * 8]);   // 4-byte aligned (odd word pitch)
+      uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[rr * kTileRow + nn * kTilePitch + p8 * 8]);   // 4-byte aligned (odd word pitch)
       dst[0] = v.x;
       dst[1] = v.y;
       dst[2] = v.z;
@@ -98,12 +135,13 @@ conv_unpack_output_kernel(const uint16_t* __restrict__ ct, long long ldc, int B,
     }
     __syncthreads();
     for (int i = threadIdx.x; i < kPackRows * n_px * (kPackCh / 8); i += blockDim.x) {
-      const int n8 = i % (kPackCh / 8), px = (i / (kPackCh / 8)) % n_px, rr = i / ((kPackCh / 8) * n_px);
+      const int n8 = i % (kPackCh / 8), pq = i / (kPackCh / 8), rr = by_px.quot(pq), px = pq - rr * n_px;
       if (y0 + rr >= H || n0 + n8 * 8 >= N) continue;
       uint32_t w[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        w[e] = tile[rr][n8 * 8 + 2 * e][px] | (static_cast<uint32_t>(tile[rr][n8 * 8 + 2 * e + 1][px]) << 16);
+        w[e] = tile[rr * kTileRow + (n8 * 8 + 2 * e) * kTilePitch + px] |
+               (static_cast<uint32_t>(tile[rr * kTileRow + (n8 * 8 + 2 * e + 1) * kTilePitch + px]) << 16);
       }
       *reinterpret_cast<uint4*>(y + ((static_cast<long long>(b) * H + y0 + rr) * W + x0 + px) * N + n0 + n8 * 8) =
           make_uint4(w[0], w[1], w[2], w[3]);
@@ -113,37 +151,73 @@ conv_unpack_output_kernel(const uint16_t* __restrict__ ct, long long ldc, int B,
 
 // Padded-space output of one convolution -> input planes of the next (same image size and padding
 // geometry): planes[j][c][m] = Ct[c][m - ph*Wp + j - pw] where that position is a real pixel, else 0.
-// Both sides are channel-major, so this is a shifted, masked copy: 16-byte stores, the one-pixel
-// shifts of the taps assembled from two aligned 16-byte loads.  grid (ceil(m_pad / 8 / 256), C, kw).
+// Both sides are channel-major, so this is a shifted, masked copy with 16-byte stores.  The source of
+// a group of 8 pixels starts d = j - pw elements off a 16-byte boundary: one 16-byte load for d = 0,
+// otherwise five aligned 32-bit words, realigned by a funnel shift when d is odd.  The position of a
+// group inside its image row and image comes from two reciprocal multiplications (the 64-bit
+// divisions this kernel started with cost more than its memory traffic).
+// grid (ceil(plane_ld / 8 / 256), ceil(C / 8), kw), eight channels per thread; (m_pad / 8) * max(Wp / 8, Hp) < 2^32.
+constexpr int kRepackCh = 8;
 __global__ void __launch_bounds__(256)
 conv_repack_kernel(const uint16_t* __restrict__ ct, long long ldc, int H, int W, int Hp, int Wp, int kh, int kw,
-                   long long m_pad, uint16_t* __restrict__ planes, long long plane_ld, int C) {
-  const long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;   // group of 8 padded pixels
-  const long long m0 = g * 8;
-  if (m0 >= m_pad) return;
-  const int c = blockIdx.y, j = blockIdx.z;
-  const int ph = (kh - 1) / 2, pw = (kw - 1) / 2;
-  const int x0 = static_cast<int>(m0 % Wp);
-  const int yp = static_cast<int>((m0 / Wp) % Hp);
-  const int y = yp - ph;
-  uint16_t out[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) out[e] = 0;
-  if (y >= 0 && y < H) {
-    const long long s0 = m0 - static_cast<long long>(ph) * Wp + (j - pw);   // source index of element 0
-    const uint16_t* row = ct + static_cast<long long>(c) * ldc;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int xs = x0 + e + j - pw;
-      if (xs >= 0 && xs < W) out[e] = __ldg(row + s0 + e);
+                   int n_groups, int n_groups_ld, uint32_t mul_wp8, uint32_t mul_hp,
+                   uint16_t* __restrict__ planes, long long plane_ld, int C) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;   // group of 8 padded pixels
+  if (g >= n_groups_ld) return;
+  const int c_begin = blockIdx.y * kRepackCh, c_end = min(C, c_begin + kRepackCh), j = blockIdx.z;
+  if (g >= n_groups) {
+    // the tail of every plane past the last image (read by the lowest kernel rows of the last pixels)
+    for (int c = c_begin; c < c_end; ++c) {
+      *reinterpret_cast<uint4*>(planes + (static_cast<long long>(j) * C + c) * plane_ld + (static_cast<long long>(g) << 3)) =
+          make_uint4(0, 0, 0, 0);
     }
+    return;
   }
-  uint4 o;
-  o.x = out[0] | (static_cast<uint32_t>(out[1]) << 16);
-  o.y = out[2] | (static_cast<uint32_t>(out[3]) << 16);
-  o.z = out[4] | (static_cast<uint32_t>(out[5]) << 16);
-  o.w = out[6] | (static_cast<uint32_t>(out[7]) << 16);
+  const int ph = (kh - 1) / 2, pw = (kw - 1) / 2;
+  const int wp8 = Wp >> 3;
+  // (a multiplier of 0 stands for a divisor of 1)
+  const int row = mul_wp8 ? static_cast<int>(__umulhi(static_cast<uint32_t>(g), mul_wp8)) : g;   // padded image row, all images
+  const int x0 = (g - row * wp8) << 3;
+  const int img = mul_hp ? static_cast<int>(__umulhi(static_cast<uint32_t>(row), mul_hp)) : row;
+  const int y = row - img * Hp - ph;
+  const long long m0 = static_cast<long long>(g) << 3;
+  const int d = j - pw;
+  const bool inside = y >= 0 && y < H && x0 + d < W && x0 + 7 + d >= 0;
+#pragma unroll 4
+  for (int c = c_begin; c < c_end; ++c) {
+  uint4 o = make_uint4(0, 0, 0, 0);
+  if (inside) {
+    const uint16_t* src_row = ct + static_cast<long long>(c) * ldc;
+    const long long s0 = m0 - static_cast<long long>(ph) * Wp + d;      // source index of element 0
+    uint32_t r[4];
+    if (d == 0) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src_row + s0));
+      r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+    } else {
+      const bool odd = (d & 1) != 0;
+      const long long w0 = (s0 - (odd ? 1 : 0)) >> 1;                    // first 32-bit word (an even element)
+      const uint32_t* rw = reinterpret_cast<const uint32_t*>(src_row);
+      uint32_t w[5];
+#pragma unroll
+      for (int k = 0; k < 5; ++k) {
+        // words outside the row are never selected below; their address is not touched
+        const long long wi = w0 + k;
+        w[k] = (wi >= 0 && wi * 2 + 1 < ldc) ? __ldg(rw + wi) : 0u;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) r[k] = odd ? __funnelshift_r(w[k], w[k + 1], 16) : w[k];
+    }
+    // zero the elements whose tap leaves the image row
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int xa = x0 + 2 * k + d, xb = xa + 1;
+      if (xa < 0 || xa >= W) r[k] &= 0xffff0000u;
+      if (xb < 0 || xb >= W) r[k] &= 0x0000ffffu;
+    }
+    o = make_uint4(r[0], r[1], r[2], r[3]);
+  }
   *reinterpret_cast<uint4*>(planes + (static_cast<long long>(j) * C + c) * plane_ld + m0) = o;
+  }
 }
 
 }  // namespace
@@ -152,14 +226,15 @@ cudaError_t conv_repack_launch(const void* ct, long long ldc, int B, int H, int 
                                int C, void* planes, long long plane_ld, cudaStream_t stream) {
   if (B <= 0 || C <= 0) return cudaSuccess;
   const long long m_pad = static_cast<long long>(B) * Hp * Wp;
-  if (plane_ld > m_pad) {
-    cudaError_t e = cudaMemset2DAsync(static_cast<uint16_t*>(planes) + m_pad, plane_ld * 2, 0, (plane_ld - m_pad) * 2,
-                                      static_cast<size_t>(kw) * C, stream);
-    if (e != cudaSuccess) return e;
-  }
-  dim3 grid(static_cast<unsigned>((m_pad / 8 + 255) / 256), C, kw);
-  conv_repack_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, H, W, Hp, Wp, kh, kw, m_pad,
-                                               static_cast<uint16_t*>(planes), plane_ld, C);
+  const long long n_groups = m_pad / 8, n_groups_ld = plane_ld / 8;   // the kernel zeroes the planes' tails too
+  // floor(i / d) = umulhi(i, ceil(2^32 / d)) holds for i * d < 2^32
+  if (n_groups * std::max<long long>(Wp / 8, Hp) >= (1LL << 32) || n_groups_ld >= (1LL << 31)) return cudaErrorInvalidValue;
+  const uint32_t mul_wp8 = Wp / 8 > 1 ? 0xffffffffu / static_cast<uint32_t>(Wp / 8) + 1u : 0u;
+  const uint32_t mul_hp = Hp > 1 ? 0xffffffffu / static_cast<uint32_t>(Hp) + 1u : 0u;
+  dim3 grid(static_cast<unsigned>((n_groups_ld + 255) / 256), (C + kRepackCh - 1) / kRepackCh, kw);
+  conv_repack_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, H, W, Hp, Wp, kh, kw,
+                                               static_cast<int>(n_groups), static_cast<int>(n_groups_ld), mul_wp8,
+                                               mul_hp, static_cast<uint16_t*>(planes), plane_ld, C);
   return cudaGetLastError();
 }
 
