@@ -107,8 +107,10 @@ int ts_masked_gemm(ts_layer_t* layer, int M, const void* At_dev, int64_t lda, vo
  *   bias_dev     fp32 [N] on the device, indexed by the column of W (row of Ct), or NULL
  *   activation   TS_ACT_NONE, TS_ACT_RELU, or TS_ACT_GELU (the tanh form of the reference's BERT,
  *                Pruning/BERT/utils/modeling.py:264-277)
- *   peer_ct      up to 7 further output buffers with the layout of Ct (same ldc): every kept row is also
- *                stored there with plain stores.  Given the peer-mapped Ct buffers of the other GPUs
+ *   peer_ct      up to 7 further output buffers with the layout of Ct (same ldc, 16-byte aligned): every
+ *                kept row is also stored there (a full tile as one TMA tile store per buffer, through
+ *                tensor maps the layer encodes once per set of buffers; a ragged tile, or any tile when
+ *                beta != 0, as plain 16-byte stores).  Given the peer-mapped Ct buffers of the other GPUs
  *                of a tile-sharded layer, the GEMM's epilogue performs the all-gather over NVLink.
  * This is what the reference's mask_dense does after its matmul (bias add, modeling.py:1003-1007)
  * folded into the GEMM; the reference has no multi-GPU path. */
