@@ -218,6 +218,22 @@ int ts_layer_schedule_stats(ts_layer_t* layer, int M, int* n_ctas, float* cta_co
  * testing aid; the reference fixes its CTA tile at compile time (basic_nn.cu:250-259). */
 int ts_layer_set_unit_rows(ts_layer_t* layer, int unit_rows);
 
+/* Split-K.  A work unit's K blocks run one after the other on one SM, so a launch cannot be shorter
+ * than its longest tile's kept rows / 64 blocks.  Where such a chain is long (>= 32 blocks) and the
+ * tile's share of the SMs is at least twice its number of 256-row units (a layer with few tiles and
+ * thousands of kept rows, e.g. a conv5 kernel pruned to a handful of column tiles), the scheduler cuts
+ * the tile's kept rows into up to four ranges that run as units of their own; they leave fp32 partial sums in scratch memory of the cached schedule
+ * and a second kernel adds them up and applies beta, bias and activation.  Deterministic, but not
+ * bit-identical to the unsplit schedule (another summation order).  On by default; calls that write
+ * peer buffers never split.  ts_layer_set_split_k(layer, 0) turns it off for a layer (no counterpart
+ * in the reference, whose tiles each run as one CUTLASS launch, basic_nn.cu:396-427).
+ * ts_plan_split returns the number of ranges per tile the scheduler would use (host logic only, no
+ * device needed): k_counts / n_counts = kept rows / kept columns per tile, K the rows of the activation
+ * matrix, M the batch size, n_ctas the number of SMs. */
+int ts_layer_set_split_k(ts_layer_t* layer, int enabled);
+int ts_plan_split(int n_tiles, const int32_t* k_counts, const int32_t* n_counts, int64_t K, int M, int n_ctas,
+                  int32_t* parts_out);
+
 /* The work distribution ts_masked_gemm would use for tiles with k_counts[t] kept rows and n_counts[t]
  * kept columns, activations of K rows and batch size M, on n_ctas SMs -- without a device (pure host
  * function).  Work units are (tile, run of batch rows); units_out receives one quadruple

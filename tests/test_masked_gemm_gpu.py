@@ -195,6 +195,58 @@ def test_host_buffer_calls_queued_back_to_back_on_one_layer():
     layer.close()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_split_k_units_match_the_oracle_and_the_unsplit_schedule(dtype):
+    """A layer with one long tile beside light ones (the VGG conv5 "10 % columns + 75 % rows" pattern):
+    the long tile's kept rows run as several units per batch block whose fp32 partial sums a second
+    kernel adds up.  Checked against the oracle, with bias + activation and with beta, with a ragged
+    batch, and against the same layer with split-K turned off."""
+    from tilesparsity_b200 import TWLayer
+    from tilesparsity_b200.tiles import tiles_from_lists
+    g = synth.rng(91)
+    K, N, M = 4608, 512, 2048 + 64
+    col = np.ones(N, bool)
+    col[g.choice(N, size=52, replace=False)] = False            # 460 kept columns: 3 full tiles + 76
+    nt = len(tile_bounds_from_col_mask(col, 128)) - 1
+    counts = [87, 155, 91, 4275][:nt]
+    lists = [np.sort(g.permutation(K)[:c]).astype(np.int32) for c in counts]
+    parts = np.zeros(nt, np.int32)
+    import ctypes as C
+    from tilesparsity_b200 import _lib
+    p32 = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+    b = tile_bounds_from_col_mask(col, 128)
+    ncols = np.array([col[b[t]:b[t + 1]].sum() for t in range(nt)], np.int32)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    _lib.check(_lib.lib.ts_plan_split(nt, p32(np.asarray(counts, np.int32)), p32(ncols), K, M, sms, p32(parts)))
+    assert parts.max() > 1, "the case is meant to exercise split units"
+    W = (g.standard_normal((K, N), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    Wd = torch.from_numpy(W).cuda()
+    A = g.standard_normal((K, M), dtype=np.float32)
+    At = torch.from_numpy(A).to(dtype).cuda()
+    A16, W16 = At.float().cpu().numpy(), Wd.to(dtype).float().cpu().numpy()
+    layer = TWLayer.from_lists(Wd, lists, col, 128, dtype)
+    ref = og.masked_matmul_compacted(A16, W16, layer.tiles)
+    C1 = layer.masked_gemm(At)
+    _accept(C1.float().cpu().numpy(), ref)
+    assert not C1.float().cpu().numpy()[~col].any()
+    # epilogue: bias + relu, then alpha / beta on top of an existing output
+    bias = torch.from_numpy(g.standard_normal(N, dtype=np.float32)).cuda()
+    C2 = layer.masked_gemm(At, bias=bias, activation="relu")
+    ref2 = np.maximum(ref + bias.cpu().numpy()[:, None], 0.0) * col[:, None]
+    _accept(C2.float().cpu().numpy(), ref2)
+    C3 = C1.clone()
+    layer.masked_gemm(At, out=C3, alpha=0.5, beta=1.0)
+    _accept(C3.float().cpu().numpy(), 1.5 * ref)
+    # deterministic, and equal to the unsplit schedule within the rounding of one 16-bit result
+    assert torch.equal(layer.masked_gemm(At), C1)
+    layer.set_split_k(False)
+    C4 = layer.masked_gemm(At)
+    _accept(C4.float().cpu().numpy(), ref)
+    assert og.max_rel_error(C4.float().cpu().numpy(), C1.float().cpu().numpy()) <= (4e-3 if dtype == torch.bfloat16 else 1e-3)
+    layer.check()
+    layer.close()
+
+
 def test_grouped_layers_equal_separate_launches():
     """Independent layers as one block-structured layer over stacked activations and outputs."""
     from tilesparsity_b200 import TWLayer

@@ -92,3 +92,38 @@ def test_unit_rows_can_be_pinned_and_bad_arguments_are_rejected():
         plan([5], [129], 768, 4096)
     with pytest.raises(_lib.TileSparseError):
         plan(kc, nc, 768, 0)
+
+
+def plan_split(k_counts, n_counts, K, M, n_ctas=148):
+    kc = np.ascontiguousarray(k_counts, dtype=np.int32)
+    nc = np.ascontiguousarray(n_counts, dtype=np.int32)
+    parts = np.zeros(len(kc), dtype=np.int32)
+    p = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+    _lib.check(lib.ts_plan_split(len(kc), p(kc), p(nc), K, M, n_ctas, p(parts)))
+    return parts.tolist()
+
+
+def test_split_k_plan_cuts_only_long_chains_with_sms_to_spare():
+    """A tile is cut into K ranges only when its chain of K blocks is long and its share of the SMs is at
+    least twice its number of 256-row units; the reference has no counterpart (one CUTLASS launch per
+    tile, StreamMaskedGEMM/perf/basic_nn.cu:396-427)."""
+    conv_rows = 3 * 512          # the planes of a 3 x 3 convolution over 512 channels that exist in memory
+    # VGG conv5 with 10 % of the columns and 75 % of the rows pruned: three light tiles and a 76-column
+    # tile that keeps about 4300 of 4608 rows; as a GEMM over the im2col matrix and as the convolution
+    assert plan_split([130, 71, 102, 4305], [128, 128, 128, 76], 4608, 12544) == [1, 1, 1, 2]
+    assert plan_split([95, 65, 26, 4422], [128, 128, 128, 76], conv_rows, 16384) == [1, 1, 1, 2]
+    # one 128-column tile with all 4608 rows kept
+    assert plan_split([4608], [128], 4608, 12544) == [3]
+    # tw2 conv5: as a GEMM the list schedule leaves a third of the SMs idle (cut), as the convolution the
+    # contiguous partition fills the machine already (whole)
+    assert plan_split([2318, 4594], [128, 128], 4608, 12544) == [1, 2]
+    assert plan_split([3749, 859], [128, 128], conv_rows, 16384) == [1, 1]
+    assert plan_split([3661, 3251], [128, 128], conv_rows, 16384) == [1, 1]
+    # BERT shapes and squares: no split
+    assert plan_split([768] * 6, [128] * 6, 3072, 4096) == [1] * 6
+    assert plan_split([192] * 24, [128] * 24, 768, 4096) == [1] * 24
+    assert plan_split([4096] * 128, [128] * 128, 16384, 16384) == [1] * 128
+    # never more than four ranges, none for an empty tile, short chains stay whole
+    assert plan_split([16384], [128], 16384, 256) == [4]
+    assert plan_split([4608, 4608], [128, 0], 4608, 12544) == [3, 1]
+    assert plan_split([1984], [128], 4608, 12544) == [1]

@@ -77,6 +77,8 @@ SIGNATURES = {
     "ts_masked_conv": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int64, C.POINTER(Epilogue), _vp]),
     "ts_conv_unpack_output": (C.c_int, [_vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     "ts_layer_set_unit_rows": (C.c_int, [_vp, C.c_int]),
+    "ts_layer_set_split_k": (C.c_int, [_vp, C.c_int]),
+    "ts_plan_split": (C.c_int, [C.c_int, _i32p, _i32p, C.c_int64, C.c_int, C.c_int, _i32p]),
     "ts_plan_schedule": (C.c_int, [C.c_int, _i32p, _i32p, C.c_int64, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int),
                                    C.POINTER(C.c_int), C.POINTER(C.c_int), _i32p, C.c_int, C.POINTER(C.c_float)]),
     "ts_stream_gemm_nn": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_float, _vp, _vp, C.c_float, _vp, C.c_int,

@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cmath>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -102,6 +103,22 @@ int make_out_tmap(CUtensorMap* map, int dtype, const void* Ct, long long n_rows,
   return TS_OK;
 }
 
+// Tensor map over the fp32 scratch [rows][M] of a split-K schedule: box 32 floats x 128 rows, 128-byte
+// swizzle (one staging group of the epilogue).
+int make_scratch_tmap(CUtensorMap* map, const float* scratch, long long rows, long long M) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(M) * 4};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(scratch), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TS_ERR_CUDA, "cuTensorMapEncodeTiled (scratch) failed (%d)", (int)r);
+  return TS_OK;
+}
+
 struct Schedule {
   ts::WorkItem* d_units = nullptr;
   ts::BlockDesc* d_blocks = nullptr;
@@ -112,7 +129,70 @@ struct Schedule {
   int n_units = 0;
   int unit_rows = 0;
   std::vector<float> cta_cost;
+  // split-K: tiles whose kept rows are spread over several units per batch block, the fp32 scratch
+  // their partial sums go to ([scratch_rows][scratch_ld]) and the descriptors for the second pass
+  int n_split = 0;
+  ts::SplitTile* d_split = nullptr;
+  float* d_scratch = nullptr;
+  long long scratch_ld = 0;
+  CUtensorMap* d_scratch_map = nullptr;   // tensor map over d_scratch, in device memory
 };
+
+void free_schedule(Schedule& s) {
+  cudaFree(s.d_units);
+  cudaFree(s.d_blocks);
+  cudaFree(s.d_meta);
+  cudaFree(s.d_split);
+  cudaFree(s.d_scratch);
+  cudaFree(s.d_scratch_map);
+  s.d_scratch_map = nullptr;
+  s.d_units = nullptr;
+  s.d_blocks = nullptr;
+  s.d_meta = nullptr;
+  s.d_split = nullptr;
+  s.d_scratch = nullptr;
+}
+
+inline bool small_activations(long long at_rows, int M);   // defined with the scheduler below
+
+// Split-K plan: parts[t] >= 1 units per batch block for tile t.  A unit's K blocks run one after the
+// other on one SM, so a launch cannot be shorter than its longest tile's K_t / 64 blocks.  A tile whose
+// share of the SMs (by its share of the K blocks) is at least twice its number of 256-row units has
+// SMs to spare or gets cut into needlessly narrow units; its kept rows are then cut into up to four
+// ranges of whole K blocks (at least 12 each), as many as keep one full-width unit per SM.  Each range
+// runs as a unit of its own whose fp32 partial sums a second kernel adds up.  Short chains (< 32
+// blocks) stay whole: the second pass costs a launch and a round trip of the partial sums.
+// Measured on B200 (VGG16 conv5, batch 64): "10 % columns + 75 % rows" as the implicit convolution
+// 66.8 -> 50.7 us with its 70-block tile cut in two; tw2 as a GEMM over the im2col matrix 41.6 -> 34.4 us
+// (list schedule: 50 SMs were idle); tw2 as the implicit convolution (share 1.9 units per SM-share, the
+// contiguous partition already fills the machine) 33.0 -> 37.2 us when cut, hence the exact "twice" there
+// and a tolerance of a tenth where the list schedule works with whole 256-row units.
+void plan_split(const std::vector<int>& k_counts, const std::vector<int>& n_counts, long long at_rows, int M,
+                int n_ctas, std::vector<int>* parts) {
+  const size_t nt = k_counts.size();
+  parts->assign(nt, 1);
+  if (M <= 0 || n_ctas <= 0) return;
+  const double units = (M + 255) / 256;
+  double blocks = 0.0;
+  long long live = 0;
+  for (size_t t = 0; t < nt; ++t) {
+    if (n_counts[t] > 0) {
+      blocks += (k_counts[t] + 63) / 64;
+      ++live;
+    }
+  }
+  if (blocks <= 0.0) return;
+  // the regime build_schedule will choose: batch rows cut freely (contiguous partition) or whole units
+  const bool contiguous = small_activations(at_rows, M) && live * static_cast<long long>(units) <= 3LL * n_ctas;
+  const double slack = contiguous ? 1e-9 : 0.1;
+  for (size_t t = 0; t < nt; ++t) {
+    const int kb = (k_counts[t] + 63) / 64;
+    if (n_counts[t] <= 0 || kb < 32) continue;
+    const double sms = n_ctas * (kb / blocks);                // the tile's share of the machine
+    const int fit = static_cast<int>(std::floor(sms / units + slack));
+    (*parts)[t] = std::max(1, std::min({4, fit, kb / 12}));
+  }
+}
 
 // Cost of one work unit of `granules` 64-row batch granules over a tile with k_count kept rows, in
 // units of 8 KiB moved between L2 and the SM: per 64-row K block 16 KiB of packed weights and 8 KiB of
@@ -324,10 +404,13 @@ void partition_blocked(const std::vector<ts::TileDesc>& tiles, const std::vector
 // batch rows of work.
 // Output: flat [rounds][grid] table; a CTA's units fill its column from round 0 without gaps,
 // tile = -1 marks the end.
+// part_kb0 (optional, one entry per tile): >= 0 marks a split-K part that starts at that K block of its
+// tile (the TileDesc then describes the part: its slice of the kept-row list, its scratch rows as
+// c_row0, no column list).
 void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, int M, int forced_unit_rows,
                     int n_ctas, std::vector<ts::WorkItem>* flat, int* rounds, int* grid, int* n_units,
                     int* unit_rows, std::vector<float>* cta_cost, std::vector<ts::BlockDesc>* blocks,
-                    int* blk_stride) {
+                    int* blk_stride, const std::vector<int>* part_kb0 = nullptr) {
   std::vector<int> order;
   for (int t = 0; t < static_cast<int>(tiles.size()); ++t) {
     if (tiles[t].n_count > 0) order.push_back(t);
@@ -370,6 +453,8 @@ void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, i
       w.w_row0 = td.w_row0;
       w.c_row0 = td.c_row0;
       w.flags = (td.relative ? ts::kItemRelative : 0) | (td.pad_ ? ts::kItemDenseRows : 0);
+      const int kb0 = part_kb0 ? (*part_kb0)[u.tile] : -1;
+      if (kb0 >= 0) w.flags |= ts::kItemScratch | (kb0 << ts::kItemKb0Shift);
       w.m_begin = u.m_begin;
       w.m_len = u.m_len;
       w.tile = u.tile;
@@ -412,8 +497,10 @@ void build_schedule(const std::vector<ts::TileDesc>& tiles, long long at_rows, i
         ts::BlockDesc d;
         d.idx = w.k_list + pos;
         d.m0 = w.m_begin;
+        // position of the block's first row inside the tile's list (a split-K part starts further in)
+        const int first = pos + ((w.flags & ts::kItemScratch) ? (w.flags >> ts::kItemKb0Shift) * 64 : 0);
         d.meta = static_cast<uint32_t>(std::min(64, w.k_count - pos)) | ((w.flags & ts::kItemRelative) ? 0x80u : 0u) |
-                 (static_cast<uint32_t>(w.m_len / 64 - 1) << 8) | (static_cast<uint32_t>(pos) << 10);
+                 (static_cast<uint32_t>(w.m_len / 64 - 1) << 8) | (static_cast<uint32_t>(first) << 10);
         (*blocks)[o++] = d;
       }
     }
@@ -447,7 +534,9 @@ struct ts_layer {
   CUtensorMap tmap;
   int* d_status = nullptr;
   // keyed by (batch size, activation row pitch, 1 for the convolution row map)
-  std::map<std::tuple<int, long long, int>, Schedule> schedules;
+  // ... and 1 when split-K units are allowed (never for calls that also write peers)
+  std::map<std::tuple<int, long long, int, int>, Schedule> schedules;
+  bool split_k = true;         // ts_layer_set_split_k
   int conv_cin = 0, conv_kh = 0, conv_kw = 0;   // set by ts_layer_set_conv: K = kh * kw * cin
   void* d_at = nullptr;
   size_t at_bytes = 0;
@@ -483,11 +572,7 @@ void free_tiles(ts_layer* l) {
   l->d_kept_k = l->d_kept_n = nullptr;
   l->d_tiles = nullptr;
   l->d_wp = nullptr;
-  for (auto& kv : l->schedules) {
-    cudaFree(kv.second.d_units);
-    cudaFree(kv.second.d_blocks);
-    cudaFree(kv.second.d_meta);
-  }
+  for (auto& kv : l->schedules) free_schedule(kv.second);
   l->schedules.clear();
   l->packed = false;
   l->ct_dirty = true;   // another tile set leaves other places of the staging output unwritten
@@ -495,8 +580,8 @@ void free_tiles(ts_layer* l) {
 
 // Schedule for batch size M over activations whose kept rows are `ld` elements apart (a matrix), or
 // over a convolution's input planes of pitch `ld` with padded image width conv_wp (conv_wp > 0).
-int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, Schedule** out) {
-  const auto key = std::make_tuple(M, ld, conv_wp);
+int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, bool allow_split, Schedule** out) {
+  const auto key = std::make_tuple(M, ld, conv_wp, allow_split ? 1 : 0);
   auto it = l->schedules.find(key);
   if (it != l->schedules.end()) {
     *out = &it->second;
@@ -504,11 +589,7 @@ int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, Schedule** out) 
   }
   if (l->schedules.size() >= 16) {  // bounded cache: drop everything, rebuild on demand
     TS_CUDA(cudaDeviceSynchronize());
-    for (auto& kv : l->schedules) {
-      cudaFree(kv.second.d_units);
-      cudaFree(kv.second.d_blocks);
-      cudaFree(kv.second.d_meta);
-    }
+    for (auto& kv : l->schedules) free_schedule(kv.second);
     l->schedules.clear();
   }
   Schedule s;
@@ -528,8 +609,64 @@ int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, Schedule** out) 
     return fail(TS_ERR_UNSUPPORTED, "activations of %lld rows x %lld elements exceed the 32 GiB the block records address",
                 at_rows, ld);
   }
-  build_schedule(l->h_tiles, at_rows, M, l->forced_unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
-                 &s.unit_rows, &s.cta_cost, &blocks, &s.blk_stride);
+  // Split-K: tiles with a long chain of K blocks become several "tiles" of the schedule, one per range
+  // of K blocks, each writing to scratch rows of its own.
+  std::vector<int> parts;
+  if (allow_split) plan_split(l->k_counts, l->n_counts, at_rows, M, l->sm_count, &parts);
+  bool any_split = false;
+  for (int p : parts) any_split = any_split || p > 1;
+  if (any_split) {
+    std::vector<ts::TileDesc> vt;
+    std::vector<int> kb0;
+    std::vector<ts::SplitTile> st;
+    int scratch_rows = 0;
+    for (size_t t = 0; t < l->h_tiles.size(); ++t) {
+      const ts::TileDesc& td = l->h_tiles[t];
+      if (parts[t] <= 1) {
+        vt.push_back(td);
+        kb0.push_back(-1);
+        continue;
+      }
+      ts::SplitTile sp;
+      sp.n_list = td.n_list;
+      sp.n_count = td.n_count;
+      sp.c_row0 = td.c_row0;
+      sp.relative = td.relative;
+      sp.parts = parts[t];
+      sp.scratch_row0 = scratch_rows;
+      sp.pad_ = 0;
+      st.push_back(sp);
+      const int kb = (td.k_count + 63) / 64;
+      for (int p = 0; p < parts[t]; ++p) {
+        const int b0 = static_cast<int>(static_cast<long long>(kb) * p / parts[t]);
+        const int b1 = static_cast<int>(static_cast<long long>(kb) * (p + 1) / parts[t]);
+        ts::TileDesc part = td;
+        part.k_list = td.k_list + static_cast<size_t>(b0) * 64;
+        part.k_count = std::min(td.k_count, b1 * 64) - b0 * 64;
+        part.n_list = nullptr;
+        part.c_row0 = scratch_rows;
+        part.pad_ = 0;          // scratch rows are written from the registers, never by a TMA store
+        vt.push_back(part);
+        kb0.push_back(b0);
+        scratch_rows += 128;
+      }
+    }
+    build_schedule(vt, at_rows, M, l->forced_unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
+                   &s.unit_rows, &s.cta_cost, &blocks, &s.blk_stride, &kb0);
+    s.n_split = static_cast<int>(st.size());
+    s.scratch_ld = M;
+    TS_CUDA(cudaMalloc(&s.d_split, st.size() * sizeof(ts::SplitTile)));
+    TS_CUDA(cudaMemcpy(s.d_split, st.data(), st.size() * sizeof(ts::SplitTile), cudaMemcpyHostToDevice));
+    TS_CUDA(cudaMalloc(&s.d_scratch, static_cast<size_t>(scratch_rows) * M * sizeof(float)));
+    CUtensorMap smap;
+    int mrc = make_scratch_tmap(&smap, s.d_scratch, scratch_rows, M);
+    if (mrc != TS_OK) return mrc;
+    TS_CUDA(cudaMalloc(&s.d_scratch_map, sizeof(CUtensorMap)));
+    TS_CUDA(cudaMemcpy(s.d_scratch_map, &smap, sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  } else {
+    build_schedule(l->h_tiles, at_rows, M, l->forced_unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
+                   &s.unit_rows, &s.cta_cost, &blocks, &s.blk_stride);
+  }
   if (!flat.empty()) {
     TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkItem)));
     TS_CUDA(cudaMemcpy(s.d_units, flat.data(), flat.size() * sizeof(ts::WorkItem),
@@ -737,13 +874,25 @@ int ts_layer_set_unit_rows(ts_layer_t* l, int unit_rows) {
   if (unit_rows == l->forced_unit_rows) return TS_OK;
   TS_CUDA(cudaSetDevice(l->device));
   TS_CUDA(cudaDeviceSynchronize());   // cached schedules may be in use by queued launches
-  for (auto& kv : l->schedules) {
-    cudaFree(kv.second.d_units);
-    cudaFree(kv.second.d_blocks);
-    cudaFree(kv.second.d_meta);
-  }
+  for (auto& kv : l->schedules) free_schedule(kv.second);
   l->schedules.clear();
   l->forced_unit_rows = unit_rows;
+  return TS_OK;
+}
+
+int ts_layer_set_split_k(ts_layer_t* l, int enabled) {
+  if (!l) return fail(TS_ERR_INVALID, "layer is NULL");
+  l->split_k = enabled != 0;
+  return TS_OK;
+}
+
+int ts_plan_split(int n_tiles, const int32_t* k_counts, const int32_t* n_counts, int64_t K, int M, int n_ctas,
+                  int32_t* parts_out) {
+  if (n_tiles < 0 || (n_tiles > 0 && (!k_counts || !n_counts || !parts_out))) return fail(TS_ERR_INVALID, "NULL argument");
+  if (M <= 0 || n_ctas <= 0) return fail(TS_ERR_INVALID, "M=%d and n_ctas=%d must be positive", M, n_ctas);
+  std::vector<int> kc(k_counts, k_counts + n_tiles), nc(n_counts, n_counts + n_tiles), parts;
+  plan_split(kc, nc, K, M, n_ctas, &parts);
+  for (int t = 0; t < n_tiles; ++t) parts_out[t] = parts[t];
   return TS_OK;
 }
 
@@ -805,9 +954,15 @@ int run_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct,
   }
   if (M == 0 || l->n_tiles == 0) return TS_OK;
   Schedule* s = nullptr;
-  rc = get_schedule(l, M, lda, conv_wp, &s);
+  // split-K units write fp32 partial sums to scratch memory of the schedule and a second kernel
+  // finishes them; calls that also write peers (tile-sharded layers) keep whole units
+  const bool allow_split = l->split_k && ep.n_peers == 0 && ep.multicast == nullptr;
+  rc = get_schedule(l, M, lda, conv_wp, allow_split, &s);
   if (rc != TS_OK) return rc;
   if (s->n_units == 0) return TS_OK;
+  ep.scratch = s->d_scratch;
+  ep.scratch_ld = s->scratch_ld;
+  ep.scratch_map = s->d_scratch_map;
   CUtensorMap tmap_c;
   rc = make_out_tmap(&tmap_c, l->dtype, Ct, l->N, M, ldc);
   if (rc != TS_OK) return rc;
@@ -842,6 +997,10 @@ int run_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct,
                                  s->grid, s->d_meta, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
                                  early, static_cast<cudaStream_t>(stream)));
   l->wp_fresh = false;
+  if (s->n_split > 0) {
+    TS_CUDA(ts::split_reduce_launch(l->dtype, s->d_split, s->n_split, s->d_scratch, s->scratch_ld, Ct, ldc, M,
+                                    ep.beta, ep.bias, ep.act, static_cast<cudaStream_t>(stream)));
+  }
   return TS_OK;
 }
 }  // namespace
@@ -1079,7 +1238,7 @@ int ts_layer_schedule_stats(ts_layer_t* l, int M, int* n_ctas, float* cta_cost, 
   if (M <= 0) return fail(TS_ERR_INVALID, "M=%d must be positive", M);
   if (!l->d_tiles) return fail(TS_ERR_INVALID, "layer has no tiles");
   Schedule* s = nullptr;
-  int rc = get_schedule(l, M, M, 0, &s);
+  int rc = get_schedule(l, M, M, 0, l->split_k, &s);
   if (rc != TS_OK) return rc;
   if (n_ctas) *n_ctas = s->grid;
   if (n_units) *n_units = s->n_units;

@@ -150,7 +150,9 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   return x;
 }
 
-template <int DT, int MT>
+// SPLIT: the schedule holds split-K parts (their code stays out of the variant every other schedule runs:
+// with it in, the BERT layer step was 1.3 % slower).
+template <int DT, int MT, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_c, int use_tma_store,
@@ -240,7 +242,9 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
         if (lane == 0) {
           const uint32_t bar = smem_u32(&bars->full[s]);
           mbar_arrive_expect_tx(bar, kWBytes);
-          tma_load_2d(smem_u32(smem + s * C::kStageBytes), &tmap_w, kb * kKB, w.w_row0, bar);
+          // (a split-K part starts at K block flags >> 8 of its tile's packed weights)
+          const int kb_first = SPLIT ? static_cast<int>(static_cast<uint32_t>(w.flags) >> kItemKb0Shift) : 0;
+          tma_load_2d(smem_u32(smem + s * C::kStageBytes), &tmap_w, (kb + kb_first) * kKB, w.w_row0, bar);
         }
         __syncwarp();
       }
@@ -455,6 +459,33 @@ masked_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w,
           mbar_arrive(smem_u32(&bars->acc_empty[a]));
         }
         if (!grp_live) continue;
+        if constexpr (SPLIT) if (w.flags & kItemScratch) {
+          // split-K part: alpha * acc leaves as fp32 for the part's 128 scratch rows.  32 fp32 columns
+          // fill one 128-row x 128-byte staging group, which goes out as one TMA tile store; bias, beta
+          // and the activation are applied by the kernel that adds the parts up.  (Tile columns past
+          // n_count carry zero weights, so their rows receive zeros.)
+          uint8_t* stage = epi + half * C::kEpiGroupBytes;
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) {
+            if (grp_col + b * 32 >= m_cnt) break;              // uniform over the half
+            if (leader) bulk_wait_read_all();
+            named_barrier_sync(half_bar, 128);
+            uint8_t* row_ptr = stage + j * 128;
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+              *reinterpret_cast<float4*>(row_ptr + ((cc ^ (j & 7)) << 4)) =
+                  make_float4(alpha * __uint_as_float(v[b][cc * 4]), alpha * __uint_as_float(v[b][cc * 4 + 1]),
+                              alpha * __uint_as_float(v[b][cc * 4 + 2]), alpha * __uint_as_float(v[b][cc * 4 + 3]));
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(half_bar, 128);
+            if (leader) {
+              tma_store_2d(ep.scratch_map, smem_u32(stage), m0 + grp_col + b * 32, w.c_row0);
+              bulk_commit();
+            }
+          }
+          continue;
+        }
         uint8_t* stage_grp = last_unit ? smem + (half * kGroups + gi) * C::kEpiGroupBytes
                                        : epi + half * C::kEpiGroupBytes;
         if (!last_unit) {
@@ -605,7 +636,47 @@ expand_block_meta_kernel(const BlockDesc* __restrict__ blocks, long long n_block
   if (r < 4) rec[r] = r == 0 ? d.m0 : (r == 1 ? static_cast<int>(d.meta) : 0);
 }
 
-template <int DT, int MT>
+// Second pass of a split-K schedule: Ct[row][m] = act(sum of the parts' fp32 partial sums + beta * Ct[row][m]
+// + bias[row]) for every kept column of every split tile.  grid (ceil(M / 8 / 256), 128, split tiles).
+template <int DT>
+__global__ void __launch_bounds__(256)
+split_reduce_kernel(const SplitTile* __restrict__ tiles, const float* __restrict__ scratch, long long sld,
+                    uint16_t* __restrict__ Ct, long long ldc, int M, float beta, const float* __restrict__ bias,
+                    int act) {
+  const SplitTile t = tiles[blockIdx.z];
+  const int j = blockIdx.y;
+  const int m = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (j >= t.n_count || m >= M) return;
+  const long long row = t.c_row0 + (t.n_list ? __ldg(t.n_list + j) + (t.relative ? j : 0) : j);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+  for (int p = 0; p < t.parts; ++p) {
+    const float4* src = reinterpret_cast<const float4*>(scratch + (static_cast<long long>(t.scratch_row0) + p * 128 + j) * sld + m);
+    const float4 a = src[0], b = src[1];
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  uint4* dst = reinterpret_cast<uint4*>(Ct + row * ldc + m);
+  uint32_t oldw[4] = {0, 0, 0, 0};
+  if (beta != 0.0f) {
+    const uint4 o = *dst;
+    oldw[0] = o.x; oldw[1] = o.y; oldw[2] = o.z; oldw[3] = o.w;
+  }
+  const float bj = bias ? __ldg(bias + row) : 0.0f;
+  uint32_t out[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float c0 = unpack1<DT>(static_cast<uint16_t>(oldw[e] & 0xffffu));
+    const float c1 = unpack1<DT>(static_cast<uint16_t>(oldw[e] >> 16));
+    const float y0 = acc[2 * e] + beta * c0 + bj;
+    const float y1 = acc[2 * e + 1] + beta * c1 + bj;
+    out[e] = pack2<DT>(apply_act(y0, act), apply_act(y1, act));
+  }
+  *dst = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+template <int DT, int MT, bool SPLIT>
 cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_c, int use_tma_store,
                            const WorkItem* sched, int rounds, int grid, const int* block_meta, int blk_stride,
                            const void* At, long long lda, void* Ct, long long ldc, int M,
@@ -614,7 +685,7 @@ cudaError_t launch_variant(const CUtensorMap& tmap_w, const CUtensorMap& tmap_c,
   // it in the stream.  The kernel reads its schedule and its packed weights before it waits for that
   // kernel, so the caller allows this only when neither was written by it.
   const bool pdl = early_start;
-  auto kern = masked_gemm_kernel<DT, MT>;
+  auto kern = masked_gemm_kernel<DT, MT, SPLIT>;
   // The dynamic shared-memory limit is a per-device, per-kernel attribute: set it once for each.
   static bool attr_set[64] = {};
   int dev = 0;
@@ -646,14 +717,30 @@ cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap
                                const WorkItem* sched, int rounds, int grid, const int* block_meta,
                                int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
                                const EpilogueArgs& ep, int* status, bool early_start, cudaStream_t stream) {
-#define TS_LAUNCH(DT, MT)                                                                                  \
-  launch_variant<DT, MT>(tmap_w, tmap_c ? *tmap_c : tmap_w, tmap_c ? 1 : 0, sched, rounds, grid, block_meta, \
-                         blk_stride, At, lda, Ct, ldc, M, ep, status, early_start, stream)
+#define TS_LAUNCH(DT, MT, SP)                                                                                  \
+  launch_variant<DT, MT, SP>(tmap_w, tmap_c ? *tmap_c : tmap_w, tmap_c ? 1 : 0, sched, rounds, grid, block_meta, \
+                             blk_stride, At, lda, Ct, ldc, M, ep, status, early_start, stream)
   const bool bf = dtype == kBF16;
-  if (unit_rows == 256) return bf ? TS_LAUNCH(kBF16, 256) : TS_LAUNCH(kF16, 256);
-  if (unit_rows == 128) return bf ? TS_LAUNCH(kBF16, 128) : TS_LAUNCH(kF16, 128);
+  const bool split = ep.scratch_map != nullptr;    // the schedule holds split-K parts
+  if (unit_rows == 256 && !split) return bf ? TS_LAUNCH(kBF16, 256, false) : TS_LAUNCH(kF16, 256, false);
+  if (unit_rows == 128 && !split) return bf ? TS_LAUNCH(kBF16, 128, false) : TS_LAUNCH(kF16, 128, false);
+  if (unit_rows == 256) return bf ? TS_LAUNCH(kBF16, 256, true) : TS_LAUNCH(kF16, 256, true);
+  if (unit_rows == 128) return bf ? TS_LAUNCH(kBF16, 128, true) : TS_LAUNCH(kF16, 128, true);
 #undef TS_LAUNCH
   return cudaErrorInvalidValue;
+}
+
+cudaError_t split_reduce_launch(int dtype, const SplitTile* tiles, int n_split, const float* scratch, long long sld,
+                                void* Ct, long long ldc, int M, float beta, const float* bias, int act,
+                                cudaStream_t stream) {
+  if (n_split <= 0 || M <= 0) return cudaSuccess;
+  dim3 grid(static_cast<unsigned>((M / 8 + 255) / 256), 128, n_split);
+  if (dtype == kBF16) {
+    split_reduce_kernel<kBF16><<<grid, 256, 0, stream>>>(tiles, scratch, sld, static_cast<uint16_t*>(Ct), ldc, M, beta, bias, act);
+  } else {
+    split_reduce_kernel<kF16><<<grid, 256, 0, stream>>>(tiles, scratch, sld, static_cast<uint16_t*>(Ct), ldc, M, beta, bias, act);
+  }
+  return cudaGetLastError();
 }
 
 cudaError_t expand_block_meta_launch(const BlockDesc* blocks, long long n_blocks, int* meta, const RowMap& map,

@@ -63,6 +63,11 @@ struct alignas(16) WorkItem {
 };
 constexpr int kItemRelative = 1;
 constexpr int kItemDenseRows = 2;
+// Split-K part: the unit covers only a range of the tile's kept rows (K blocks flags >> 8 onwards,
+// k_list / k_count already describe the part) and writes alpha * acc as fp32 into the schedule's
+// scratch rows c_row0 + j instead of Ct; a second kernel adds the parts up and finishes the epilogue.
+constexpr int kItemScratch = 4;
+constexpr int kItemKb0Shift = 8;
 static_assert(sizeof(WorkItem) == 48, "WorkItem is read as three 16-byte words");
 
 // What the GEMM epilogue does with an accumulator value x of tile column n before it is stored:
@@ -85,6 +90,23 @@ struct EpilogueArgs {
   // a tile whose kept columns are consecutive rows of Ct then leaves for every peer as TMA tile
   // stores issued by one thread, like the local copy, instead of 16-byte stores from every lane.
   const CUtensorMap* peer_maps;
+  // fp32 partial sums of split-K units: scratch[row][m], row pitch scratch_ld elements, and a tensor
+  // map over it in global memory (box 32 floats x 128 rows, 128-byte swizzle) for the units' TMA stores
+  float* scratch;
+  long long scratch_ld;
+  const CUtensorMap* scratch_map;
+};
+
+// One tile whose kept rows were split over `parts` units per batch block: part p wrote its fp32 partial
+// sums to scratch rows scratch_row0 + p * 128 + j (j = position of the kept column in the tile).
+struct SplitTile {
+  const int* n_list;
+  int n_count;
+  int c_row0;
+  int relative;
+  int parts;
+  int scratch_row0;
+  int pad_;
 };
 
 // One 64-row K block of a work unit.  A CTA's blocks are stored in processing order; the host

@@ -25,6 +25,12 @@ cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap
                                int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
                                const EpilogueArgs& ep, int* status, bool early_start, cudaStream_t stream);
 
+// Adds up the fp32 partial sums the split-K units of a schedule left in `scratch` and finishes the
+// epilogue (beta * Ct, bias, activation, conversion) for the kept columns of the split tiles.
+cudaError_t split_reduce_launch(int dtype, const SplitTile* tiles, int n_split, const float* scratch, long long sld,
+                                void* Ct, long long ldc, int M, float beta, const float* bias, int act,
+                                cudaStream_t stream);
+
 // meta[b*kBlockMetaInts ...] = record of block b, for all n_blocks (= grid*blk_stride) descriptors:
 // resolves the kept-row lists, relative or absolute, into the 16-byte segment at which each kept row
 // of the activations starts (`map`: a matrix with its row pitch, or a convolution's input planes).

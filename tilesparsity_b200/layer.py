@@ -126,6 +126,11 @@ class TWLayer:
         with torch.cuda.device(self.device):
             check(lib.ts_layer_set_unit_rows(self._h, int(unit_rows)))
 
+    def set_split_k(self, enabled: bool) -> None:
+        """Allows (default) or forbids split-K units: a tile with a long chain of K blocks cut into ranges
+        that run as units of their own, their fp32 partial sums added up by a second kernel."""
+        check(lib.ts_layer_set_split_k(self._h, 1 if enabled else 0))
+
     def close(self) -> None:
         if getattr(self, "_h", None) is not None and self._h.value:
             lib.ts_layer_destroy(self._h)
