@@ -593,6 +593,14 @@ int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, bool allow_split
     l->schedules.clear();
   }
   Schedule s;
+  // frees what has been allocated so far if a step below fails
+  struct Guard {
+    Schedule* s;
+    bool armed;
+    ~Guard() {
+      if (armed) free_schedule(*s);
+    }
+  } guard{&s, true};
   std::vector<ts::WorkItem> flat;
   std::vector<ts::BlockDesc> blocks;
   ts::RowMap map;
@@ -678,6 +686,7 @@ int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, bool allow_split
     TS_CUDA(ts::expand_block_meta_launch(s.d_blocks, static_cast<long long>(blocks.size()), s.d_meta, map, nullptr));
     TS_CUDA(cudaStreamSynchronize(nullptr));
   }
+  guard.armed = false;
   auto ins = l->schedules.emplace(key, s);
   *out = &ins.first->second;
   return TS_OK;
