@@ -110,3 +110,47 @@ def test_two_convolutions_chained_in_the_padded_layout():
     assert og.elementwise_violations(y, ref, rtol=1e-2, floor=1e-3) == 0
     l1.close()
     l2.close()
+
+
+def test_convolution_with_split_k_units():
+    """One 128-channel output tile that keeps 3456 of its 4608 kernel rows: 54 K blocks on a machine with
+    SMs to spare, so the scheduler cuts the tile's kept rows into ranges (split-K) and a second kernel
+    adds the partial sums up; with bias and ReLU in the epilogue, against the oracle and against the same
+    layer with split-K turned off."""
+    import ctypes as C
+    from tilesparsity_b200 import ConvTWLayer, _lib
+    from tilesparsity_b200.tiles import tiles_from_lists
+    g = synth.rng(77)
+    B, H, W, cin, cout, kh, kw = 16, 14, 14, 512, 128, 3, 3
+    K = kh * kw * cin
+    x = np.maximum(g.standard_normal((B, H, W, cin), dtype=np.float32), 0)
+    w = (g.standard_normal((kh, kw, cin, cout), dtype=np.float32) * np.float32(np.sqrt(2.0 / K))).astype(np.float32)
+    rows = np.sort(g.permutation(K)[:3456]).astype(np.int32)
+    ts = tiles_from_lists(K, cout, 128, [rows])
+    wd = torch.from_numpy(w).cuda()
+    layer = ConvTWLayer(wd, ts, torch.bfloat16)
+    xd = torch.from_numpy(x).to(torch.bfloat16).cuda()
+    from tilesparsity_b200.conv import geometry
+    geo = geometry(B, H, W, kh, kw)
+    parts = np.zeros(1, np.int32)
+    p32 = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    _lib.check(_lib.lib.ts_plan_split(1, p32(np.array([3456], np.int32)), p32(np.array([128], np.int32)), kw * cin,
+                                      int(geo["m_padded"]), sms, p32(parts)))
+    assert parts[0] > 1, "the case is meant to exercise split units"
+    bias = torch.from_numpy(g.standard_normal(cout, dtype=np.float32)).cuda()
+    y = layer.forward(xd, bias=bias, activation="relu")
+    layer.layer.check()
+    mask = np.zeros((K, cout), bool)
+    mask[rows] = True
+    x16 = xd.float().cpu().numpy()
+    w16 = wd.to(torch.bfloat16).float().cpu().numpy().reshape(-1, cout)
+    ref = og.masked_matmul_dense(og.im2col_nhwc(x16, kh, kw), w16, mask).reshape(B, H, W, cout)
+    ref = np.maximum(ref + bias.cpu().numpy(), 0.0)
+    out = y.float().cpu().numpy()
+    assert og.max_rel_error(out, ref) <= 1e-2
+    assert og.elementwise_violations(out, ref, rtol=1e-2, floor=1e-3) == 0
+    layer.layer.set_split_k(False)
+    y2 = layer.forward(xd, bias=bias, activation="relu")
+    assert og.max_rel_error(y2.float().cpu().numpy(), out) <= 4e-3
+    layer.close()
