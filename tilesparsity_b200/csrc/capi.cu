@@ -136,6 +136,7 @@ struct Schedule {
   float* d_scratch = nullptr;
   long long scratch_ld = 0;
   CUtensorMap* d_scratch_map = nullptr;   // tensor map over d_scratch, in device memory
+  bool all_dense = false;                 // every unit's tile keeps 128 consecutive columns (TMA tile stores only)
 };
 
 void free_schedule(Schedule& s) {
@@ -675,6 +676,10 @@ int get_schedule(ts_layer* l, int M, long long ld, int conv_wp, bool allow_split
     build_schedule(l->h_tiles, at_rows, M, l->forced_unit_rows, l->sm_count, &flat, &s.rounds, &s.grid, &s.n_units,
                    &s.unit_rows, &s.cta_cost, &blocks, &s.blk_stride);
   }
+  s.all_dense = s.n_split == 0;
+  for (const ts::WorkItem& w : flat) {
+    if (w.tile >= 0 && !(w.flags & ts::kItemDenseRows)) s.all_dense = false;
+  }
   if (!flat.empty()) {
     TS_CUDA(cudaMalloc(&s.d_units, flat.size() * sizeof(ts::WorkItem)));
     TS_CUDA(cudaMemcpy(s.d_units, flat.data(), flat.size() * sizeof(ts::WorkItem),
@@ -1004,7 +1009,7 @@ int run_masked_gemm(ts_layer_t* l, int M, const void* At, int64_t lda, void* Ct,
   const bool early = !l->wp_fresh;
   TS_CUDA(ts::masked_gemm_launch(l->dtype, s->unit_rows, l->tmap, &tmap_c, s->d_units, s->rounds,
                                  s->grid, s->d_meta, s->blk_stride, At, lda, Ct, ldc, M, ep, l->d_status,
-                                 early, static_cast<cudaStream_t>(stream)));
+                                 early, s->all_dense, static_cast<cudaStream_t>(stream)));
   l->wp_fresh = false;
   if (s->n_split > 0) {
     TS_CUDA(ts::split_reduce_launch(l->dtype, s->d_split, s->n_split, s->d_scratch, s->scratch_ld, Ct, ldc, M,
@@ -1386,7 +1391,8 @@ int ts_stream_gemm_nn(int M, int N, int K, float alpha, const void* A, const voi
   ep.alpha = alpha;
   ep.beta = beta;
   TS_CUDA(ts::masked_gemm_launch(dtype, unit_rows, tmap, nullptr, ws.d_units, rounds, grid,
-                                 ws.d_meta, blk_stride, A, M, C, M, M, ep, ws.d_status, /*early_start=*/false, s));
+                                 ws.d_meta, blk_stride, A, M, C, M, M, ep, ws.d_status, /*early_start=*/false,
+                                 /*lean=*/false, s));
   return TS_OK;
 }
 

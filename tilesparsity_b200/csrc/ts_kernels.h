@@ -20,10 +20,13 @@ namespace ts {
 // for the work items whose flags say their kept columns are consecutive rows of Ct.  early_start
 // allows programmatic dependent launch: the kernel reads sched, block_meta and the packed weights before
 // it waits for the kernel before it in the stream, so it must be false when that kernel wrote them.
+// lean: every unit of the schedule has kItemDenseRows set (the kernel then takes its store-only variant
+// when the epilogue is alpha * acc).
 cudaError_t masked_gemm_launch(int dtype, int unit_rows, const CUtensorMap& tmap_w, const CUtensorMap* tmap_c,
                                const WorkItem* sched, int rounds, int grid, const int* block_meta,
                                int blk_stride, const void* At, long long lda, void* Ct, long long ldc, int M,
-                               const EpilogueArgs& ep, int* status, bool early_start, cudaStream_t stream);
+                               const EpilogueArgs& ep, int* status, bool early_start, bool lean,
+                               cudaStream_t stream);
 
 // Adds up the fp32 partial sums the split-K units of a schedule left in `scratch` and finishes the
 // epilogue (beta * Ct, bias, activation, conversion) for the kept columns of the split tiles.
