@@ -77,15 +77,17 @@ def test_geometry_and_bad_arguments():
         conv.geometry(0, 4, 4, 3, 3)
 
 
-def test_two_convolutions_chained_in_the_padded_layout():
+@pytest.mark.parametrize("kh,kw,B,H,W", [(3, 3, 2, 6, 10), (5, 5, 1, 9, 13), (3, 7, 2, 5, 17), (1, 9, 1, 4, 23), (1, 1, 3, 5, 6)])
+def test_two_convolutions_chained_in_the_padded_layout(kh, kw, B, H, W):
     """conv -> ReLU -> conv without an NHWC round trip: the first layer's padded-space output goes
-    through ts_conv_repack straight into the second layer's input planes."""
+    through ts_conv_repack straight into the second layer's input planes (every kernel width the pack
+    and repack kernels are instantiated for)."""
     from tilesparsity_b200 import ConvTWLayer, build_mask, masks
-    g = synth.rng(909)
-    B, H, W, c0, c1, c2 = 2, 6, 10, 32, 64, 128
+    g = synth.rng(909 + kh * 10 + kw)
+    c0, c1, c2 = 32, 64, 128
     x = np.maximum(g.standard_normal((B, H, W, c0), dtype=np.float32), 0)
-    w1 = (g.standard_normal((3, 3, c0, c1), dtype=np.float32) * np.float32(np.sqrt(2.0 / (9 * c0)))).astype(np.float32)
-    w2 = (g.standard_normal((3, 3, c1, c2), dtype=np.float32) * np.float32(np.sqrt(2.0 / (9 * c1)))).astype(np.float32)
+    w1 = (g.standard_normal((kh, kw, c0, c1), dtype=np.float32) * np.float32(np.sqrt(2.0 / (kh * kw * c0)))).astype(np.float32)
+    w2 = (g.standard_normal((kh, kw, c1, c2), dtype=np.float32) * np.float32(np.sqrt(2.0 / (kh * kw * c1)))).astype(np.float32)
     dt = torch.float16
     wd1, wd2 = torch.from_numpy(w1).cuda(), torch.from_numpy(w2).cuda()
     r1 = build_mask("tw2", masks.img2col_forward([wd1]), 50.0, 128)       # prunes output channels of layer 1 too
@@ -98,13 +100,13 @@ def test_two_convolutions_chained_in_the_padded_layout():
     y = l2.unpack_output(l2.masked_conv(planes2, geo2), geo2).float().cpu().numpy()
     # oracle: layer 1 in float32 on the 16-bit inputs, rounded to 16 bit as the GPU stores it, then layer 2
     x16 = xd.float().cpu().numpy()
-    a1 = og.masked_matmul_dense(og.im2col_nhwc(x16, 3, 3), wd1.to(dt).float().cpu().numpy().reshape(-1, c1),
+    a1 = og.masked_matmul_dense(og.im2col_nhwc(x16, kh, kw), wd1.to(dt).float().cpu().numpy().reshape(-1, c1),
                                 r1.masks[0].cpu().numpy())
     a1 = np.maximum(a1, 0).astype(np.float16).astype(np.float32).reshape(B, H, W, c1)
     # the GPU's own layer-1 output must be that, up to the last bit of the 16-bit rounding
     got1 = l1.unpack_output(ct1, geo).float().cpu().numpy()
     assert og.max_rel_error(got1, a1) <= 1e-2
-    ref = og.masked_matmul_dense(og.im2col_nhwc(got1, 3, 3), wd2.to(dt).float().cpu().numpy().reshape(-1, c2),
+    ref = og.masked_matmul_dense(og.im2col_nhwc(got1, kh, kw), wd2.to(dt).float().cpu().numpy().reshape(-1, c2),
                                  r2.masks[0].cpu().numpy()).reshape(B, H, W, c2)
     assert og.max_rel_error(y, ref) <= 1e-2
     assert og.elementwise_violations(y, ref, rtol=1e-2, floor=1e-3) == 0

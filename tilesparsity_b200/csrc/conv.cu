@@ -108,6 +108,69 @@ conv_pack_input_kernel(const uint16_t* __restrict__ x, int B, int H, int W, int 
   }
 }
 
+// The same packing without shared memory, for images whose padded pixel count stays below the range of
+// the reciprocal divisions: a thread takes one group of 8 padded pixels and 8 channels, reads the
+// 8 + KW - 1 input pixels the group's taps touch (16 bytes = 8 channels each; zeros outside the image),
+// transposes them in registers (two byte permutes per output word) and writes, for every tap and every
+// one of its channels, the 8 pixels as one 16-byte store.  Lanes run along the pixel groups, so a warp's
+// store instruction covers 512 contiguous bytes of one plane row; the loads of a warp touch 32 pixels,
+// whose other channels neighbouring blocks (blockIdx.y) pick up from L2.  Threads past the last image
+// zero the planes' tails.  grid (ceil(plane_ld / 8 / 128), C / 8), block 128.
+template <int KW>
+__global__ void __launch_bounds__(128)
+conv_pack_input_reg_kernel(const uint16_t* __restrict__ x, int H, int W, int C, int kh, int Hp, int Wp,
+                           int n_groups, int n_groups_ld, uint32_t mul_wp8, uint32_t mul_hp,
+                           uint16_t* __restrict__ planes, long long plane_ld) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;   // group of 8 padded pixels
+  if (g >= n_groups_ld) return;
+  const int c0 = blockIdx.y * 8;
+  const long long m0 = static_cast<long long>(g) << 3;
+  if (g >= n_groups) {
+#pragma unroll
+    for (int j = 0; j < KW; ++j) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        *reinterpret_cast<uint4*>(planes + (static_cast<long long>(j) * C + c0 + c) * plane_ld + m0) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+  constexpr int PW = (KW - 1) / 2;
+  const int ph = (kh - 1) / 2;
+  const int wp8 = Wp >> 3;
+  const int row = mul_wp8 ? static_cast<int>(__umulhi(static_cast<uint32_t>(g), mul_wp8)) : g;   // padded image row, all images
+  const int x0 = (g - row * wp8) << 3;
+  const int img = mul_hp ? static_cast<int>(__umulhi(static_cast<uint32_t>(row), mul_hp)) : row;
+  const int y = row - img * Hp - ph;
+  uint4 px[8 + KW - 1];
+  const bool row_ok = y >= 0 && y < H;
+  const uint16_t* src = x + ((static_cast<long long>(img) * H + (row_ok ? y : 0)) * W) * C + c0;
+#pragma unroll
+  for (int k = 0; k < 8 + KW - 1; ++k) {
+    const int xs = x0 + k - PW;
+    px[k] = (row_ok && xs >= 0 && xs < W) ? __ldg(reinterpret_cast<const uint4*>(src + static_cast<long long>(xs) * C))
+                                          : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int j = 0; j < KW; ++j) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {           // channel pair (2q, 2q + 1): word q of every pixel
+      uint32_t lo[4], hi[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {         // pixels 2t, 2t + 1 of the tap's window
+        const uint4 a = px[j + 2 * t], b = px[j + 2 * t + 1];
+        const uint32_t wa = q == 0 ? a.x : (q == 1 ? a.y : (q == 2 ? a.z : a.w));
+        const uint32_t wb = q == 0 ? b.x : (q == 1 ? b.y : (q == 2 ? b.z : b.w));
+        lo[t] = __byte_perm(wa, wb, 0x5410);
+        hi[t] = __byte_perm(wa, wb, 0x7632);
+      }
+      uint16_t* dst = planes + (static_cast<long long>(j) * C + c0 + 2 * q) * plane_ld + m0;
+      *reinterpret_cast<uint4*>(dst) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      *reinterpret_cast<uint4*>(dst + plane_ld) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    }
+  }
+}
+
 // y[b][yy][xx][n] = Ct[n][b*Hp*Wp + yy*Wp + xx] for yy < H, xx < W.  grid (ceil(H / 4), B, ceil(N / 64)),
 // block 256: 16-byte loads along the pixels, 16-byte stores along the channels.  Needs N % 8 == 0,
 // ldc % 8 == 0 and 16-byte aligned pointers.
@@ -220,6 +283,66 @@ conv_repack_kernel(const uint16_t* __restrict__ ct, long long ldc, int H, int W,
   }
 }
 
+// The repack with all taps of a pixel group produced from one read: a thread loads, per channel, the
+// three aligned 16-byte groups around the source position (24 elements; the neighbours' groups come out
+// of L1) and cuts every tap's 8 elements out of them with funnel shifts; 16-byte stores, lanes along the
+// pixel groups.  grid (ceil(plane_ld / 8 / 128), ceil(C / 8)), block 128, kRepackCh channels per thread.
+template <int KW>
+__global__ void __launch_bounds__(128)
+conv_repack_reg_kernel(const uint16_t* __restrict__ ct, long long ldc, int H, int W, int Hp, int Wp, int kh,
+                       int n_groups, int n_groups_ld, uint32_t mul_wp8, uint32_t mul_hp,
+                       uint16_t* __restrict__ planes, long long plane_ld, int C) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;   // group of 8 padded pixels
+  if (g >= n_groups_ld) return;
+  const int c_begin = blockIdx.y * kRepackCh, c_end = min(C, c_begin + kRepackCh);
+  const long long m0 = static_cast<long long>(g) << 3;
+  constexpr int PW = (KW - 1) / 2;
+  const int ph = (kh - 1) / 2;
+  const int wp8 = Wp >> 3;
+  int x0 = 0, y = -1;
+  if (g < n_groups) {
+    const int row = mul_wp8 ? static_cast<int>(__umulhi(static_cast<uint32_t>(g), mul_wp8)) : g;
+    x0 = (g - row * wp8) << 3;
+    const int img = mul_hp ? static_cast<int>(__umulhi(static_cast<uint32_t>(row), mul_hp)) : row;
+    y = row - img * Hp - ph;
+  }
+  const bool inside = g < n_groups && y >= 0 && y < H && x0 - PW < W;   // else zeros (halo rows, scratch, tails)
+  const long long gs = static_cast<long long>(g) - static_cast<long long>(ph) * wp8;   // source group of tap offset 0
+  const long long ld8 = ldc >> 3;
+  for (int c = c_begin; c < c_end; ++c) {
+    uint32_t w[12];
+#pragma unroll
+    for (int k = 0; k < 12; ++k) w[k] = 0u;
+    if (inside) {
+      const uint4* src_row = reinterpret_cast<const uint4*>(ct + static_cast<long long>(c) * ldc);
+#pragma unroll
+      for (int k = 0; k < 3; ++k) {
+        const long long gi = gs + k - 1;
+        if (gi >= 0 && gi < ld8) {
+          const uint4 v = __ldg(src_row + gi);
+          w[4 * k] = v.x; w[4 * k + 1] = v.y; w[4 * k + 2] = v.z; w[4 * k + 3] = v.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < KW; ++j) {
+      constexpr int kBase = 8 - PW;                 // window element of output element 0 for tap 0
+      const int first = kBase + j;                  // ... for tap j (compile-time after unrolling)
+      uint32_t r[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int e0 = first + 2 * t;               // window element of output element 2t
+        r[t] = (e0 & 1) ? __funnelshift_r(w[e0 >> 1], w[(e0 >> 1) + 1], 16) : w[e0 >> 1];
+        const int xa = x0 + 2 * t + j - PW, xb = xa + 1;
+        if (xa < 0 || xa >= W) r[t] &= 0xffff0000u;
+        if (xb < 0 || xb >= W) r[t] &= 0x0000ffffu;
+      }
+      *reinterpret_cast<uint4*>(planes + (static_cast<long long>(j) * C + c) * plane_ld + m0) =
+          make_uint4(r[0], r[1], r[2], r[3]);
+    }
+  }
+}
+
 }  // namespace
 
 cudaError_t conv_repack_launch(const void* ct, long long ldc, int B, int H, int W, int Hp, int Wp, int kh, int kw,
@@ -231,6 +354,22 @@ cudaError_t conv_repack_launch(const void* ct, long long ldc, int B, int H, int 
   if (n_groups * std::max<long long>(Wp / 8, Hp) >= (1LL << 32) || n_groups_ld >= (1LL << 31)) return cudaErrorInvalidValue;
   const uint32_t mul_wp8 = Wp / 8 > 1 ? 0xffffffffu / static_cast<uint32_t>(Wp / 8) + 1u : 0u;
   const uint32_t mul_hp = Hp > 1 ? 0xffffffffu / static_cast<uint32_t>(Hp) + 1u : 0u;
+  if (kw == 1 || kw == 3 || kw == 5 || kw == 7 || kw == 9) {
+    dim3 rgrid(static_cast<unsigned>((n_groups_ld + 127) / 128), (C + kRepackCh - 1) / kRepackCh);
+#define TS_REPACK(KW)                                                                                           \
+  conv_repack_reg_kernel<KW><<<rgrid, 128, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, H, W, Hp, Wp, kh, \
+                                                        static_cast<int>(n_groups), static_cast<int>(n_groups_ld),  \
+                                                        mul_wp8, mul_hp, static_cast<uint16_t*>(planes), plane_ld, C)
+    switch (kw) {
+      case 1: TS_REPACK(1); break;
+      case 3: TS_REPACK(3); break;
+      case 5: TS_REPACK(5); break;
+      case 7: TS_REPACK(7); break;
+      default: TS_REPACK(9); break;
+    }
+#undef TS_REPACK
+    return cudaGetLastError();
+  }
   dim3 grid(static_cast<unsigned>((n_groups_ld + 255) / 256), (C + kRepackCh - 1) / kRepackCh, kw);
   conv_repack_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, H, W, Hp, Wp, kh, kw,
                                                static_cast<int>(n_groups), static_cast<int>(n_groups_ld), mul_wp8,
@@ -241,8 +380,32 @@ cudaError_t conv_repack_launch(const void* ct, long long ldc, int B, int H, int 
 cudaError_t conv_pack_input_launch(const void* x_nhwc, int B, int H, int W, int C, int kh, int kw, int Hp, int Wp,
                                    void* planes, long long plane_ld, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || W <= 0 || C <= 0) return cudaSuccess;
-  // the tail of every plane past the last image (read by the lowest kernel rows of the last pixels)
   const long long m_pad = static_cast<long long>(B) * Hp * Wp;
+  const long long n_groups = m_pad / 8, n_groups_ld = plane_ld / 8;
+  // register-transpose kernel: floor(i / d) = umulhi(i, ceil(2^32 / d)) holds for i * d < 2^32
+  const bool reg_ok = (C % 8) == 0 && C / 8 <= 65535 && n_groups_ld < (1LL << 31) &&
+                      n_groups * std::max<long long>(Wp / 8, Hp) < (1LL << 32) &&
+                      (kw == 1 || kw == 3 || kw == 5 || kw == 7 || kw == 9);
+  if (reg_ok) {
+    const uint32_t mul_wp8 = Wp / 8 > 1 ? 0xffffffffu / static_cast<uint32_t>(Wp / 8) + 1u : 0u;
+    const uint32_t mul_hp = Hp > 1 ? 0xffffffffu / static_cast<uint32_t>(Hp) + 1u : 0u;
+    dim3 grid(static_cast<unsigned>((n_groups_ld + 127) / 128), C / 8);
+    const uint16_t* xin = static_cast<const uint16_t*>(x_nhwc);
+    uint16_t* pl = static_cast<uint16_t*>(planes);
+#define TS_PACK(KW)                                                                                             \
+  conv_pack_input_reg_kernel<KW><<<grid, 128, 0, stream>>>(xin, H, W, C, kh, Hp, Wp, static_cast<int>(n_groups), \
+                                                           static_cast<int>(n_groups_ld), mul_wp8, mul_hp, pl, plane_ld)
+    switch (kw) {
+      case 1: TS_PACK(1); break;
+      case 3: TS_PACK(3); break;
+      case 5: TS_PACK(5); break;
+      case 7: TS_PACK(7); break;
+      default: TS_PACK(9); break;
+    }
+#undef TS_PACK
+    return cudaGetLastError();
+  }
+  // the tail of every plane past the last image (read by the lowest kernel rows of the last pixels)
   if (plane_ld > m_pad) {
     cudaError_t e = cudaMemset2DAsync(static_cast<uint16_t*>(planes) + m_pad, plane_ld * 2, 0, (plane_ld - m_pad) * 2,
                                       static_cast<size_t>(kw) * C, stream);
