@@ -212,6 +212,44 @@ conv_unpack_output_kernel(const uint16_t* __restrict__ ct, long long ldc, int B,
   }
 }
 
+// The unpacking without shared memory: a thread takes one group of 8 padded pixels and 8 output channels,
+// reads the 8 channel rows (16 bytes each, a warp 512 contiguous bytes per row), transposes in registers
+// and writes the pixels that exist as 16-byte pieces of their NHWC rows (the neighbouring channel blocks
+// complete the sectors in L2).  grid (ceil(m_pad / 8 / 128), N / 8), block 128.
+__global__ void __launch_bounds__(128)
+conv_unpack_output_reg_kernel(const uint16_t* __restrict__ ct, long long ldc, int H, int W, int Hp, int Wp, int N,
+                              int n_groups, uint32_t mul_wp8, uint32_t mul_hp, uint16_t* __restrict__ y) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;   // group of 8 padded pixels
+  if (g >= n_groups) return;
+  const int n0 = blockIdx.y * 8;
+  const int wp8 = Wp >> 3;
+  const int row = mul_wp8 ? static_cast<int>(__umulhi(static_cast<uint32_t>(g), mul_wp8)) : g;
+  const int x0 = (g - row * wp8) << 3;
+  const int img = mul_hp ? static_cast<int>(__umulhi(static_cast<uint32_t>(row), mul_hp)) : row;
+  const int yy = row - img * Hp;
+  if (yy >= H || x0 >= W) return;                         // scratch rows and columns of the padded space
+  const uint4* src = reinterpret_cast<const uint4*>(ct + static_cast<long long>(n0) * ldc) + g;
+  const long long ld8 = ldc >> 3;
+  uint4 ch[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) ch[c] = __ldg(src + c * ld8);
+  uint16_t* dst = y + ((static_cast<long long>(img) * H + yy) * W + x0) * N + n0;
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {           // pixels 2t, 2t + 1: word t of every channel row
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {         // channels 2q, 2q + 1
+      const uint4 a = ch[2 * q], b = ch[2 * q + 1];
+      const uint32_t wa = t == 0 ? a.x : (t == 1 ? a.y : (t == 2 ? a.z : a.w));
+      const uint32_t wb = t == 0 ? b.x : (t == 1 ? b.y : (t == 2 ? b.z : b.w));
+      lo[q] = __byte_perm(wa, wb, 0x5410);
+      hi[q] = __byte_perm(wa, wb, 0x7632);
+    }
+    if (x0 + 2 * t < W) *reinterpret_cast<uint4*>(dst + static_cast<long long>(2 * t) * N) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    if (x0 + 2 * t + 1 < W) *reinterpret_cast<uint4*>(dst + static_cast<long long>(2 * t + 1) * N) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  }
+}
+
 // Padded-space output of one convolution -> input planes of the next (same image size and padding
 // geometry): planes[j][c][m] = Ct[c][m - ph*Wp + j - pw] where that position is a real pixel, else 0.
 // Both sides are channel-major, so this is a shifted, masked copy with 16-byte stores.  The source of
@@ -420,6 +458,17 @@ cudaError_t conv_pack_input_launch(const void* x_nhwc, int B, int H, int W, int 
 cudaError_t conv_unpack_output_launch(const void* ct, long long ldc, int B, int H, int W, int Hp, int Wp, int N,
                                       void* y_nhwc, cudaStream_t stream) {
   if (B <= 0 || H <= 0 || W <= 0 || N <= 0) return cudaSuccess;
+  const long long n_groups = static_cast<long long>(B) * Hp * Wp / 8;
+  // register-transpose kernel: floor(i / d) = umulhi(i, ceil(2^32 / d)) holds for i * d < 2^32
+  if ((N % 8) == 0 && N / 8 <= 65535 && n_groups < (1LL << 31) && n_groups * std::max<long long>(Wp / 8, Hp) < (1LL << 32)) {
+    const uint32_t mul_wp8 = Wp / 8 > 1 ? 0xffffffffu / static_cast<uint32_t>(Wp / 8) + 1u : 0u;
+    const uint32_t mul_hp = Hp > 1 ? 0xffffffffu / static_cast<uint32_t>(Hp) + 1u : 0u;
+    dim3 rgrid(static_cast<unsigned>((n_groups + 127) / 128), N / 8);
+    conv_unpack_output_reg_kernel<<<rgrid, 128, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, H, W, Hp, Wp, N,
+                                                             static_cast<int>(n_groups), mul_wp8, mul_hp,
+                                                             static_cast<uint16_t*>(y_nhwc));
+    return cudaGetLastError();
+  }
   dim3 grid((H + kPackRows - 1) / kPackRows, B, (N + kPackCh - 1) / kPackCh);
   conv_unpack_output_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(ct), ldc, B, H, W, Hp, Wp, N,
                                                       static_cast<uint16_t*>(y_nhwc));
