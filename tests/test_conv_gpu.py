@@ -42,6 +42,8 @@ def _run(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype, seed, relu_in=Tr
     (3, 14, 14, 64, 256, 3, 3, "tw2", 75.0, None, torch.bfloat16),         # pruned output channels
     (1, 9, 20, 32, 136, 5, 3, "tw1", 60.0, None, torch.float16),           # non-square kernel, Wp > W + kw - 1
     (4, 8, 8, 128, 128, 1, 1, "tw1", 75.0, None, torch.bfloat16),          # 1 x 1: a plain GEMM over pixels
+    (1, 224, 224, 8, 16, 3, 3, "tw1", 50.0, None, torch.float16),          # ImageNet-sized image, 226 x 232 padded
+    (2, 30, 41, 8, 24, 7, 5, "tw1", 40.0, None, torch.bfloat16),           # wide kernel, Wp / 8 and Hp not powers of two
 ])
 def test_small_convolutions_match_the_oracle(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype):
     layer, _, _ = _run(B, H, W, cin, cout, kh, kw, algo, sparsity, g1, dtype, seed=B + H + W + cin)
